@@ -1,0 +1,182 @@
+"""ctypes binding of ``libflashsinkhorn_b200.so`` (the sm_100a CUDA engine).
+
+The shared library is the product; this module only marshals PyTorch device
+pointers, the current CUDA stream and a caller-owned workspace into the C ABI
+declared in ``include/flash_sinkhorn_b200.h``. There is no fallback: if the
+library is missing, or a call returns a non-zero status, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_double, c_float, c_int, c_size_t, c_void_p
+from typing import Optional
+
+import torch
+
+_LIB_NAME = "libflashsinkhorn_b200.so"
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", _LIB_NAME)
+
+PREC_TF32 = 0
+PREC_FP32 = 1
+PREC_SIMT = 2
+
+OP_LSE = 0
+OP_STEP = 1
+OP_SOLVE_SYMMETRIC = 2
+OP_SOLVE_ALTERNATING = 3
+OP_APPLY_VEC = 4
+OP_APPLY_MAT = 5
+OP_GRAD = 6
+OP_MAT5 = 7
+OP_SCHUR = 8
+
+_STATUS_NAMES = {
+    1: "FS_ERR_BAD_ARG",
+    2: "FS_ERR_UNSUPPORTED",
+    3: "FS_ERR_CUDA",
+    4: "FS_ERR_TIMEOUT",
+    5: "FS_ERR_WORKSPACE",
+}
+
+# name -> (restype, argtypes); mirrors include/flash_sinkhorn_b200.h one to one.
+_P = c_void_p
+SIGNATURES = {
+    "fs_version": (c_int, []),
+    "fs_last_error": (c_char_p, []),
+    "fs_device_arch": (c_int, []),
+    "fs_launch_count": (ctypes.c_longlong, []),
+    "fs_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "fs_lse": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_float, c_float, c_float, c_int, _P, c_size_t, _P]),
+    "fs_symmetric_step": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
+         c_float, c_float, c_float, c_float, c_float, c_int, _P, c_size_t, _P],
+    ),
+    "fs_solve_symmetric": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_float, c_double, c_double,
+         c_double, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_size_t, _P],
+    ),
+    "fs_solve_alternating": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_float, c_double, c_double,
+         c_int, c_double, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_size_t, _P],
+    ),
+    "fs_apply_vec": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_float, c_int, c_float, c_int, _P, c_size_t, _P],
+    ),
+    "fs_apply_mat": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_float, c_int, c_float,
+         c_int, _P, c_size_t, _P],
+    ),
+    "fs_grad": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float,
+         c_int, _P, c_size_t, _P],
+    ),
+    "fs_mat5": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_float, c_float, c_int, _P, c_size_t, _P],
+    ),
+    "fs_schur_cg": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float, c_int,
+         c_float, c_float, c_int, _P, c_size_t, _P],
+    ),
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class FlashSinkhornError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+def library_path() -> str:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Load the CUDA library (once). Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_NAME} not found at {_LIB_PATH}. Build it with "
+            "`python -m flash_sinkhorn_b200.build_ext` (needs nvcc with sm_100a support). "
+            "There is no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(_LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def precision_id(allow_tf32: bool) -> int:
+    """``allow_tf32`` of the reference API -> engine precision mode.
+
+    The environment variable FLASH_SINKHORN_B200_PREC (tf32|fp32|simt) overrides it,
+    which the tests use to cross-check the engines against each other.
+    """
+    env = os.environ.get("FLASH_SINKHORN_B200_PREC", "").lower()
+    if env == "simt":
+        return PREC_SIMT
+    if env == "fp32":
+        return PREC_FP32
+    if env == "tf32":
+        return PREC_TF32
+    return PREC_TF32 if allow_tf32 else PREC_FP32
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def f32c(t: torch.Tensor) -> torch.Tensor:
+    """Contiguous fp32 view/copy (the engine reads fp32 only)."""
+    if t.dtype != torch.float32:
+        t = t.float()
+    return t.contiguous()
+
+
+def require_cuda(**tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor.")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"{name} must be on the same CUDA device as the other tensors ({dev}), got {t.device}")
+    assert dev is not None
+    return dev
+
+
+def workspace(op: int, n: int, m: int, d: int, prec: int, device: torch.device) -> torch.Tensor:
+    nbytes = int(load().fs_workspace_bytes(op, n, m, d, prec))
+    return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+
+
+def stream_ptr(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def call(name: str, device: torch.device, *args) -> None:
+    """Invoke a compute entry point with `device` current; raise on failure."""
+    lib = load()
+    with torch.cuda.device(device):
+        status = getattr(lib, name)(*args)
+    if status != 0:
+        msg = lib.fs_last_error().decode("utf-8", "replace")
+        raise FlashSinkhornError(f"{name} failed with {_STATUS_NAMES.get(status, status)}: {msg}")

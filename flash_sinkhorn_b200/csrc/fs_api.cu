@@ -1,0 +1,783 @@
+// C-ABI layer: argument checks, workspace carving, the solver/CG drivers and the
+// small vector kernels that sit between streaming passes. All device work is
+// enqueued on the caller's stream; nothing here allocates or synchronises.
+#include "../../include/flash_sinkhorn_b200.h"
+#include "fs_common.cuh"
+#include "fs_tc.cuh"
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+namespace fs {
+namespace {
+
+thread_local char g_err[512] = "";
+
+// Kernels enqueued by this library since load (all threads); read by fs_launch_count().
+std::atomic<long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FS_CUDA(expr)                                                                      \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess)                                                                 \
+      return fail(FS_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),     \
+                  __FILE__, __LINE__);                                                     \
+  } while (0)
+
+#define FS_TRY(expr)                 \
+  do {                               \
+    int _s = (expr);                 \
+    if (_s != FS_OK) return _s;      \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// Workspace: bump allocator; with base == nullptr it only measures.
+// ---------------------------------------------------------------------------
+struct Ws {
+  char* base;
+  size_t cap;
+  size_t off = 0;
+  bool overflow = false;
+  Ws(void* b, size_t c) : base(static_cast<char*>(b)), cap(c) {}
+  template <typename T>
+  T* take(size_t count) {
+    size_t bytes = (count * sizeof(T) + 255) & ~size_t(255);
+    size_t o = off;
+    off += bytes;
+    if (!base) return nullptr;
+    if (off > cap) { overflow = true; return nullptr; }
+    return reinterpret_cast<T*>(base + o);
+  }
+};
+
+// ---------------------------------------------------------------------------
+// Small vector kernels
+// ---------------------------------------------------------------------------
+// out_i = coef * |row_i|^2, one warp per row.
+__global__ void sqnorm_kernel(const float* __restrict__ x, int n, int d, float coef, float* __restrict__ out) {
+  int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (warp >= n) return;
+  const float* r = x + (size_t)warp * d;
+  float s = 0.f;
+  for (int k = lane; k < d; k += 32) { float v = r[k]; s = fmaf(v, v, s); }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) out[warp] = coef * s;
+}
+
+// out = ca*a + cb*b (a or b may be null => treated as 0)
+__global__ void axpby_kernel(int n, float ca, const float* a, float cb, const float* b, float* out) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = 0.f;
+  if (a) v += ca * a[i];
+  if (b) v += cb * b[i];
+  out[i] = v;
+}
+
+__global__ void fill_kernel(int n, float v, float* out) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = v;
+}
+
+__global__ void ctrl_init_kernel(Ctrl* c, int have_prev) {
+  c->delta_bits = 0u;
+  c->converged = 0;
+  c->have_prev = have_prev;
+  c->iters_used = 0;
+  c->error = 0;
+}
+
+__global__ void bump_iters_kernel(Ctrl* c, int only_if_running) {
+  if (only_if_running && c->converged) return;
+  c->iters_used += 1;
+}
+
+// max |cur - prev| over both potentials -> ctrl->delta_bits
+__global__ void delta_kernel(const float* f, const float* pf, int n, const float* g, const float* pg, int m,
+                             Ctrl* c) {
+  if (c->converged || !c->have_prev) return;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  float d = 0.f;
+  if (i < n) d = fabsf(f[i] - pf[i]);
+  else if (i < n + m) d = fabsf(g[i - n] - pg[i - n]);
+  // NaN compares false everywhere in the reference's `max(...) < threshold`; map NaN to +inf.
+  if (d != d) d = INFINITY;
+#pragma unroll
+  for (int o = 16; o; o >>= 1) d = fmaxf(d, __shfl_xor_sync(0xffffffffu, d, o));
+  if ((threadIdx.x & 31) == 0 && d > 0.f) atomicMax(&c->delta_bits, __float_as_uint(d));
+}
+
+__global__ void decide_kernel(Ctrl* c, double threshold) {
+  if (c->converged) return;
+  if (c->have_prev) {
+    float d = __uint_as_float(c->delta_bits);
+    if ((double)d < threshold) c->converged = 1;
+  }
+  c->have_prev = 1;
+  c->delta_bits = 0u;
+}
+
+__global__ void snapshot_kernel(const float* f, float* pf, int n, const float* g, float* pg, int m,
+                                const Ctrl* c) {
+  if (c->converged) return;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) pf[i] = f[i];
+  else if (i < n + m) pg[i - n] = g[i - n];
+}
+
+__global__ void copy_int_kernel(const int* src, int* dst) { *dst = *src; }
+
+inline dim3 g1(int n, int bs = 256) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);  // every small-kernel launch sizes its grid here
+  return dim3((n + bs - 1) / bs);
+}
+
+// ---------------------------------------------------------------------------
+// Problem: the two clouds plus engine selection. Side 0 streams rows of x
+// against y (f-update, P v); side 1 streams rows of y against x (g-update, P^T v).
+// ---------------------------------------------------------------------------
+struct Problem {
+  const float* x;
+  const float* y;
+  int n, m, d;
+  float cs;
+  int prec;
+  cudaStream_t st;
+  const int* csr_rp[2] = {nullptr, nullptr};
+  const int* csr_ci[2] = {nullptr, nullptr};
+  tc::Staged staged;  // tcgen05 operands (valid when use_tc)
+  bool use_tc = false;
+
+  StreamArgs stream_args(int side, const float* pot, const float* logw, float eps) const {
+    StreamArgs s;
+    s.rows = side == 0 ? x : y;
+    s.cols = side == 0 ? y : x;
+    s.nr = side == 0 ? n : m;
+    s.nc = side == 0 ? m : n;
+    s.d = d;
+    s.pot = pot;
+    s.logw = logw;
+    s.eps = eps;
+    s.cost_scale = cs;
+    s.tile_row_ptr = csr_rp[side];
+    s.tile_col_idx = csr_ci[side];
+    return s;
+  }
+
+  cudaError_t lse(int side, const float* pot, const float* logw, float eps, const LseEpilogue& ep) const {
+    StreamArgs s = stream_args(side, pot, logw, eps);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (use_tc) return tc::lse(staged, side, s, ep, st);
+    return simt_lse(s, ep, st);
+  }
+  cudaError_t vec(int side, const float* pot, const float* logw, float eps, const VecArgs& v) const {
+    StreamArgs s = stream_args(side, pot, logw, eps);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return simt_vec(s, v, st);
+  }
+  cudaError_t pv(int side, const float* pot, const float* logw, float eps, const PvArgs& p) const {
+    StreamArgs s = stream_args(side, pot, logw, eps);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return simt_pv(s, p, st);
+  }
+};
+
+int check_common(const void* x, const void* y, int n, int m, int d, float eps, float cost_scale, int prec) {
+  if (!x || !y) return fail(FS_ERR_BAD_ARG, "x and y must be non-null device pointers");
+  if (n <= 0 || m <= 0 || d <= 0) return fail(FS_ERR_BAD_ARG, "n, m, d must be positive (got %d, %d, %d)", n, m, d);
+  if (!(eps > 0.f)) return fail(FS_ERR_BAD_ARG, "eps must be > 0 (got %g)", (double)eps);
+  if (!(cost_scale > 0.f)) return fail(FS_ERR_BAD_ARG, "cost_scale must be > 0 (got %g)", (double)cost_scale);
+  if (prec != FS_PREC_TF32 && prec != FS_PREC_FP32 && prec != FS_PREC_SIMT)
+    return fail(FS_ERR_BAD_ARG, "unknown precision mode %d", prec);
+  return FS_OK;
+}
+
+int check_device() {
+  int arch = fs_device_arch();
+  if (arch < 0) return fail(FS_ERR_CUDA, "cannot query the current CUDA device");
+  if (arch / 10 != 10) return fail(FS_ERR_UNSUPPORTED, "this library is built for sm_100a only; current device is sm_%d", arch);
+  return FS_OK;
+}
+
+// Sets up `p` (engine choice + staged tcgen05 operands carved from ws).
+// `lse_only` is true for ops that only run LSE passes.
+int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int m, int d, float cs, int prec,
+                 cudaStream_t st, bool measure_only) {
+  p.x = x; p.y = y; p.n = n; p.m = m; p.d = d; p.cs = cs; p.prec = prec; p.st = st;
+  p.use_tc = (prec != FS_PREC_SIMT) && tc::supported(n, m, d, prec);
+  if (p.use_tc) {
+    size_t bytes = tc::staged_bytes(n, m, d, prec);
+    char* buf = ws.take<char>(bytes);
+    if (!measure_only) {
+      if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
+      cudaError_t e = tc::stage(p.staged, buf, x, y, n, m, d, prec, st);
+      if (e != cudaSuccess) return fail(FS_ERR_CUDA, "staging tcgen05 operands failed: %s", cudaGetErrorString(e));
+    }
+  }
+  return FS_OK;
+}
+
+struct SolveBufs {
+  float *alpha, *beta, *fh[2], *gh[2], *pf, *pg, *zeros_n, *zeros_m;
+  Ctrl* ctrl;
+};
+
+void carve_solve(Ws& ws, SolveBufs& b, int n, int m) {
+  b.ctrl = ws.take<Ctrl>(1);
+  b.alpha = ws.take<float>(n);
+  b.beta = ws.take<float>(m);
+  for (int i = 0; i < 2; ++i) { b.fh[i] = ws.take<float>(n); b.gh[i] = ws.take<float>(m); }
+  b.pf = ws.take<float>(n);
+  b.pg = ws.take<float>(m);
+  b.zeros_n = ws.take<float>(n);
+  b.zeros_m = ws.take<float>(m);
+}
+
+inline double dampening(double eps, double rho) {
+  if (!(rho >= 0.0)) return 1.0;  // negative or NaN: balanced
+  return 1.0 / (1.0 + eps / rho);
+}
+
+}  // namespace
+}  // namespace fs
+
+using namespace fs;
+
+extern "C" {
+
+int fs_version(void) { return 100; }
+
+long long fs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* fs_last_error(void) { return g_err; }
+
+int fs_device_arch(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  int major = 0, minor = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) return -1;
+  return major * 10 + minor;
+}
+
+size_t fs_workspace_bytes(int op, int n, int m, int d, int prec) {
+  if (n <= 0 || m <= 0 || d <= 0) return 0;
+  Ws ws(nullptr, 0);
+  Problem p;
+  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true);
+  size_t nm = (size_t)(n > m ? n : m);
+  switch (op) {
+    case FS_OP_LSE:
+      ws.take<float>(nm);
+      break;
+    case FS_OP_STEP:
+      ws.take<float>(nm);
+      break;
+    case FS_OP_SOLVE_SYMMETRIC:
+    case FS_OP_SOLVE_ALTERNATING: {
+      SolveBufs b;
+      carve_solve(ws, b, n, m);
+      break;
+    }
+    case FS_OP_APPLY_VEC:
+      ws.take<float>(nm);
+      break;
+    case FS_OP_APPLY_MAT:
+      ws.take<float>(nm);
+      ws.take<float>(nm);
+      break;
+    case FS_OP_GRAD:
+      ws.take<float>(n); ws.take<float>(m); ws.take<float>(n); ws.take<float>(m);
+      break;
+    case FS_OP_MAT5:
+      ws.take<float>(n); ws.take<float>(m); ws.take<float>(n); ws.take<float>(m); ws.take<float>(m);
+      break;
+    case FS_OP_SCHUR:
+      ws.take<float>(16);
+      for (int i = 0; i < 3; ++i) ws.take<float>(m);
+      ws.take<float>(n);
+      break;
+    default:
+      return 0;
+  }
+  return ws.off + 256;
+}
+
+int fs_lse(const float* x, const float* y, int n, int m, int d, const float* pot, const float* logw, float* out,
+           float eps, float cost_scale, float damping, int prec, void* wsp, size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!pot || !out) return fail(FS_ERR_BAD_ARG, "pot and out must be non-null");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  LseEpilogue ep;
+  ep.damping = damping;
+  ep.w = 1.f;
+  ep.out = out;
+  FS_CUDA(p.lse(0, pot, logw, eps, ep));
+  return FS_OK;
+}
+
+int fs_symmetric_step(const float* x, const float* y, int n, int m, int d, const float* f_hat, const float* g_hat,
+                      const float* log_a, const float* log_b, float* f_out, float* g_out, const float* alpha_x,
+                      const float* beta_y, float eps, float w, float damp_f, float damp_g, float cost_scale,
+                      int prec, void* wsp, size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!f_hat || !g_hat || !log_a || !log_b || !f_out || !g_out)
+    return fail(FS_ERR_BAD_ARG, "potentials, log-weights and outputs must be non-null");
+  if (f_out == f_hat || g_out == g_hat) return fail(FS_ERR_BAD_ARG, "outputs must not alias the inputs (Jacobi step)");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  LseEpilogue ef;
+  ef.damping = damp_f; ef.old = f_hat; ef.w = w; ef.out = f_out;
+  if (alpha_x && damp_f < 1.f) { ef.shift = alpha_x; ef.shiftcoef = w * (1.f - damp_f); }
+  LseEpilogue eg;
+  eg.damping = damp_g; eg.old = g_hat; eg.w = w; eg.out = g_out;
+  if (beta_y && damp_g < 1.f) { eg.shift = beta_y; eg.shiftcoef = w * (1.f - damp_g); }
+  FS_CUDA(p.lse(0, g_hat, log_b, eps, ef));
+  FS_CUDA(p.lse(1, f_hat, log_a, eps, eg));
+  return FS_OK;
+}
+
+int fs_solve_symmetric(const float* x, const float* y, int n, int m, int d, const float* log_a, const float* log_b,
+                       const double* eps_list, int n_eps, int last_extrapolation, float cost_scale, double rho_x,
+                       double rho_y, double threshold, int check_every, const float* f_init, const float* g_init,
+                       float* f, float* g, float* f_pre, float* g_pre, int* iters_used, int prec, void* wsp,
+                       size_t ws_bytes, void* stream) {
+  if (!eps_list || n_eps <= 0) return fail(FS_ERR_BAD_ARG, "eps_list must be non-empty");
+  FS_TRY(check_common(x, y, n, m, d, (float)eps_list[0], cost_scale, prec));
+  for (int i = 0; i < n_eps; ++i)
+    if (!(eps_list[i] > 0.0)) return fail(FS_ERR_BAD_ARG, "eps_list[%d] must be > 0", i);
+  if (!log_a || !log_b || !f || !g) return fail(FS_ERR_BAD_ARG, "log_a, log_b, f, g must be non-null");
+  const bool early = threshold >= 0.0;
+  if (early && check_every <= 0) return fail(FS_ERR_BAD_ARG, "check_every must be positive");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  SolveBufs b;
+  carve_solve(ws, b, n, m);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+
+  ctrl_init_kernel<<<1, 1, 0, st>>>(b.ctrl, 0);
+  sqnorm_kernel<<<g1(n * 32), 256, 0, st>>>(x, n, d, cost_scale, b.alpha);
+  sqnorm_kernel<<<g1(m * 32), 256, 0, st>>>(y, m, d, cost_scale, b.beta);
+  // f_hat = f_init - alpha (or -alpha)
+  axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, f_init, -1.f, b.alpha, b.fh[0]);
+  axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, g_init, -1.f, b.beta, b.gh[0]);
+  FS_CUDA(cudaGetLastError());
+
+  int cur = 0;
+  auto step = [&](double eps, float w, bool in_loop) -> int {
+    float df = (float)dampening(eps, rho_x), dg = (float)dampening(eps, rho_y);
+    LseEpilogue ef;
+    ef.damping = df; ef.old = b.fh[cur]; ef.w = w; ef.out = b.fh[cur ^ 1];
+    if (df < 1.f) { ef.shift = b.alpha; ef.shiftcoef = w * (1.f - df); }
+    LseEpilogue eg;
+    eg.damping = dg; eg.old = b.gh[cur]; eg.w = w; eg.out = b.gh[cur ^ 1];
+    if (dg < 1.f) { eg.shift = b.beta; eg.shiftcoef = w * (1.f - dg); }
+    if (in_loop && early) { ef.ctrl = b.ctrl; eg.ctrl = b.ctrl; }
+    FS_CUDA(p.lse(0, b.gh[cur], log_b, (float)eps, ef));
+    FS_CUDA(p.lse(1, b.fh[cur], log_a, (float)eps, eg));
+    bump_iters_kernel<<<1, 1, 0, st>>>(b.ctrl, in_loop && early ? 1 : 0);
+    cur ^= 1;
+    return FS_OK;
+  };
+
+  FS_TRY(step(eps_list[0], 1.0f, false));
+  for (int it = 0; it < n_eps; ++it) {
+    FS_TRY(step(eps_list[it], 0.5f, true));
+    if (early && (it + 1) % check_every == 0) {
+      delta_kernel<<<g1(n + m), 256, 0, st>>>(b.fh[cur], b.pf, n, b.gh[cur], b.pg, m, b.ctrl);
+      decide_kernel<<<1, 1, 0, st>>>(b.ctrl, threshold);
+      snapshot_kernel<<<g1(n + m), 256, 0, st>>>(b.fh[cur], b.pf, n, b.gh[cur], b.pg, m, b.ctrl);
+    }
+  }
+  if (last_extrapolation) {
+    if (f_pre) axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, b.fh[cur], 1.f, b.alpha, f_pre);
+    if (g_pre) axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, b.gh[cur], 1.f, b.beta, g_pre);
+    FS_TRY(step(eps_list[n_eps - 1], 1.0f, false));
+  }
+  axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, b.fh[cur], 1.f, b.alpha, f);
+  axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, b.gh[cur], 1.f, b.beta, g);
+  if (!last_extrapolation) {
+    if (f_pre) axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, b.fh[cur], 1.f, b.alpha, f_pre);
+    if (g_pre) axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, b.gh[cur], 1.f, b.beta, g_pre);
+  }
+  if (iters_used) copy_int_kernel<<<1, 1, 0, st>>>(&b.ctrl->iters_used, iters_used);
+  FS_CUDA(cudaGetLastError());
+  return FS_OK;
+}
+
+int fs_solve_alternating(const float* x, const float* y, int n, int m, int d, const float* log_a,
+                         const float* log_b, const double* eps_list, int n_eps, int iters_per_eps,
+                         float cost_scale, double rho_x, double rho_y, int ott_convention, double threshold,
+                         int check_every, const int* tile_row_ptr, const int* tile_col_idx,
+                         const int* tile_row_ptr_t, const int* tile_col_idx_t, float* f, float* g,
+                         int* iters_used, int prec, void* wsp, size_t ws_bytes, void* stream) {
+  if (!eps_list || n_eps <= 0) return fail(FS_ERR_BAD_ARG, "eps_list must be non-empty");
+  FS_TRY(check_common(x, y, n, m, d, (float)eps_list[0], cost_scale, prec));
+  for (int i = 0; i < n_eps; ++i)
+    if (!(eps_list[i] > 0.0)) return fail(FS_ERR_BAD_ARG, "eps_list[%d] must be > 0", i);
+  if (iters_per_eps < 0) return fail(FS_ERR_BAD_ARG, "iters_per_eps must be >= 0");
+  if (!log_a || !log_b || !f || !g) return fail(FS_ERR_BAD_ARG, "log_a, log_b, f, g must be non-null");
+  if ((tile_row_ptr != nullptr) != (tile_row_ptr_t != nullptr) || (tile_row_ptr != nullptr) != (tile_col_idx != nullptr) ||
+      (tile_row_ptr_t != nullptr) != (tile_col_idx_t != nullptr))
+    return fail(FS_ERR_BAD_ARG, "tile lists: pass all four CSR arrays (tile list and its transpose) or none");
+  const bool early = threshold >= 0.0;
+  if (early && check_every <= 0) return fail(FS_ERR_BAD_ARG, "check_every must be positive");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  // Block-sparse tile lists are taken by the CUDA-core engine only.
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, tile_row_ptr ? FS_PREC_SIMT : prec, st, false));
+  p.csr_rp[0] = tile_row_ptr; p.csr_ci[0] = tile_col_idx;
+  p.csr_rp[1] = tile_row_ptr_t; p.csr_ci[1] = tile_col_idx_t;
+  SolveBufs b;
+  carve_solve(ws, b, n, m);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+
+  ctrl_init_kernel<<<1, 1, 0, st>>>(b.ctrl, 1);
+  sqnorm_kernel<<<g1(n * 32), 256, 0, st>>>(x, n, d, cost_scale, b.alpha);
+  sqnorm_kernel<<<g1(m * 32), 256, 0, st>>>(y, m, d, cost_scale, b.beta);
+  float* fh = b.fh[0];
+  float* gh = b.gh[0];
+  axpby_kernel<<<g1(n), 256, 0, st>>>(n, 0.f, nullptr, -1.f, b.alpha, fh);
+  axpby_kernel<<<g1(m), 256, 0, st>>>(m, 0.f, nullptr, -1.f, b.beta, gh);
+  if (early) {
+    axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, fh, 0.f, nullptr, b.pf);
+    axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, gh, 0.f, nullptr, b.pg);
+  }
+  if (ott_convention) {
+    fill_kernel<<<g1(n), 256, 0, st>>>(n, 0.f, b.zeros_n);
+    fill_kernel<<<g1(m), 256, 0, st>>>(m, 0.f, b.zeros_m);
+  }
+  FS_CUDA(cudaGetLastError());
+
+  int global_it = 0;
+  for (int e = 0; e < n_eps; ++e) {
+    const double eps = eps_list[e];
+    const float df = (float)dampening(eps, rho_x), dg = (float)dampening(eps, rho_y);
+    for (int it = 0; it < iters_per_eps; ++it, ++global_it) {
+      LseEpilogue ef, eg;
+      ef.damping = df; ef.w = 1.f; ef.out = fh;
+      eg.damping = dg; eg.w = 1.f; eg.out = gh;
+      if (early) { ef.ctrl = b.ctrl; eg.ctrl = b.ctrl; }
+      if (ott_convention) {
+        // g first, log-marginals outside the LSE (sinkhorn_solvers.py:188-217)
+        eg.addvec = log_b; eg.addcoef = (float)eps;
+        ef.addvec = log_a; ef.addcoef = (float)eps;
+        FS_CUDA(p.lse(1, fh, b.zeros_n, (float)eps, eg));
+        FS_CUDA(p.lse(0, gh, b.zeros_m, (float)eps, ef));
+      } else {
+        FS_CUDA(p.lse(0, gh, log_b, (float)eps, ef));
+        FS_CUDA(p.lse(1, fh, log_a, (float)eps, eg));
+      }
+      bump_iters_kernel<<<1, 1, 0, st>>>(b.ctrl, early ? 1 : 0);
+      if (early && (global_it + 1) % check_every == 0) {
+        delta_kernel<<<g1(n + m), 256, 0, st>>>(fh, b.pf, n, gh, b.pg, m, b.ctrl);
+        decide_kernel<<<1, 1, 0, st>>>(b.ctrl, threshold);
+        snapshot_kernel<<<g1(n + m), 256, 0, st>>>(fh, b.pf, n, gh, b.pg, m, b.ctrl);
+      }
+    }
+  }
+  axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, fh, 1.f, b.alpha, f);
+  axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, gh, 1.f, b.beta, g);
+  if (iters_used) copy_int_kernel<<<1, 1, 0, st>>>(&b.ctrl->iters_used, iters_used);
+  FS_CUDA(cudaGetLastError());
+  return FS_OK;
+}
+
+int fs_apply_vec(const float* x, const float* y, int n, int m, int d, const float* f_hat, const float* g_hat,
+                 const float* log_a, const float* log_b, const float* vec, float* out, float eps, int axis,
+                 float cost_scale, int prec, void* wsp, size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (axis != 0 && axis != 1) return fail(FS_ERR_BAD_ARG, "axis must be 0 or 1");
+  if (!f_hat || !g_hat || !log_a || !log_b || !vec || !out) return fail(FS_ERR_BAD_ARG, "null argument");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  VecArgs v;
+  v.v = vec; v.out = out;
+  if (axis == 1) {
+    v.rowpot = f_hat; v.rowlogw = log_a;
+    FS_CUDA(p.vec(0, g_hat, log_b, eps, v));
+  } else {
+    v.rowpot = g_hat; v.rowlogw = log_b;
+    FS_CUDA(p.vec(1, f_hat, log_a, eps, v));
+  }
+  return FS_OK;
+}
+
+int fs_apply_mat(const float* x, const float* y, int n, int m, int d, const float* f_hat, const float* g_hat,
+                 const float* log_a, const float* log_b, const float* mat, int dv, const float* scale, float* out,
+                 float eps, int axis, float cost_scale, int prec, void* wsp, size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (axis != 0 && axis != 1) return fail(FS_ERR_BAD_ARG, "axis must be 0 or 1");
+  if (dv <= 0) return fail(FS_ERR_BAD_ARG, "dv must be positive");
+  if (scale && axis != 1) return fail(FS_ERR_BAD_ARG, "scale is only supported for axis=1");
+  if (!f_hat || !g_hat || !log_a || !log_b || !mat || !out) return fail(FS_ERR_BAD_ARG, "null argument");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  const int side = axis == 1 ? 0 : 1;
+  const int nr = side == 0 ? n : m;
+  float* R = ws.take<float>(n > m ? n : m);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+  (void)nr;
+  const float* cpot = side == 0 ? g_hat : f_hat;
+  const float* clw = side == 0 ? log_b : log_a;
+  LseEpilogue ep;
+  ep.lse2 = R;
+  FS_CUDA(p.lse(side, cpot, clw, eps, ep));
+  PvArgs a;
+  a.R = R; a.V = mat; a.dv = dv; a.colscale = scale; a.epilogue = PV_APPLY;
+  a.rowpot = side == 0 ? f_hat : g_hat;
+  a.rowlogw = side == 0 ? log_a : log_b;
+  a.out = out;
+  FS_CUDA(p.pv(side, cpot, clw, eps, a));
+  return FS_OK;
+}
+
+int fs_grad(const float* x, const float* y, int n, int m, int d, const float* a, const float* b,
+            const float* log_a, const float* log_b, const float* f, const float* g, const float* grad_scale,
+            float* grad_x, float* grad_y, float eps, float cost_scale, int prec, void* wsp, size_t ws_bytes,
+            void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!a || !b || !log_a || !log_b || !f || !g) return fail(FS_ERR_BAD_ARG, "null argument");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  float* fh = ws.take<float>(n);
+  float* gh = ws.take<float>(m);
+  float* Rn = ws.take<float>(n);
+  float* Rm = ws.take<float>(m);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+  // Shifted potentials: the row-constant part of (g_j - C_ij)/eps cancels in the softmax.
+  if (grad_x) {
+    sqnorm_kernel<<<g1(m * 32), 256, 0, st>>>(y, m, d, cost_scale, Rm);
+    axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, g, -1.f, Rm, gh);
+    LseEpilogue ep;
+    ep.lse2 = Rn;
+    FS_CUDA(p.lse(0, gh, log_b, eps, ep));
+    PvArgs pa;
+    pa.R = Rn; pa.V = y; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = a; pa.gs = grad_scale;
+    pa.coef = 2.f * cost_scale; pa.out = grad_x;
+    FS_CUDA(p.pv(0, gh, log_b, eps, pa));
+  }
+  if (grad_y) {
+    sqnorm_kernel<<<g1(n * 32), 256, 0, st>>>(x, n, d, cost_scale, Rn);
+    axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, f, -1.f, Rn, fh);
+    LseEpilogue ep;
+    ep.lse2 = Rm;
+    FS_CUDA(p.lse(1, fh, log_a, eps, ep));
+    PvArgs pa;
+    pa.R = Rm; pa.V = x; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = b; pa.gs = grad_scale;
+    pa.coef = 2.f * cost_scale; pa.out = grad_y;
+    FS_CUDA(p.pv(1, fh, log_a, eps, pa));
+  }
+  FS_CUDA(cudaGetLastError());
+  return FS_OK;
+}
+
+int fs_mat5(const float* x, const float* y, int n, int m, int d, const float* f_ott, const float* g_ott,
+            const float* A, float* out, float eps, float cost_scale, int prec, void* wsp, size_t ws_bytes,
+            void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!f_ott || !g_ott || !A || !out) return fail(FS_ERR_BAD_ARG, "null argument");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  float* fh = ws.take<float>(n);
+  float* gh = ws.take<float>(m);
+  float* R = ws.take<float>(n);
+  float* tmp = ws.take<float>(m);
+  float* zeros_m = ws.take<float>(m);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+  sqnorm_kernel<<<g1(n * 32), 256, 0, st>>>(x, n, d, cost_scale, R);
+  axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, f_ott, -1.f, R, fh);
+  sqnorm_kernel<<<g1(m * 32), 256, 0, st>>>(y, m, d, cost_scale, tmp);
+  axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, g_ott, -1.f, tmp, gh);
+  fill_kernel<<<g1(m), 256, 0, st>>>(m, 0.f, zeros_m);
+  LseEpilogue ep;
+  ep.lse2 = R;
+  FS_CUDA(p.lse(0, gh, zeros_m, eps, ep));
+  PvArgs pa;
+  pa.R = R; pa.rows2 = A; pa.V = y; pa.dv = d; pa.epilogue = PV_MAT5;
+  pa.rowpot = fh; pa.rowlogw = nullptr; pa.coef = -4.f * cost_scale / eps; pa.out = out;
+  FS_CUDA(p.pv(0, gh, zeros_m, eps, pa));
+  FS_CUDA(cudaGetLastError());
+  return FS_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Device-resident conjugate gradient on the Schur complement
+// ---------------------------------------------------------------------------
+namespace fs {
+namespace {
+
+struct CgState {
+  float rz_old, tol, res, init_res;
+  int done, converged, iters, pad;
+};
+
+__device__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+// z = 0, r = p = rhs, rz_old = |r|^2, tol = max(atol, rtol*|r|).  One block.
+__global__ void cg_init_kernel(int m, const float* rhs, float* z, float* r, float* pvec, CgState* s, float rtol,
+                               float atol) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < m; i += blockDim.x) {
+    float v = rhs[i];
+    z[i] = 0.f; r[i] = v; pvec[i] = v;
+    acc = fmaf(v, v, acc);
+  }
+  float rr = block_sum(acc, red);
+  if (threadIdx.x == 0) {
+    s->rz_old = rr;
+    s->init_res = sqrtf(rr);
+    s->res = s->init_res;
+    s->tol = fmaxf(atol, rtol * s->init_res);
+    s->done = 0; s->converged = 0; s->iters = 0;
+  }
+}
+
+// u = t / diag_x  (skipped once done)
+__global__ void cg_div_kernel(int n, const float* t, const float* diag, float* u, const CgState* s) {
+  if (s->done) return;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) u[i] = t[i] / diag[i];
+}
+
+// One block: Ap = denom*p - q; alpha = rz/(p.Ap); z += alpha p; r -= alpha Ap; test; p = r + beta p.
+__global__ void cg_update_kernel(int m, const float* denom, const float* q, float* z, float* r, float* pvec,
+                                 CgState* s, int it) {
+  __shared__ float red[32];
+  if (s->done) return;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < m; i += blockDim.x) {
+    float ap = denom[i] * pvec[i] - q[i];
+    acc = fmaf(pvec[i], ap, acc);
+  }
+  float pAp = block_sum(acc, red);
+  if (pAp == 0.f) {  // reference: `if denom.abs() == 0: break`
+    if (threadIdx.x == 0) s->done = 1;
+    return;
+  }
+  float rz_old = s->rz_old;
+  float alpha = rz_old / pAp;
+  acc = 0.f;
+  for (int i = threadIdx.x; i < m; i += blockDim.x) {
+    float pi = pvec[i];
+    float ap = denom[i] * pi - q[i];
+    z[i] = z[i] + alpha * pi;
+    float ri = r[i] - alpha * ap;
+    r[i] = ri;
+    acc = fmaf(ri, ri, acc);
+  }
+  float rz_new = block_sum(acc, red);
+  float res = sqrtf(rz_new);
+  bool conv = res <= s->tol;
+  if (!conv) {
+    float beta = rz_new / rz_old;
+    for (int i = threadIdx.x; i < m; i += blockDim.x) pvec[i] = r[i] + beta * pvec[i];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s->res = res;
+    s->rz_old = rz_new;
+    if (conv) { s->done = 1; s->converged = 1; s->iters = it + 1; }
+  }
+}
+
+__global__ void cg_finish_kernel(const CgState* s, float* info, int max_iter) {
+  info[0] = s->converged ? 1.f : 0.f;
+  info[1] = s->converged ? (float)s->iters : (float)max_iter;
+  info[2] = s->res;
+  info[3] = s->init_res;
+}
+
+}  // namespace
+}  // namespace fs
+
+extern "C" int fs_schur_cg(const float* x, const float* y, int n, int m, int d, const float* f_hat,
+                           const float* g_hat, const float* log_a, const float* log_b, const float* diag_x,
+                           const float* denom, const float* rhs, float* z, float* info, float eps,
+                           float cost_scale, int max_iter, float rtol, float atol, int prec, void* wsp,
+                           size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!f_hat || !g_hat || !log_a || !log_b || !diag_x || !denom || !rhs || !z || !info)
+    return fail(FS_ERR_BAD_ARG, "null argument");
+  if (max_iter < 0) return fail(FS_ERR_BAD_ARG, "max_iter must be >= 0");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  CgState* s = reinterpret_cast<CgState*>(ws.take<float>(16));
+  float* r = ws.take<float>(m);
+  float* pv = ws.take<float>(m);
+  float* q = ws.take<float>(m);
+  float* t = ws.take<float>(n);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+  cg_init_kernel<<<1, 1024, 0, st>>>(m, rhs, z, r, pv, s, rtol, atol);
+  for (int it = 0; it < max_iter; ++it) {
+    VecArgs v1;
+    v1.v = pv; v1.rowpot = f_hat; v1.rowlogw = log_a; v1.out = t; v1.skip = &s->done;
+    FS_CUDA(p.vec(0, g_hat, log_b, eps, v1));
+    cg_div_kernel<<<g1(n), 256, 0, st>>>(n, t, diag_x, t, s);
+    VecArgs v0;
+    v0.v = t; v0.rowpot = g_hat; v0.rowlogw = log_b; v0.out = q; v0.skip = &s->done;
+    FS_CUDA(p.vec(1, f_hat, log_a, eps, v0));
+    cg_update_kernel<<<1, 1024, 0, st>>>(m, denom, q, z, r, pv, s, it);
+  }
+  cg_finish_kernel<<<1, 1, 0, st>>>(s, info, max_iter);
+  FS_CUDA(cudaGetLastError());
+  return FS_OK;
+}

@@ -1,0 +1,262 @@
+"""Hessian-vector product of the entropic OT cost w.r.t. the source points.
+
+Public surface of the reference's ``hvp.py``: ``HvpInfo`` (:44-52),
+``geomloss_to_ott_potentials`` (:55-76), ``hvp_x_sqeuclid_from_potentials`` (:164-623),
+``hvp_x_sqeuclid`` (:626-693). The algebra is the Schur-complement form the reference
+uses (marginals, ``P y``, ``P^T A``, a CG solve on ``diag(denom) - P^T diag(1/D_x) P``,
+back-substitution, then the five explicit terms); every plan application streams
+through the CUDA engine and nothing of size n*m is formed.
+
+With the default ``preconditioner="none"`` and no warm start the CG loop runs entirely
+on the device (``fs_schur_cg``): dot products, the stopping test and the iteration
+counter never visit the host, and the only synchronisation is reading the four-float
+result record. Other preconditioners / ``cg_x0`` / ``cg_stabilise_every`` use the
+host-driven ``conjugate_gradient``. The reference's optional dense / batched / compiled /
+fused-matvec CG variants are accepted as keywords and ignored.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from flash_sinkhorn_b200 import _lib
+from flash_sinkhorn_b200.cg import CGInfo, conjugate_gradient
+from flash_sinkhorn_b200.kernels._common import log_weights
+from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_mat_flashstyle, apply_plan_vec_flashstyle
+from flash_sinkhorn_b200.kernels.apply_ott import mat5_sqeuclid
+from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_symmetric
+
+__all__ = [
+    "HvpInfo",
+    "geomloss_to_ott_potentials",
+    "ott_to_geomloss_potentials",
+    "hvp_x_sqeuclid",
+    "hvp_x_sqeuclid_from_potentials",
+    "sinkhorn_prelast_potentials_sqeuclid",
+]
+
+
+@dataclass(frozen=True)
+class HvpInfo:
+    cg_converged: bool
+    cg_iters: int
+    cg_residual: float
+    cg_initial_residual: float
+    converged_lambda: float = 0.0
+    hit_neg_curv: bool = False
+    diagnostic_msg: str = ""
+
+
+def geomloss_to_ott_potentials(f, g, a, b, *, eps: float):
+    """``(f + eps*log a, g + eps*log b)``: absorb the weights so that ``P = exp((f+g-C)/eps)``."""
+    e = float(eps)
+    return f.float() + e * log_weights(a), g.float() + e * log_weights(b)
+
+
+def ott_to_geomloss_potentials(f_hat, g_hat, a, b, *, eps: float):
+    """Inverse of :func:`geomloss_to_ott_potentials`."""
+    e = float(eps)
+    return f_hat.float() - e * log_weights(a), g_hat.float() - e * log_weights(b)
+
+
+def sinkhorn_prelast_potentials_sqeuclid(
+    x, y, a, b, *, eps_list: Sequence[float], allow_tf32: bool = False, use_exp2: bool = True,
+    autotune: bool = True, block_m=None, block_n=None, block_k=None, num_warps=None, num_stages: int = 2,
+    use_flashstyle: Optional[bool] = None, cost_scale: float = 1.0,
+    rho_x: Optional[float] = None, rho_y: Optional[float] = None,
+):
+    """Potentials before the final extrapolation step of a symmetric solve on ``eps_list``."""
+    _, _, f_pre, g_pre = sinkhorn_flashstyle_symmetric(
+        x, y, a, b, use_epsilon_scaling=False, last_extrapolation=True, allow_tf32=allow_tf32,
+        eps_list=eps_list, return_prelast=True, cost_scale=cost_scale, rho_x=rho_x, rho_y=rho_y,
+    )
+    return f_pre, g_pre
+
+
+def _device_schur_cg(x, y, f_shift, g_shift, log_a, log_b, diag_x, denom, rhs, *, eps, cost_scale,
+                     max_iter, rtol, atol, allow_tf32):
+    n, d = x.shape
+    m = y.shape[0]
+    dev = x.device
+    prec = _lib.precision_id(allow_tf32)
+    z = torch.empty((m,), device=dev, dtype=torch.float32)
+    info = torch.zeros((4,), device=dev, dtype=torch.float32)
+    ws = _lib.workspace(_lib.OP_SCHUR, n, m, d, prec, dev)
+    x32, y32 = _lib.f32c(x), _lib.f32c(y)
+    _lib.call(
+        "fs_schur_cg", dev,
+        _lib.ptr(x32), _lib.ptr(y32), n, m, d,
+        _lib.ptr(f_shift), _lib.ptr(g_shift), _lib.ptr(log_a), _lib.ptr(log_b),
+        _lib.ptr(_lib.f32c(diag_x)), _lib.ptr(_lib.f32c(denom)), _lib.ptr(_lib.f32c(rhs)),
+        _lib.ptr(z), _lib.ptr(info),
+        float(eps), float(cost_scale), int(max_iter), float(rtol), float(atol),
+        prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+    )
+    rec = info.tolist()
+    return z, CGInfo(bool(rec[0] != 0.0), int(rec[1]), float(rec[2]), float(rec[3]))
+
+
+def hvp_x_sqeuclid_from_potentials(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    f_hat: torch.Tensor,
+    g_hat: torch.Tensor,
+    A: torch.Tensor,
+    *,
+    eps: float,
+    rho_x: Optional[float] = None,
+    rho_y: Optional[float] = None,
+    cost_scale: float = 1.0,
+    lambda_indef: float = 1.0,
+    return_components: bool = False,
+    tau2: float = 1e-5,
+    max_cg_iter: int = 300,
+    cg_rtol: float = 1e-6,
+    cg_atol: float = 1e-6,
+    cg_stabilise_every: int = 0,
+    preconditioner: str = "none",
+    precond_terms: int = 3,
+    use_preconditioner: bool = True,
+    allow_tf32: bool = False,
+    use_exp2: bool = True,
+    block_m: Optional[int] = None,
+    block_n: Optional[int] = None,
+    block_k: Optional[int] = None,
+    num_warps: int = 4,
+    num_stages: int = 2,
+    use_fused_matvec: bool = False,
+    use_batched_cg: bool = False,
+    use_compiled_cg: bool = False,
+    use_dense_cg: bool = False,
+    autotune: bool = True,
+    cg_x0: Optional[torch.Tensor] = None,
+):
+    """``H @ A`` for the Hessian of the OT cost in x, from OTT-convention potentials.
+
+    ``f_hat, g_hat`` satisfy ``P = exp((f_hat + g_hat - C)/eps)``. Returns ``(hvp, HvpInfo)``,
+    or ``(psd_part, indefinite_part, HvpInfo)`` with ``return_components``.
+    """
+    if x.ndim != 2 or y.ndim != 2 or A.ndim != 2:
+        raise ValueError("x,y,A must be 2D tensors.")
+    if not x.is_cuda or not y.is_cuda or not f_hat.is_cuda or not g_hat.is_cuda:
+        raise ValueError("hvp_x_sqeuclid_from_potentials requires CUDA tensors.")
+    n, d = x.shape
+    m, d2 = y.shape
+    if d != d2 or A.shape != (n, d):
+        raise ValueError("Shapes must satisfy x:(n,d), y:(m,d), A:(n,d).")
+
+    mode = str(preconditioner).lower() if use_preconditioner else "none"
+    if mode not in ("none", "neumann", "jacobi"):
+        raise ValueError("preconditioner must be one of {'none','neumann','jacobi'}.")
+    n_terms = int(precond_terms)
+    if n_terms < 0:
+        raise ValueError("precond_terms must be >= 0.")
+
+    e = float(eps)
+    c = 2.0 * cost_scale
+    dev = x.device
+    xf, yf, Af = x.float(), y.float(), A.float()
+
+    # Shifted potentials in a uniform-weight gauge: the log-weights the kernels add back
+    # are subtracted here, so any constant works (reference hvp.py:295-300).
+    log_a = torch.full((n,), -math.log(n), device=dev, dtype=torch.float32)
+    log_b = torch.full((m,), -math.log(m), device=dev, dtype=torch.float32)
+    f_shift = (f_hat.float() - e * log_a - cost_scale * xf.pow(2).sum(dim=1)).contiguous()
+    g_shift = (g_hat.float() - e * log_b - cost_scale * yf.pow(2).sum(dim=1)).contiguous()
+    kw = dict(eps=e, cost_scale=cost_scale, allow_tf32=allow_tf32)
+
+    def P(v):   # [m] -> [n]
+        return apply_plan_vec_flashstyle(x, y, f_shift, g_shift, log_a, log_b, v, axis=1, **kw)
+
+    def Pt(u):  # [n] -> [m]
+        return apply_plan_vec_flashstyle(x, y, f_shift, g_shift, log_a, log_b, u, axis=0, **kw)
+
+    def Pmat(V, axis, scale=None):
+        return apply_plan_mat_flashstyle(x, y, f_shift, g_shift, log_a, log_b, V, axis=axis, scale=scale, **kw)
+
+    row_mass = P(torch.ones((m,), device=dev, dtype=torch.float32))
+    col_mass = Pt(torch.ones((n,), device=dev, dtype=torch.float32))
+    kx = 1.0 if rho_x is None else (float(rho_x) + e) / float(rho_x)
+    ky = 1.0 if rho_y is None else (float(rho_y) + e) / float(rho_y)
+    floor = max(1e-12, e * 1e-10)
+    D_x = kx * row_mass.clamp(min=floor)
+    D_y = ky * col_mass.clamp(min=floor)
+    balanced = rho_x is None and rho_y is None
+    denom = D_y + e * float(tau2) if balanced else D_y
+
+    xa = (x * A).sum(dim=1)                          # x_i . A_i
+    Py = Pmat(yf, 1)                                 # [n, d]
+    PtA = Pmat(Af, 0)                                # [m, d]
+    r_x = c * (row_mass * xa - (A * Py).sum(dim=1))
+    r_y = c * (Pt(xa) - (y * PtA).sum(dim=1))
+    y1 = r_x / D_x
+    rhs_raw = r_y - Pt(y1)
+
+    def schur(zv):
+        return denom * zv - Pt(P(zv) / D_x)
+
+    if mode == "none":
+        rhs = rhs_raw
+        if cg_x0 is None and int(cg_stabilise_every) == 0:
+            z, cg = _device_schur_cg(
+                x, y, f_shift, g_shift, log_a, log_b, D_x, denom, rhs.contiguous(), eps=e,
+                cost_scale=cost_scale, max_iter=max_cg_iter, rtol=cg_rtol, atol=cg_atol, allow_tf32=allow_tf32,
+            )
+        else:
+            z, cg = conjugate_gradient(schur, rhs, x0=cg_x0, max_iter=max_cg_iter, rtol=cg_rtol,
+                                       atol=cg_atol, stabilise_every=cg_stabilise_every)
+    else:
+        def B(zv):
+            return Pt(P(zv) / D_x) / denom
+
+        def neumann(v):
+            total, term = v, v
+            for _ in range(n_terms):
+                term = B(term)
+                total = total + term
+            return total
+
+        z, cg = conjugate_gradient(
+            lambda zv: zv - B(zv), rhs_raw / denom, x0=cg_x0, max_iter=max_cg_iter, rtol=cg_rtol,
+            atol=cg_atol, preconditioner=neumann if mode == "neumann" else None,
+            stabilise_every=cg_stabilise_every,
+        )
+
+    Pz = P(z)
+    z1 = y1 - Pz / D_x
+    Pyz = Pmat(yf, 1, scale=z)
+    RTz = c * (x * (row_mass * z1)[:, None] - Py * z1[:, None] + x * Pz[:, None] - Pyz)
+
+    k2 = 2.0 * c / e
+    term1 = c * row_mass[:, None] * A
+    term2 = -k2 * x * (xa * row_mass)[:, None]
+    term3 = k2 * Py * xa[:, None]
+    term4 = k2 * x * (Py * A).sum(dim=1)[:, None]
+    term5 = mat5_sqeuclid(x, y, f_hat, g_hat, A, eps=e, cost_scale=cost_scale, allow_tf32=allow_tf32)
+
+    psd = RTz / e + term1
+    indef = term2 + term3 + term4 + term5
+    info = HvpInfo(bool(cg.cg_converged), int(cg.cg_iters), float(cg.cg_residual), float(cg.cg_initial_residual))
+    if return_components:
+        return psd, indef, info
+    return (psd + indef if lambda_indef == 1.0 else psd + lambda_indef * indef), info
+
+
+def hvp_x_sqeuclid(
+    x, y, a, b, A, *, eps_list: Sequence[float], tau2: float = 1e-5, max_cg_iter: int = 300,
+    cg_rtol: float = 1e-6, cg_atol: float = 1e-6, cg_stabilise_every: int = 0, preconditioner: str = "none",
+    precond_terms: int = 3, use_preconditioner: bool = True, allow_tf32: bool = False, use_exp2: bool = True,
+    autotune: bool = True, block_m=None, block_n=None, block_k=None, num_warps=None, num_stages: int = 2,
+):
+    """Solve for the pre-extrapolation potentials on ``eps_list``, then apply the Hessian to ``A``."""
+    eps = float(eps_list[-1])
+    f_pre, g_pre = sinkhorn_prelast_potentials_sqeuclid(x, y, a, b, eps_list=eps_list, allow_tf32=allow_tf32)
+    f_hat, g_hat = geomloss_to_ott_potentials(f_pre, g_pre, a, b, eps=eps)
+    return hvp_x_sqeuclid_from_potentials(
+        x, y, f_hat, g_hat, A, eps=eps, tau2=tau2, max_cg_iter=max_cg_iter, cg_rtol=cg_rtol, cg_atol=cg_atol,
+        cg_stabilise_every=cg_stabilise_every, preconditioner=preconditioner, precond_terms=precond_terms,
+        use_preconditioner=use_preconditioner, allow_tf32=allow_tf32,
+    )

@@ -1,0 +1,236 @@
+"""Sinkhorn solver entry points (symmetric / alternating) over the CUDA engine.
+
+Signatures, defaults, return shapes and error behaviour follow the reference's
+``sinkhorn_solvers.py`` (sinkhorn_flashstyle_alternating :30-287,
+sinkhorn_flashstyle_symmetric :290-707). Unlike the reference, the iteration loop
+itself runs inside the library (``fs_solve_symmetric`` / ``fs_solve_alternating``):
+the eps schedule, damping, shift correction, Jacobi averaging and the early-stop test
+are enqueued on the current stream without any host synchronisation. The only sync
+is the optional read-back of the iteration counter (``return_n_iters=True``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from flash_sinkhorn_b200 import _lib
+from flash_sinkhorn_b200.kernels._common import (
+    epsilon_schedule,
+    log_weights,
+    max_diameter,
+    resolve_marginal_penalties,
+)
+
+__all__ = ["sinkhorn_flashstyle_alternating", "sinkhorn_flashstyle_symmetric", "tile_mask_to_csr"]
+
+
+def _neg_if_none(v: Optional[float]) -> float:
+    return -1.0 if v is None else float(v)
+
+
+def _eps_array(eps_list: Sequence[float]):
+    arr = (ctypes.c_double * len(eps_list))(*[float(e) for e in eps_list])
+    return arr
+
+
+def tile_mask_to_csr(mask: torch.Tensor, device: torch.device):
+    """Boolean ``[ceil(n/128), ceil(m/128)]`` tile mask -> CSR arrays of the mask and of its transpose.
+
+    Returns ``(row_ptr, col_idx, row_ptr_t, col_idx_t)`` as int32 device tensors, the form
+    ``fs_solve_alternating`` takes for block-sparse tile skipping.
+    """
+    if mask.ndim != 2:
+        raise ValueError("tile mask must be 2D")
+    mk = mask.to(device="cpu", dtype=torch.bool)
+
+    def one(mt: torch.Tensor):
+        counts = mt.sum(dim=1)
+        rp = torch.zeros(mt.shape[0] + 1, dtype=torch.int64)
+        rp[1:] = torch.cumsum(counts, dim=0)
+        ci = mt.nonzero(as_tuple=False)[:, 1]
+        return rp.to(torch.int32).to(device), ci.to(torch.int32).to(device).contiguous()
+
+    rp, ci = one(mk)
+    rpt, cit = one(mk.t().contiguous())
+    return rp, ci, rpt, cit
+
+
+def sinkhorn_flashstyle_alternating(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    eps: float = 0.1,
+    n_iters: int = 100,
+    cost_scale: float = 1.0,
+    rho: Optional[float] = None,
+    reach: Optional[float] = None,
+    rho_x: Optional[float] = None,
+    rho_y: Optional[float] = None,
+    reach_x: Optional[float] = None,
+    reach_y: Optional[float] = None,
+    allow_tf32: bool = True,
+    use_exp2: bool = True,
+    autotune: bool = True,
+    threshold: Optional[float] = None,
+    check_every: int = 5,
+    return_n_iters: bool = False,
+    ott_convention: bool = False,
+    eps_list: Optional[Sequence[float]] = None,
+    iters_per_eps: Optional[int] = None,
+    tile_mask: Optional[torch.Tensor] = None,
+):
+    """Gauss-Seidel Sinkhorn at fixed ``eps``: f from g, then g from the new f.
+
+    Returns ``(f, g)`` (plus the iteration count with ``return_n_iters``). In the default
+    GeomLoss convention the log-weights sit inside the soft-min; ``ott_convention=True``
+    updates g first and keeps ``eps*log a``, ``eps*log b`` outside. Damped (unbalanced)
+    updates get no shift correction, exactly like the reference.
+
+    Extensions without a reference counterpart: ``eps_list`` + ``iters_per_eps`` run an
+    annealed sequence of fixed-eps stages, each warm-started from the previous one, and
+    ``tile_mask`` (bool ``[ceil(n/128), ceil(m/128)]``) drops 128x128 tiles from both soft-mins.
+    """
+    n, d = x.shape
+    m = y.shape[0]
+    rho_x, rho_y = resolve_marginal_penalties(rho, reach, rho_x, rho_y, reach_x, reach_y)
+    dev = _lib.require_cuda(x=x, y=y, a=a, b=b)
+
+    if eps_list is None:
+        stages, per_stage = [float(eps)], int(n_iters)
+    else:
+        stages = [float(e) for e in eps_list]
+        per_stage = int(n_iters if iters_per_eps is None else iters_per_eps)
+        if len(stages) == 0:
+            raise ValueError("eps_list must be non-empty")
+
+    x32, y32 = _lib.f32c(x), _lib.f32c(y)
+    log_a, log_b = log_weights(a).contiguous(), log_weights(b).contiguous()
+    prec = _lib.precision_id(allow_tf32)
+    f = torch.empty((n,), device=dev, dtype=torch.float32)
+    g = torch.empty((m,), device=dev, dtype=torch.float32)
+    iters = torch.zeros((1,), device=dev, dtype=torch.int32)
+    csr = (None, None, None, None)
+    if tile_mask is not None:
+        nt, mt = (n + 127) // 128, (m + 127) // 128
+        if tuple(tile_mask.shape) != (nt, mt):
+            raise ValueError(f"tile_mask must have shape ({nt}, {mt})")
+        csr = tile_mask_to_csr(tile_mask, dev)
+    ws = _lib.workspace(_lib.OP_SOLVE_ALTERNATING, n, m, d, prec, dev)
+    eps_arr = _eps_array(stages)
+    _lib.call(
+        "fs_solve_alternating", dev,
+        _lib.ptr(x32), _lib.ptr(y32), n, m, d, _lib.ptr(log_a), _lib.ptr(log_b),
+        ctypes.cast(eps_arr, ctypes.c_void_p), len(stages), per_stage,
+        float(cost_scale), _neg_if_none(rho_x), _neg_if_none(rho_y),
+        1 if ott_convention else 0, _neg_if_none(threshold), int(check_every),
+        _lib.ptr(csr[0]), _lib.ptr(csr[1]), _lib.ptr(csr[2]), _lib.ptr(csr[3]),
+        _lib.ptr(f), _lib.ptr(g), _lib.ptr(iters),
+        prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+    )
+    if return_n_iters:
+        return f, g, int(iters.item())
+    return f, g
+
+
+def sinkhorn_flashstyle_symmetric(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    blur: float = 0.05,
+    scaling: float = 0.5,
+    use_epsilon_scaling: bool = True,
+    last_extrapolation: bool = True,
+    cost_scale: float = 1.0,
+    eps: Optional[float] = None,
+    n_iters: Optional[int] = None,
+    diameter: Optional[float] = None,
+    eps_list: Optional[Sequence[float]] = None,
+    rho: Optional[float] = None,
+    reach: Optional[float] = None,
+    rho_x: Optional[float] = None,
+    rho_y: Optional[float] = None,
+    reach_x: Optional[float] = None,
+    reach_y: Optional[float] = None,
+    allow_tf32: bool = True,
+    use_exp2: bool = True,
+    autotune: bool = True,
+    fused: Optional[bool] = None,
+    threshold: Optional[float] = None,
+    check_every: int = 5,
+    return_n_iters: bool = False,
+    return_prelast: bool = False,
+    f_init: Optional[torch.Tensor] = None,
+    g_init: Optional[torch.Tensor] = None,
+    label_x: Optional[torch.Tensor] = None,
+    label_y: Optional[torch.Tensor] = None,
+    label_cost_matrix: Optional[torch.Tensor] = None,
+    lambda_x: float = 1.0,
+    lambda_y: float = 0.0,
+):
+    """GeomLoss-style symmetric Sinkhorn (Jacobi steps averaged with weight 1/2).
+
+    Step sequence: one full step at ``eps_list[0]``, one averaged step per schedule entry,
+    and (``last_extrapolation``) one full step at the last eps. Returns standard potentials
+    ``(f, g)``; with ``return_prelast`` (and extrapolation on) also the potentials before the
+    last step, and with ``return_n_iters`` the number of steps taken. ``fused`` is accepted
+    and ignored (one implementation serves both of the reference's paths).
+    """
+    if label_x is not None and label_y is not None and label_cost_matrix is not None and lambda_y != 0.0:
+        raise NotImplementedError("The OTDD label-augmented cost is not implemented in flash_sinkhorn_b200.")
+    n, d = x.shape
+    m = y.shape[0]
+    rho_x, rho_y = resolve_marginal_penalties(rho, reach, rho_x, rho_y, reach_x, reach_y)
+
+    if eps_list is None:
+        if use_epsilon_scaling:
+            if diameter is None:
+                diameter = max_diameter(x, y)
+            eps_list = epsilon_schedule(diameter, blur, scaling, p=2.0)
+        else:
+            if eps is None or n_iters is None:
+                raise ValueError("When use_epsilon_scaling=False, provide eps and n_iters")
+            eps_list = [float(eps)] * int(n_iters)
+    if len(eps_list) == 0:
+        raise ValueError("eps_list must be non-empty")
+    if n_iters is not None:
+        eps_list = list(eps_list)[: int(n_iters)]
+    if len(eps_list) == 0:
+        raise ValueError("eps_list must be non-empty")
+
+    dev = _lib.require_cuda(x=x, y=y, a=a, b=b, f_init=f_init, g_init=g_init)
+    x32, y32 = _lib.f32c(x), _lib.f32c(y)
+    log_a, log_b = log_weights(a).contiguous(), log_weights(b).contiguous()
+    fi = None if f_init is None else _lib.f32c(f_init)
+    gi = None if g_init is None else _lib.f32c(g_init)
+    prec = _lib.precision_id(allow_tf32)
+
+    f = torch.empty((n,), device=dev, dtype=torch.float32)
+    g = torch.empty((m,), device=dev, dtype=torch.float32)
+    want_pre = bool(return_prelast and last_extrapolation)
+    f_pre = torch.empty((n,), device=dev, dtype=torch.float32) if want_pre else None
+    g_pre = torch.empty((m,), device=dev, dtype=torch.float32) if want_pre else None
+    iters = torch.zeros((1,), device=dev, dtype=torch.int32) if return_n_iters else None
+    ws = _lib.workspace(_lib.OP_SOLVE_SYMMETRIC, n, m, d, prec, dev)
+    eps_arr = _eps_array(eps_list)
+    _lib.call(
+        "fs_solve_symmetric", dev,
+        _lib.ptr(x32), _lib.ptr(y32), n, m, d, _lib.ptr(log_a), _lib.ptr(log_b),
+        ctypes.cast(eps_arr, ctypes.c_void_p), len(eps_list), 1 if last_extrapolation else 0,
+        float(cost_scale), _neg_if_none(rho_x), _neg_if_none(rho_y),
+        _neg_if_none(threshold), int(check_every),
+        _lib.ptr(fi), _lib.ptr(gi), _lib.ptr(f), _lib.ptr(g), _lib.ptr(f_pre), _lib.ptr(g_pre),
+        _lib.ptr(iters),
+        prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+    )
+    out = (f, g)
+    if want_pre:
+        out = out + (f_pre, g_pre)
+    if return_n_iters:
+        out = out + (int(iters.item()),)
+    return out

@@ -1,0 +1,208 @@
+/*
+ * flash_sinkhorn_b200 -- C ABI of the B200 (sm_100a) streaming-Sinkhorn engine.
+ *
+ * Every entry point replaces one kernel launcher (or one host loop over
+ * launchers) of the reference package ot-triton-lab/flash-sinkhorn; the
+ * reference has no FFI of its own, so each declaration cites the Python
+ * function whose body it stands in for (paths are relative to the reference's
+ * src/flash_sinkhorn/).
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers to contiguous fp32 (row-major for
+ *    matrices) owned by the caller, unless the name ends in _host.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *  - `ws`/`ws_bytes`: caller-owned scratch, at least fs_workspace_bytes() for
+ *    the same (op, n, m, d, prec); 256-byte aligned. Nothing is allocated, and
+ *    nothing synchronises with the host unless stated.
+ *  - Return value: FS_OK or an fs_status; fs_last_error() gives the message of
+ *    the calling thread's last failure.
+ *  - `prec`: FS_PREC_TF32 (one tcgen05 kind::tf32 pass), FS_PREC_FP32 (3xTF32
+ *    split, fp32-equivalent products) or FS_PREC_SIMT (CUDA-core fp32 FMA).
+ *  - rho < 0 (or NaN) means "balanced side" (no marginal relaxation).
+ *  - Notation: cs = cost_scale, C_ij = cs*|x_i-y_j|^2, alpha_i = cs*|x_i|^2,
+ *    beta_j = cs*|y_j|^2, shifted potentials f_hat = f-alpha, g_hat = g-beta.
+ */
+#ifndef FLASH_SINKHORN_B200_H
+#define FLASH_SINKHORN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  FS_OK = 0,
+  FS_ERR_BAD_ARG = 1,
+  FS_ERR_UNSUPPORTED = 2,
+  FS_ERR_CUDA = 3,
+  FS_ERR_TIMEOUT = 4,
+  FS_ERR_WORKSPACE = 5
+} fs_status;
+
+enum { FS_PREC_TF32 = 0, FS_PREC_FP32 = 1, FS_PREC_SIMT = 2 };
+
+/* op ids for fs_workspace_bytes */
+enum {
+  FS_OP_LSE = 0,
+  FS_OP_STEP = 1,
+  FS_OP_SOLVE_SYMMETRIC = 2,
+  FS_OP_SOLVE_ALTERNATING = 3,
+  FS_OP_APPLY_VEC = 4,
+  FS_OP_APPLY_MAT = 5,
+  FS_OP_GRAD = 6,
+  FS_OP_MAT5 = 7,
+  FS_OP_SCHUR = 8
+};
+
+/* Library/ABI version (major*10000 + minor*100 + patch). */
+int fs_version(void);
+
+/* Message of the calling thread's most recent non-FS_OK return ("" if none). */
+const char* fs_last_error(void);
+
+/* Compute capability of the current device as major*10+minor (100 on B200);
+ * negative on CUDA error. The compute entry points return FS_ERR_UNSUPPORTED
+ * on anything that is not sm_100. */
+int fs_device_arch(void);
+
+/* Number of kernels this library has enqueued since it was loaded (monotonic, all
+ * threads; single-thread <<<1,1>>> bookkeeping kernels are not counted). Lets a caller
+ * verify that its work ran on the GPU path: difference two readings around a call. */
+long long fs_launch_count(void);
+
+/* Scratch bytes needed by `op` (one of FS_OP_*) at these sizes. */
+size_t fs_workspace_bytes(int op, int n, int m, int d, int prec);
+
+/* Row log-sum-exp potential update.
+ *   out_i = -eps*damping * log sum_j exp( (2cs/eps) x_i.y_j + bias_j )
+ *   bias_j = pot_j/eps + logw_j   when logw != NULL
+ *          = pot_j                when logw == NULL (bias already scaled)
+ * Replaces kernels/sinkhorn_flashstyle_sqeuclid.py:815-955 (flashsinkhorn_lse,
+ * raw bias) and :958-1090 (flashsinkhorn_lse_fused); the g-update is the same
+ * call with (y, x) swapped, as sinkhorn_solvers.py:629-632 does. */
+int fs_lse(const float* x, const float* y, int n, int m, int d,
+           const float* pot, const float* logw, float* out,
+           float eps, float cost_scale, float damping,
+           int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* One Jacobi (symmetric) step: both sides read the OLD potentials.
+ *   f_out = (1-w) f_hat + w * (-eps*damp_f*LSE_j[(2cs/eps)x_i.y_j + g_hat_j/eps + log_b_j])
+ *   g_out likewise with roles swapped.
+ * When alpha_x/beta_y are non-NULL the unbalanced shift correction
+ *   f_out -= w*alpha_x*(1-damp_f),  g_out -= w*beta_y*(1-damp_g)
+ * (sinkhorn_solvers.py:509-517) is fused in; pass NULL to get exactly the
+ * kernel result of kernels/sinkhorn_flashstyle_sqeuclid.py:1093-1317
+ * (flashsinkhorn_symmetric_step). f_out/g_out must not alias f_hat/g_hat. */
+int fs_symmetric_step(const float* x, const float* y, int n, int m, int d,
+                      const float* f_hat, const float* g_hat,
+                      const float* log_a, const float* log_b,
+                      float* f_out, float* g_out,
+                      const float* alpha_x, const float* beta_y,
+                      float eps, float w, float damp_f, float damp_g, float cost_scale,
+                      int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* Whole symmetric (GeomLoss-style) solve, enqueued without host synchronisation.
+ * Schedule: one step with weight 1 at eps_list[0]; one step with weight 1/2 per
+ * entry of eps_list; if last_extrapolation, one more step with weight 1 at
+ * eps_list[n_eps-1]. Early stop (threshold >= 0): every check_every loop steps
+ * max|delta f_hat|, max|delta g_hat| against the snapshot of the previous check
+ * is evaluated ON THE DEVICE; once below threshold the remaining loop steps are
+ * skipped (the final extrapolation still runs).
+ *   f_init/g_init : standard (unshifted) warm-start potentials or NULL (zeros)
+ *   f, g          : final standard potentials
+ *   f_pre, g_pre  : potentials before the extrapolation step (may be NULL)
+ *   iters_used    : device int, number of steps executed (may be NULL)
+ * Replaces sinkhorn_solvers.py:290-707 (sinkhorn_flashstyle_symmetric). */
+int fs_solve_symmetric(const float* x, const float* y, int n, int m, int d,
+                       const float* log_a, const float* log_b,
+                       const double* eps_list_host, int n_eps, int last_extrapolation,
+                       float cost_scale, double rho_x, double rho_y,
+                       double threshold, int check_every,
+                       const float* f_init, const float* g_init,
+                       float* f, float* g, float* f_pre, float* g_pre,
+                       int* iters_used,
+                       int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* Whole alternating (Gauss-Seidel) solve. For each eps of eps_list, iters_per_eps
+ * iterations of { f_hat <- LSE(g_hat) ; g_hat <- LSE(new f_hat) } (no averaging,
+ * no shift correction), warm-started from the previous eps. With n_eps == 1 this
+ * is sinkhorn_solvers.py:30-287 (sinkhorn_flashstyle_alternating) with
+ * n_iters = iters_per_eps; ott_convention != 0 selects its :188-228 branch
+ * (g first, log-marginals outside the LSE). Early stop as above, counted in
+ * iterations across the whole run. tile_row_ptr/tile_col_idx (may be NULL) give a
+ * CSR list of kept 128x128 (x-tile, y-tile) pairs: tiles not listed contribute
+ * nothing to either LSE (block-sparse skipping; no reference counterpart). */
+int fs_solve_alternating(const float* x, const float* y, int n, int m, int d,
+                         const float* log_a, const float* log_b,
+                         const double* eps_list_host, int n_eps, int iters_per_eps,
+                         float cost_scale, double rho_x, double rho_y,
+                         int ott_convention, double threshold, int check_every,
+                         const int* tile_row_ptr, const int* tile_col_idx,
+                         const int* tile_row_ptr_t, const int* tile_col_idx_t,
+                         float* f, float* g, int* iters_used,
+                         int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* out = P v (axis 1, v has m entries, out n) or P^T v (axis 0), with
+ * P_ij = exp( (f_hat_i + g_hat_j + 2cs x_i.y_j)/eps + log_a_i + log_b_j ).
+ * Replaces kernels/apply_flash.py:835-951 (apply_plan_vec_flashstyle). */
+int fs_apply_vec(const float* x, const float* y, int n, int m, int d,
+                 const float* f_hat, const float* g_hat,
+                 const float* log_a, const float* log_b,
+                 const float* vec, float* out,
+                 float eps, int axis, float cost_scale,
+                 int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* out = P V (axis 1: V is [m,dv], out [n,dv]; optional scale[m] multiplies the
+ * rows of V) or P^T V (axis 0: V is [n,dv], out [m,dv]; scale must be NULL).
+ * Replaces kernels/apply_flash.py:360-579 (apply_plan_mat_flashstyle; the
+ * reference requires dv == d, this ABI does not). */
+int fs_apply_mat(const float* x, const float* y, int n, int m, int d,
+                 const float* f_hat, const float* g_hat,
+                 const float* log_a, const float* log_b,
+                 const float* mat, int dv, const float* scale, float* out,
+                 float eps, int axis, float cost_scale,
+                 int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* Analytic gradient of the OT cost (barycentric form), standard potentials f, g:
+ *   grad_x_i = 2cs*gs*a_i*( x_i - sum_j w_ij y_j / max(sum_j w_ij, 1e-40) ),
+ *   w_ij = exp( (g_j - C_ij)/eps + log_b_j );  grad_y symmetric with f, a.
+ * grad_scale points to one device float (gs) or is NULL (gs = 1). Either output
+ * may be NULL. Any d (no separate large-d entry point). Replaces
+ * kernels/sinkhorn_triton_grad_sqeuclid.py:891-1207
+ * (sinkhorn_geomloss_online_grad_sqeuclid). */
+int fs_grad(const float* x, const float* y, int n, int m, int d,
+            const float* a, const float* b, const float* log_a, const float* log_b,
+            const float* f, const float* g, const float* grad_scale,
+            float* grad_x, float* grad_y,
+            float eps, float cost_scale,
+            int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* out_i = (-4cs/eps) sum_j P_ij (A_i.y_j) y_j with P_ij = exp((f_i+g_j-C_ij)/eps)
+ * (OTT-convention potentials, log-weights already inside f, g). Replaces
+ * kernels/apply_ott.py:453-566 (mat5_sqeuclid). */
+int fs_mat5(const float* x, const float* y, int n, int m, int d,
+            const float* f_ott, const float* g_ott, const float* A, float* out,
+            float eps, float cost_scale,
+            int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* Conjugate gradient on the HVP's Schur complement, entirely on the device:
+ *   solve (diag(denom) - P^T diag(1/diag_x) P) z = rhs,  z0 = 0,
+ * stopping when |r| <= max(atol, rtol*|r0|) or after max_iter iterations; all
+ * dot products, the stopping test and the iteration counter stay on the GPU.
+ * info (device, 4 floats): [converged(0/1), iterations, |r|, |r0|].
+ * Replaces the loop of cg.py:27-121 (conjugate_gradient) as driven by
+ * hvp.py:505-520 (two plan applications per iteration). */
+int fs_schur_cg(const float* x, const float* y, int n, int m, int d,
+                const float* f_hat, const float* g_hat,
+                const float* log_a, const float* log_b,
+                const float* diag_x, const float* denom, const float* rhs,
+                float* z, float* info,
+                float eps, float cost_scale, int max_iter, float rtol, float atol,
+                int prec, void* ws, size_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_SINKHORN_B200_H */

@@ -1,0 +1,303 @@
+"""Generate the golden fixtures under tests/golden/ by running the REFERENCE itself.
+
+Run once, in a container that has the reference checkout (no GPU needed):
+
+    TRITON_INTERPRET=1 PYTHONPATH=<reference>/src python tests/golden/make_golden.py [--skip-c1]
+
+Two sources of truth are used:
+  * the reference's dense PyTorch oracles (testing/reference_sinkhorn.py,
+    testing/reference_hvp.py), on CPU tensors;
+  * the reference's own Triton kernels and host loops (SamplesLoss, solvers, apply,
+    gradient, mat5, HVP) executed on CPU tensors by the Triton interpreter. The library
+    refuses non-CUDA tensors in a few wrappers, so ``torch.Tensor.is_cuda`` is patched to
+    report True for the duration of this script; no reference source is modified.
+
+Inputs are drawn from a CPU ``torch.Generator`` and stored next to the outputs, so the
+tests never need the reference. Everything is float32 unless noted.
+"""
+import argparse
+import math
+import os
+import sys
+import time
+
+os.environ.setdefault("TRITON_INTERPRET", "1")
+
+import numpy as np
+import torch
+
+torch.Tensor.is_cuda = property(lambda self: True)  # see module docstring
+
+import flash_sinkhorn  # noqa: E402  (the reference)
+from flash_sinkhorn import SamplesLoss  # noqa: E402
+from flash_sinkhorn.hvp import geomloss_to_ott_potentials, hvp_x_sqeuclid_from_potentials  # noqa: E402
+from flash_sinkhorn.kernels.apply_flash import apply_plan_mat_flashstyle, apply_plan_vec_flashstyle  # noqa: E402
+from flash_sinkhorn.kernels.apply_ott import mat5_sqeuclid  # noqa: E402
+from flash_sinkhorn.kernels.sinkhorn_flashstyle_sqeuclid import (  # noqa: E402
+    flashsinkhorn_lse,
+    flashsinkhorn_lse_fused,
+    flashsinkhorn_symmetric_step,
+)
+from flash_sinkhorn.kernels.sinkhorn_triton_grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid  # noqa: E402
+from flash_sinkhorn.kernels._common import epsilon_schedule, log_weights, max_diameter  # noqa: E402
+from flash_sinkhorn.sinkhorn_solvers import sinkhorn_flashstyle_alternating, sinkhorn_flashstyle_symmetric  # noqa: E402
+from flash_sinkhorn.testing import reference_hvp, reference_sinkhorn  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+MANUAL = dict(autotune=False, block_m=32, block_n=32, block_k=16)  # the autotuner needs a GPU driver
+
+
+def np32(t):
+    return t.detach().cpu().numpy().astype(np.float32)
+
+
+def clouds(seed, n, m, d, shift=0.0, weights="uniform", mass_b=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, d, generator=gen)
+    y = shift + torch.randn(m, d, generator=gen)
+    if weights == "uniform":
+        a = torch.full((n,), 1.0 / n)
+        b = torch.full((m,), mass_b / m)
+    else:
+        a = torch.softmax(torch.randn(n, generator=gen), dim=0)
+        b = torch.softmax(torch.randn(m, generator=gen), dim=0) * mass_b
+    return x, y, a, b
+
+
+def save(name, **arrays):
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **arrays)
+    print(f"wrote {path} ({os.path.getsize(path)} bytes)")
+
+
+def gen_kernels():
+    """Single kernel calls: LSE (raw/fused bias), symmetric step, apply vec/mat, gradient, mat5."""
+    n, m, d = 70, 52, 12
+    x, y, a, b = clouds(11, n, m, d, shift=0.3, weights="softmax", mass_b=1.3)
+    eps, cs = 0.37, 0.5
+    gen = torch.Generator().manual_seed(12)
+    f_hat = -cs * (x**2).sum(1) + 0.1 * torch.randn(n, generator=gen)
+    g_hat = -cs * (y**2).sum(1) + 0.1 * torch.randn(m, generator=gen)
+    la, lb = log_weights(a), log_weights(b)
+    bias = g_hat / eps + lb
+    out = dict(x=np32(x), y=np32(y), a=np32(a), b=np32(b), f_hat=np32(f_hat), g_hat=np32(g_hat),
+               eps=np.float64(eps), cost_scale=np.float64(cs))
+    kw = dict(allow_tf32=False, **MANUAL)
+    out["lse_raw"] = np32(flashsinkhorn_lse(x, y, bias, eps, cost_scale=cs, damping=0.8, **kw))
+    out["lse_fused"] = np32(flashsinkhorn_lse_fused(x, y, g_hat, lb, eps, cost_scale=cs, damping=1.0, **kw))
+    fs, gs = flashsinkhorn_symmetric_step(x, y, f_hat, g_hat, la, lb, eps, cost_scale=cs, alpha=0.5,
+                                          damping_f=0.9, damping_g=0.7, **kw)
+    out["step_f"], out["step_g"] = np32(fs), np32(gs)
+    vec_m = torch.randn(m, generator=gen)
+    vec_n = torch.randn(n, generator=gen)
+    akw = dict(eps=eps, cost_scale=cs, allow_tf32=False)
+    out["vec_m"], out["vec_n"] = np32(vec_m), np32(vec_n)
+    out["apply_vec_axis1"] = np32(apply_plan_vec_flashstyle(x, y, f_hat, g_hat, la, lb, vec_m, axis=1,
+                                                            block_m=32, block_n=32, block_k=16, **akw))
+    out["apply_vec_axis0"] = np32(apply_plan_vec_flashstyle(x, y, f_hat, g_hat, la, lb, vec_n, axis=0,
+                                                            block_m=32, block_n=32, block_k=16, **akw))
+    mat_m = torch.randn(m, d, generator=gen)
+    mat_n = torch.randn(n, d, generator=gen)
+    scale = torch.randn(m, generator=gen)
+    out["mat_m"], out["mat_n"], out["scale"] = np32(mat_m), np32(mat_n), np32(scale)
+    mkw = dict(block_d=16, **MANUAL)
+    out["apply_mat_axis1"] = np32(apply_plan_mat_flashstyle(x, y, f_hat, g_hat, la, lb, mat_m, axis=1, **akw, **mkw))
+    out["apply_mat_axis1_scaled"] = np32(apply_plan_mat_flashstyle(x, y, f_hat, g_hat, la, lb, mat_m, axis=1,
+                                                                   scale=scale, **akw, **mkw))
+    out["apply_mat_axis0"] = np32(apply_plan_mat_flashstyle(x, y, f_hat, g_hat, la, lb, mat_n, axis=0, **akw, **mkw))
+    # gradient kernel from standard potentials
+    f_std = f_hat + cs * (x**2).sum(1)
+    g_std = g_hat + cs * (y**2).sum(1)
+    gsc = torch.tensor(1.7)
+    gx, gy = sinkhorn_geomloss_online_grad_sqeuclid(x, y, a, b, f_std, g_std, eps=eps, allow_tf32=False,
+                                                    cost_scale=cs, grad_scale=gsc, num_warps=4, **MANUAL)
+    out["f_std"], out["g_std"], out["grad_scale"] = np32(f_std), np32(g_std), np.float32(1.7)
+    out["grad_x"], out["grad_y"] = np32(gx), np32(gy)
+    # mat5 with OTT-convention potentials
+    f_ott, g_ott = geomloss_to_ott_potentials(f_std, g_std, a, b, eps=eps)
+    out["f_ott"], out["g_ott"] = np32(f_ott), np32(g_ott)
+    out["mat5"] = np32(mat5_sqeuclid(x, y, f_ott, g_ott, mat_n, eps=eps, cost_scale=cs, allow_tf32=False, **MANUAL))
+    save("kernels_small", **out)
+
+
+def gen_solvers():
+    """Whole solves through the reference's host loops + Triton kernels (interpreter)."""
+    n, m, d = 96, 80, 16
+    x, y, a, b = clouds(21, n, m, d, shift=0.2, weights="softmax", mass_b=1.3)
+    base = dict(x=np32(x), y=np32(y), a=np32(a), b=np32(b))
+    out = dict(base)
+    cases = {
+        "bal_sched": dict(cost_scale=1.0, rho_x=None, rho_y=None),
+        "half_semi": dict(cost_scale=0.5, rho_x=1.0, rho_y=None),
+        "unbal": dict(cost_scale=1.0, rho_x=1.0, rho_y=4.0),
+    }
+    diam = max_diameter(x, y)
+    sched = epsilon_schedule(diam, 0.3, 0.6, p=2.0)
+    out["sched"] = np.array(sched, np.float64)
+    out["diameter"] = np.float64(diam)
+    for name, c in cases.items():
+        for fused in (True, False):
+            f, g, fp, gp, k = sinkhorn_flashstyle_symmetric(
+                x, y, a, b, blur=0.3, scaling=0.6, use_epsilon_scaling=True, allow_tf32=False, autotune=False,
+                fused=fused, return_prelast=True, return_n_iters=True, **c)
+            tag = f"sym_{name}_{'fused' if fused else 'sep'}"
+            out[tag + "_f"], out[tag + "_g"] = np32(f), np32(g)
+            out[tag + "_fpre"], out[tag + "_gpre"] = np32(fp), np32(gp)
+            out[tag + "_iters"] = np.int64(k)
+    # fixed eps + early stopping
+    f, g, k = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=0.5, n_iters=60,
+                                            allow_tf32=False, autotune=False, threshold=1e-3, check_every=4,
+                                            return_n_iters=True)
+    out["sym_early_f"], out["sym_early_g"], out["sym_early_iters"] = np32(f), np32(g), np.int64(k)
+    # warm start
+    f2, g2 = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=0.5, n_iters=3,
+                                           allow_tf32=False, autotune=False, f_init=f, g_init=g,
+                                           last_extrapolation=False)
+    out["sym_warm_f"], out["sym_warm_g"] = np32(f2), np32(g2)
+    # alternating
+    for conv in (False, True):
+        for rho in (None, 2.0):
+            f, g, k = sinkhorn_flashstyle_alternating(x, y, a, b, eps=0.4, n_iters=12, cost_scale=0.5,
+                                                      rho_x=rho, rho_y=rho, allow_tf32=False, autotune=False,
+                                                      ott_convention=conv, return_n_iters=True)
+            tag = f"alt_{'ott' if conv else 'geo'}_{'bal' if rho is None else 'unb'}"
+            out[tag + "_f"], out[tag + "_g"], out[tag + "_iters"] = np32(f), np32(g), np.int64(k)
+    f, g, k = sinkhorn_flashstyle_alternating(x, y, a, b, eps=0.4, n_iters=80, allow_tf32=False, autotune=False,
+                                              threshold=1e-4, check_every=3, return_n_iters=True)
+    out["alt_early_f"], out["alt_early_g"], out["alt_early_iters"] = np32(f), np32(g), np.int64(k)
+    save("solvers_small", **out)
+
+
+def gen_samples_loss():
+    """SamplesLoss forward / backward / double backward through the reference's autograd glue."""
+    n, m, d = 64, 48, 8
+    x, y, a, b = clouds(31, n, m, d, shift=0.25, weights="softmax", mass_b=1.0)
+    out = dict(x=np32(x), y=np32(y), a=np32(a), b=np32(b))
+    gen = torch.Generator().manual_seed(32)
+    v = torch.randn(n, d, generator=gen)
+    out["v"] = np32(v)
+    common = dict(allow_tf32=False, autotune=False, block_m=32, block_n=32, block_k=16)
+    configs = {
+        "bal_debias_half": dict(blur=0.5, scaling=0.7, debias=True, half_cost=True),
+        "bal_fixed": dict(blur=0.6, use_epsilon_scaling=False, eps=0.36, n_iters=25),
+        "semi": dict(blur=0.5, scaling=0.7, reach_x=1.5),
+        "unbal": dict(blur=0.5, scaling=0.7, reach=1.2, normalize=False),
+        "alt": dict(backend="alternating", use_epsilon_scaling=False, eps=0.3, n_iters=15, blur=0.5),
+    }
+    for name, cfg in configs.items():
+        xs = x.clone().requires_grad_(True)
+        ys = y.clone().requires_grad_(True)
+        a_s = a.clone().requires_grad_(True)
+        loss_fn = SamplesLoss("sinkhorn", **cfg, **common)
+        val = loss_fn(a_s, xs, b, ys)
+        gx, gy, ga = torch.autograd.grad(val, (xs, ys, a_s))
+        out[name + "_loss"] = np.float32(val.item())
+        out[name + "_gx"], out[name + "_gy"], out[name + "_ga"] = np32(gx), np32(gy), np32(ga)
+        f, g = SamplesLoss("sinkhorn", potentials=True, **cfg, **common)(a, x, b, y)
+        out[name + "_f"], out[name + "_g"] = np32(f), np32(g)
+    # (x, y) call form with uniform weights
+    out["xy_loss"] = np.float32(SamplesLoss("sinkhorn", blur=0.5, scaling=0.7, **common)(x, y).item())
+    save("samples_loss_small", **out)
+
+
+def gen_hvp():
+    """HVP: reference streaming implementation (interpreter) and its dense oracle."""
+    n, m, d = 40, 32, 6
+    x, y, a, b = clouds(41, n, m, d, shift=0.2, weights="softmax", mass_b=1.0)
+    gen = torch.Generator().manual_seed(42)
+    A = torch.randn(n, d, generator=gen)
+    eps = 0.45
+    out = dict(x=np32(x), y=np32(y), a=np32(a), b=np32(b), A=np32(A), eps=np.float64(eps))
+    for name, (rx, ry, cs) in {"bal": (None, None, 1.0), "semi_half": (2.0, None, 0.5)}.items():
+        f, g, fp, gp = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=eps, n_iters=200,
+                                                     allow_tf32=False, autotune=False, return_prelast=True,
+                                                     cost_scale=cs, rho_x=rx, rho_y=ry)
+        f_ott, g_ott = geomloss_to_ott_potentials(fp, gp, a, b, eps=eps)
+        hv, info = hvp_x_sqeuclid_from_potentials(x, y, f_ott, g_ott, A, eps=eps, rho_x=rx, rho_y=ry, cost_scale=cs,
+                                                  max_cg_iter=400, autotune=False, block_m=32, block_n=32, block_k=16)
+        out[name + "_f_ott"], out[name + "_g_ott"] = np32(f_ott), np32(g_ott)
+        out[name + "_hvp"] = np32(hv)
+        out[name + "_cg"] = np.array([float(info.cg_converged), info.cg_iters, info.cg_residual,
+                                      info.cg_initial_residual], np.float64)
+        if cs == 1.0:
+            dense, _ = reference_hvp.hvp_x_dense_sqeuclid_semi_unbalanced(
+                x, y, f_ott, g_ott, A, eps=eps, rho_x=rx, rho_y=ry, max_cg_iter=400,
+                use_preconditioner=False)  # its default Neumann preconditioner diverges on this case
+            out[name + "_hvp_dense"] = np32(dense)
+    save("hvp_small", **out)
+
+
+def gen_dense_reference():
+    """The reference's dense oracles alone (no Triton): symmetric potentials, OTT alternating, gradients."""
+    n, m, d = 128, 96, 32
+    x, y, a, b = clouds(51, n, m, d, shift=0.1, weights="softmax")
+    out = dict(x=np32(x), y=np32(y), a=np32(a), b=np32(b))
+    f, g = reference_sinkhorn.sinkhorn_geomloss_potentials_ref(x, y, a, b, blur=0.4, scaling=0.6)
+    out["sym_f"], out["sym_g"] = np32(f), np32(g)
+    f, g = reference_sinkhorn.sinkhorn_geomloss_potentials_ref(x, y, a, b, use_epsilon_scaling=False, eps=0.3,
+                                                               n_iters=20, last_extrapolation=False)
+    out["fix_f"], out["fix_g"] = np32(f), np32(g)
+    gx, gy = reference_sinkhorn.sinkhorn_geomloss_barycentric_grads_ref(x, y, a, b, f, g, eps=0.3)
+    out["bary_gx"], out["bary_gy"] = np32(gx), np32(gy)
+    fo, go = reference_sinkhorn.sinkhorn_potentials_ref(x, y, a.log(), b.log(), 0.3, 15)
+    out["ott_f"], out["ott_g"] = np32(fo), np32(go)
+    save("dense_reference", **out)
+
+
+def gen_config1():
+    """BASELINE config 1 (n=m=4096, d=64, eps=0.01, half cost, debias, 100 fixed iterations) with the
+    reference's dense fp32 functions. Inputs are NOT stored: CPU generator seed 0, x then y."""
+    t0 = time.time()
+    gen = torch.Generator().manual_seed(0)
+    n = m = 4096
+    d = 64
+    x = torch.randn(n, d, generator=gen)
+    y = torch.randn(m, d, generator=gen)
+    a = torch.full((n,), 1.0 / n)
+    b = torch.full((m,), 1.0 / m)
+    eps, iters = 0.01, 100
+    s = math.sqrt(0.5)  # half cost == squared distance of inputs scaled by sqrt(1/2) (exact scaling of the cost)
+
+    def solve(p, q, wp, wq):
+        eps_list = [eps] * iters
+        ps, qs = p * s, q * s
+        f_pre, g_pre = reference_sinkhorn.sinkhorn_geomloss_potentials_ref(
+            ps, qs, wp, wq, use_epsilon_scaling=False, eps=eps, n_iters=iters, last_extrapolation=False)
+        f, g = reference_sinkhorn.sinkhorn_geomloss_potentials_ref(
+            ps, qs, wp, wq, use_epsilon_scaling=False, eps=eps, n_iters=iters, last_extrapolation=True)
+        cost = (wp * f).sum() + (wq * g).sum()
+        gp, gq = reference_sinkhorn.sinkhorn_geomloss_barycentric_grads_ref(ps, qs, wp, wq, f_pre, g_pre, eps)
+        return cost.item(), gp * s, gq * s  # chain rule through the sqrt(1/2) scaling
+
+    c_xy, gx_xy, _ = solve(x, y, a, b)
+    c_xx, gx_xx, gy_xx = solve(x, x, a, a)
+    c_yy, _, _ = solve(y, y, b, b)
+    loss = c_xy - 0.5 * c_xx - 0.5 * c_yy
+    grad_x = gx_xy - 0.5 * (gx_xx + gy_xx)
+    print(f"config1: OT_xy={c_xy!r} OT_xx={c_xx!r} OT_yy={c_yy!r} loss={loss!r} |grad|={grad_x.norm().item()!r} "
+          f"({time.time() - t0:.0f}s)")
+    save("config1", ot_xy=np.float64(c_xy), ot_xx=np.float64(c_xx), ot_yy=np.float64(c_yy), loss=np.float64(loss),
+         grad_x_norm=np.float64(grad_x.norm().item()), grad_x_head=np32(grad_x[:16]),
+         grad_x_rowsum=np32(grad_x.sum(dim=1)))
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--skip-c1", action="store_true", help="skip the 4096x4096 dense solves (several minutes)")
+    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,dense,c1")
+    args = ap.parse_args()
+    which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "dense", "c1"}
+    print("reference version", flash_sinkhorn.__version__, "from", os.path.dirname(flash_sinkhorn.__file__))
+    if "dense" in which:
+        gen_dense_reference()
+    if "kernels" in which:
+        gen_kernels()
+    if "solvers" in which:
+        gen_solvers()
+    if "loss" in which:
+        gen_samples_loss()
+    if "hvp" in which:
+        gen_hvp()
+    if "c1" in which and not args.skip_c1:
+        gen_config1()
+    sys.exit(0)

@@ -1,0 +1,159 @@
+"""Pins the CPU oracle (oracle/dense_sinkhorn.py) against fixtures produced by the reference itself
+(tests/golden/make_golden.py). CPU only."""
+import numpy as np
+import pytest
+
+from conftest import load_golden, rel_err
+from oracle import dense_sinkhorn as O
+
+F64 = np.float64
+
+
+def d64(z, *names):
+    return [z[k].astype(F64) for k in names]
+
+
+def test_host_scalars():
+    z = load_golden("solvers_small")
+    x, y = z["x"], z["y"]
+    assert abs(O.max_diameter(x, y) - float(z["diameter"])) < 1e-5 * float(z["diameter"])
+    sched = O.epsilon_schedule(float(z["diameter"]), 0.3, 0.6)
+    assert np.array_equal(np.array(sched, F64), z["sched"])  # bit-identical schedule
+    assert O.dampening(0.5, None) == 1.0
+    assert O.dampening(0.5, 2.0) == pytest.approx(1.0 / 1.25)
+    lw = O.log_weights(np.array([0.5, 0.0, -1.0]))
+    assert lw[1] == -100000.0 and lw[2] == -100000.0 and lw[0] == pytest.approx(np.log(0.5))
+
+
+def test_single_kernels():
+    z = load_golden("kernels_small")
+    x, y, a, b, fh, gh = d64(z, "x", "y", "a", "b", "f_hat", "g_hat")
+    eps, cs = float(z["eps"]), float(z["cost_scale"])
+    la, lb = O.log_weights(a), O.log_weights(b)
+    assert rel_err(O.lse_update(x, y, gh / eps + lb, eps, cs, 0.8), z["lse_raw"]) < 2e-5
+    assert rel_err(O.lse_update_fused(x, y, gh, lb, eps, cs, 1.0), z["lse_fused"]) < 2e-5
+    sf, sg = O.symmetric_step(x, y, fh, gh, la, lb, eps, cs, 0.5, 0.9, 0.7)
+    assert rel_err(sf, z["step_f"]) < 2e-5 and rel_err(sg, z["step_g"]) < 2e-5
+    vm, vn, mm, mn, sc = d64(z, "vec_m", "vec_n", "mat_m", "mat_n", "scale")
+    assert rel_err(O.apply_vec(x, y, fh, gh, la, lb, vm, eps, 1, cs), z["apply_vec_axis1"]) < 1e-4
+    assert rel_err(O.apply_vec(x, y, fh, gh, la, lb, vn, eps, 0, cs), z["apply_vec_axis0"]) < 1e-4
+    assert rel_err(O.apply_mat(x, y, fh, gh, la, lb, mm, eps, 1, cs), z["apply_mat_axis1"]) < 1e-4
+    assert rel_err(O.apply_mat(x, y, fh, gh, la, lb, mm, eps, 1, cs, scale=sc), z["apply_mat_axis1_scaled"]) < 1e-4
+    assert rel_err(O.apply_mat(x, y, fh, gh, la, lb, mn, eps, 0, cs), z["apply_mat_axis0"]) < 1e-4
+    f, g = d64(z, "f_std", "g_std")
+    gx, gy = O.grad_xy(x, y, a, b, f, g, eps, cs, float(z["grad_scale"]))
+    assert rel_err(gx, z["grad_x"]) < 1e-4 and rel_err(gy, z["grad_y"]) < 1e-4
+    fo, go = d64(z, "f_ott", "g_ott")
+    assert rel_err(O.mat5(x, y, fo, go, mn, eps, cs), z["mat5"]) < 1e-4
+
+
+@pytest.mark.parametrize("name,cs,rx,ry", [("bal_sched", 1.0, None, None), ("half_semi", 0.5, 1.0, None),
+                                           ("unbal", 1.0, 1.0, 4.0)])
+def test_symmetric_solver(name, cs, rx, ry):
+    z = load_golden("solvers_small")
+    x, y, a, b = d64(z, "x", "y", "a", "b")
+    s = O.solve_symmetric(x, y, a, b, list(z["sched"]), cost_scale=cs, rho_x=rx, rho_y=ry)
+    for variant in ("fused", "sep"):
+        tag = f"sym_{name}_{variant}"
+        assert s["n_iters"] == int(z[tag + "_iters"])
+        for k, key in (("f", "_f"), ("g", "_g"), ("f_pre", "_fpre"), ("g_pre", "_gpre")):
+            assert rel_err(s[k], z[tag + key]) < 3e-5, (tag, k)
+
+
+def test_symmetric_early_stop_and_warm_start():
+    z = load_golden("solvers_small")
+    x, y, a, b = d64(z, "x", "y", "a", "b")
+    s = O.solve_symmetric(x, y, a, b, [0.5] * 60, threshold=1e-3, check_every=4)
+    assert s["n_iters"] == int(z["sym_early_iters"])
+    assert rel_err(s["f"], z["sym_early_f"]) < 3e-5 and rel_err(s["g"], z["sym_early_g"]) < 3e-5
+    w = O.solve_symmetric(x, y, a, b, [0.5] * 3, last_extrapolation=False,
+                          f_init=z["sym_early_f"].astype(F64), g_init=z["sym_early_g"].astype(F64))
+    assert rel_err(w["f"], z["sym_warm_f"]) < 3e-5 and rel_err(w["g"], z["sym_warm_g"]) < 3e-5
+
+
+@pytest.mark.parametrize("conv", [False, True])
+@pytest.mark.parametrize("rho", [None, 2.0])
+def test_alternating_solver(conv, rho):
+    z = load_golden("solvers_small")
+    x, y, a, b = d64(z, "x", "y", "a", "b")
+    s = O.solve_alternating(x, y, a, b, [0.4], 12, cost_scale=0.5, rho_x=rho, rho_y=rho, ott_convention=conv)
+    tag = f"alt_{'ott' if conv else 'geo'}_{'bal' if rho is None else 'unb'}"
+    assert s["n_iters"] == int(z[tag + "_iters"]) == 12
+    assert rel_err(s["f"], z[tag + "_f"]) < 3e-5 and rel_err(s["g"], z[tag + "_g"]) < 3e-5
+
+
+def test_alternating_early_stop():
+    z = load_golden("solvers_small")
+    x, y, a, b = d64(z, "x", "y", "a", "b")
+    s = O.solve_alternating(x, y, a, b, [0.4], 80, threshold=1e-4, check_every=3)
+    assert s["n_iters"] == int(z["alt_early_iters"])
+    assert rel_err(s["f"], z["alt_early_f"]) < 3e-5
+
+
+def test_dense_reference_functions():
+    z = load_golden("dense_reference")
+    x, y, a, b = d64(z, "x", "y", "a", "b")
+    diam = O.max_diameter(z["x"], z["y"])
+    s = O.solve_symmetric(x, y, a, b, O.epsilon_schedule(diam, 0.4, 0.6))
+    assert rel_err(s["f"], z["sym_f"]) < 3e-5 and rel_err(s["g"], z["sym_g"]) < 3e-5
+    s = O.solve_symmetric(x, y, a, b, [0.3] * 20, last_extrapolation=False)
+    assert rel_err(s["f"], z["fix_f"]) < 3e-5 and rel_err(s["g"], z["fix_g"]) < 3e-5
+    gx, gy = O.grad_xy(x, y, a, b, z["fix_f"].astype(F64), z["fix_g"].astype(F64), 0.3)
+    assert rel_err(gx, z["bary_gx"]) < 1e-4 and rel_err(gy, z["bary_gy"]) < 1e-4
+    s = O.solve_alternating(x, y, a, b, [0.3], 15, ott_convention=True)
+    assert rel_err(s["f"], z["ott_f"]) < 3e-5 and rel_err(s["g"], z["ott_g"]) < 3e-5
+
+
+LOSS_CASES = {
+    "bal_debias_half": dict(blur=0.5, scaling=0.7, debias=True, cost_scale=0.5),
+    "bal_fixed": dict(eps_list=[0.36] * 25),
+    "semi": dict(blur=0.5, scaling=0.7, rho_x=1.5**2),
+    "unbal": dict(blur=0.5, scaling=0.7, rho_x=1.2**2, rho_y=1.2**2),
+}
+
+
+@pytest.mark.parametrize("name", sorted(LOSS_CASES))
+def test_samples_loss(name):
+    z = load_golden("samples_loss_small")
+    x, y, a, b = d64(z, "x", "y", "a", "b")
+    cfg = dict(LOSS_CASES[name])
+    if "eps_list" in cfg:
+        sched = cfg.pop("eps_list")
+    else:
+        sched = O.epsilon_schedule(O.max_diameter(z["x"], z["y"]), cfg.pop("blur"), cfg.pop("scaling"))
+    r = O.samples_loss(x, y, a, b, sched, want_grad_x=True, **cfg)
+    assert abs(r["loss"] - float(z[name + "_loss"])) < 2e-5 * max(1.0, abs(float(z[name + "_loss"])))
+    assert rel_err(r["grad_x"], z[name + "_gx"]) < 2e-4
+
+
+def test_samples_loss_alternating_and_uniform():
+    z = load_golden("samples_loss_small")
+    x, y, a, b = d64(z, "x", "y", "a", "b")
+    s = O.solve_alternating(x, y, a, b, [0.3], 15)
+    assert rel_err(s["f"], z["alt_f"]) < 3e-5
+    assert abs(O.ot_cost(a, b, s["f"], s["g"], 0.3) - float(z["alt_loss"])) < 2e-5 * abs(float(z["alt_loss"]))
+    n, m = x.shape[0], y.shape[0]
+    sched = O.epsilon_schedule(O.max_diameter(z["x"], z["y"]), 0.5, 0.7)
+    r = O.samples_loss(x, y, np.full(n, 1.0 / n), np.full(m, 1.0 / m), sched)
+    # weights created in fp32 by the reference (1/n rounded): tolerance covers that
+    assert abs(r["loss"] - float(z["xy_loss"])) < 1e-5 * abs(float(z["xy_loss"]))
+
+
+@pytest.mark.parametrize("name,rx,ry,cs", [("bal", None, None, 1.0), ("semi_half", 2.0, None, 0.5)])
+def test_hvp(name, rx, ry, cs):
+    z = load_golden("hvp_small")
+    x, y, A, fo, go = d64(z, "x", "y", "A", name + "_f_ott", name + "_g_ott")
+    eps = float(z["eps"])
+    r = O.hvp_x(x, y, fo, go, A, eps, rho_x=rx, rho_y=ry, cost_scale=cs, max_cg_iter=400)
+    assert rel_err(r["hvp"], z[name + "_hvp"]) < 3e-4
+    if name + "_hvp_dense" in z:
+        assert rel_err(r["hvp"], z[name + "_hvp_dense"]) < 1e-4
+    direct = O.hvp_x(x, y, fo, go, A, eps, rho_x=rx, rho_y=ry, cost_scale=cs, direct_solve=True)
+    assert rel_err(direct["hvp"], r["hvp"]) < 1e-3
+
+
+def test_config1_golden_is_recorded():
+    z = load_golden("config1")
+    # Values measured independently during the survey of the reference (fp32 dense path).
+    assert float(z["loss"]) == pytest.approx(36.8802109, rel=2e-6)
+    assert float(z["grad_x_norm"]) == pytest.approx(0.128287598, rel=2e-4)
