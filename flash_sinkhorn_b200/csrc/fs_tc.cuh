@@ -1,20 +1,33 @@
 // tcgen05 / TMEM / TMA engine interface (implemented in fs_tc.cu).
+//
+// The score tile S = rows x cols^T is a dense contraction, so it runs on the 5th-gen
+// tensor cores: operands are staged once per call as K-padded, TF32-rounded copies
+// (3xTF32 hi/lo splits in exact-fp32 mode) whose last K columns carry the per-column
+// bias, split into three TF32 pieces that multiply constant ones on the row side --
+// the bias add is done by the MMA itself and the soft-max warps only see finished
+// logits (up to a common positive scale).
 #pragma once
 #include "fs_common.cuh"
 
 namespace fs {
 namespace tc {
 
-// Operands staged for the tensor-core path: K-padded, TF32-rounded copies of the
-// two clouds with the per-column bias folded into extra K columns.
+struct CloudOps {
+  float* opA = nullptr;  // [rows_pad, kp] row-operand form (ones in the bias columns)
+  float* opB = nullptr;  // [rows_pad, kp] column-operand form (bias columns rewritten per pass)
+  int rows = 0, rows_pad = 0;
+};
+
 struct Staged {
-  void* impl = nullptr;
+  CloudOps cloud[2];  // 0 = x, 1 = y
+  int d = 0, kc = 0, kp = 0, prec = 0;
 };
 
 bool supported(int n, int m, int d, int prec);
 size_t staged_bytes(int n, int m, int d, int prec);
 cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
                   cudaStream_t st);
+// One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st);
 
 }  // namespace tc

@@ -144,13 +144,15 @@ def gen_solvers():
             out[tag + "_f"], out[tag + "_g"] = np32(f), np32(g)
             out[tag + "_fpre"], out[tag + "_gpre"] = np32(fp), np32(gp)
             out[tag + "_iters"] = np.int64(k)
-    # fixed eps + early stopping
-    f, g, k = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=0.5, n_iters=60,
+    # fixed eps + early stopping (equal masses, otherwise the balanced iteration drifts and never stops)
+    bn = b / b.sum()
+    out["b_normalised"] = np32(bn)
+    f, g, k = sinkhorn_flashstyle_symmetric(x, y, a, bn, use_epsilon_scaling=False, eps=5.0, n_iters=60,
                                             allow_tf32=False, autotune=False, threshold=1e-3, check_every=4,
                                             return_n_iters=True)
     out["sym_early_f"], out["sym_early_g"], out["sym_early_iters"] = np32(f), np32(g), np.int64(k)
     # warm start
-    f2, g2 = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=0.5, n_iters=3,
+    f2, g2 = sinkhorn_flashstyle_symmetric(x, y, a, bn, use_epsilon_scaling=False, eps=5.0, n_iters=3,
                                            allow_tf32=False, autotune=False, f_init=f, g_init=g,
                                            last_extrapolation=False)
     out["sym_warm_f"], out["sym_warm_g"] = np32(f2), np32(g2)
@@ -162,7 +164,7 @@ def gen_solvers():
                                                       ott_convention=conv, return_n_iters=True)
             tag = f"alt_{'ott' if conv else 'geo'}_{'bal' if rho is None else 'unb'}"
             out[tag + "_f"], out[tag + "_g"], out[tag + "_iters"] = np32(f), np32(g), np.int64(k)
-    f, g, k = sinkhorn_flashstyle_alternating(x, y, a, b, eps=0.4, n_iters=80, allow_tf32=False, autotune=False,
+    f, g, k = sinkhorn_flashstyle_alternating(x, y, a, bn, eps=5.0, n_iters=80, allow_tf32=False, autotune=False,
                                               threshold=1e-4, check_every=3, return_n_iters=True)
     out["alt_early_f"], out["alt_early_g"], out["alt_early_iters"] = np32(f), np32(g), np.int64(k)
     save("solvers_small", **out)

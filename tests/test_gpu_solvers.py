@@ -38,14 +38,14 @@ def test_symmetric_early_stop_and_warm_start(monkeypatch, mode):
     from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_symmetric
     set_mode(monkeypatch, mode)
     z = load_golden("solvers_small")
-    x, y, a, b = (dev(z[k]) for k in ("x", "y", "a", "b"))
-    f, g, k = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=0.5, n_iters=60,
+    x, y, a, b = (dev(z[k]) for k in ("x", "y", "a", "b_normalised"))
+    f, g, k = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=5.0, n_iters=60,
                                             threshold=1e-3, check_every=4, return_n_iters=True)
     if mode != "tf32":  # the stopping iteration is a discrete function of rounding noise
         assert k == int(z["sym_early_iters"])
     assert k < 62
     assert rel(host(f), z["sym_early_f"]) < max(TOL[mode], 2e-3)
-    f2, g2 = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=0.5, n_iters=3,
+    f2, g2 = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=5.0, n_iters=3,
                                            f_init=dev(z["sym_early_f"]), g_init=dev(z["sym_early_g"]),
                                            last_extrapolation=False)
     assert rel(host(f2), z["sym_warm_f"]) < TOL[mode] and rel(host(g2), z["sym_warm_g"]) < TOL[mode]
@@ -70,8 +70,8 @@ def test_alternating_early_stop_vs_reference(monkeypatch):
     from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating
     set_mode(monkeypatch, "fp32")
     z = load_golden("solvers_small")
-    x, y, a, b = (dev(z[k]) for k in ("x", "y", "a", "b"))
-    f, g, k = sinkhorn_flashstyle_alternating(x, y, a, b, eps=0.4, n_iters=80, threshold=1e-4, check_every=3,
+    x, y, a, b = (dev(z[k]) for k in ("x", "y", "a", "b_normalised"))
+    f, g, k = sinkhorn_flashstyle_alternating(x, y, a, b, eps=5.0, n_iters=80, threshold=1e-4, check_every=3,
                                               return_n_iters=True)
     assert k == int(z["alt_early_iters"])
     assert rel(host(f), z["alt_early_f"]) < 2e-4
@@ -183,7 +183,7 @@ def test_double_backward_equals_direct_hvp():
     z = load_golden("samples_loss_small")
     x, y, a, b, v = (dev(z[k]) for k in ("x", "y", "a", "b", "v"))
     xs = x.clone().requires_grad_(True)
-    cfg = dict(blur=0.6, use_epsilon_scaling=False, eps=0.36, n_iters=25, allow_tf32=False)
+    cfg = dict(blur=0.6, use_epsilon_scaling=False, eps=0.36, n_iters=25, allow_tf32=False, normalize=False)
     val = SamplesLoss("sinkhorn", **cfg)(a, xs, b, y)
     (gx,) = torch.autograd.grad(val, xs, create_graph=True)
     (hv,) = torch.autograd.grad((gx * v).sum(), xs)

@@ -62,11 +62,11 @@ def test_symmetric_solver(name, cs, rx, ry):
 
 def test_symmetric_early_stop_and_warm_start():
     z = load_golden("solvers_small")
-    x, y, a, b = d64(z, "x", "y", "a", "b")
-    s = O.solve_symmetric(x, y, a, b, [0.5] * 60, threshold=1e-3, check_every=4)
-    assert s["n_iters"] == int(z["sym_early_iters"])
+    x, y, a, b = d64(z, "x", "y", "a", "b_normalised")
+    s = O.solve_symmetric(x, y, a, b, [5.0] * 60, threshold=1e-3, check_every=4)
+    assert s["n_iters"] == int(z["sym_early_iters"]) < 62
     assert rel_err(s["f"], z["sym_early_f"]) < 3e-5 and rel_err(s["g"], z["sym_early_g"]) < 3e-5
-    w = O.solve_symmetric(x, y, a, b, [0.5] * 3, last_extrapolation=False,
+    w = O.solve_symmetric(x, y, a, b, [5.0] * 3, last_extrapolation=False,
                           f_init=z["sym_early_f"].astype(F64), g_init=z["sym_early_g"].astype(F64))
     assert rel_err(w["f"], z["sym_warm_f"]) < 3e-5 and rel_err(w["g"], z["sym_warm_g"]) < 3e-5
 
@@ -84,9 +84,9 @@ def test_alternating_solver(conv, rho):
 
 def test_alternating_early_stop():
     z = load_golden("solvers_small")
-    x, y, a, b = d64(z, "x", "y", "a", "b")
-    s = O.solve_alternating(x, y, a, b, [0.4], 80, threshold=1e-4, check_every=3)
-    assert s["n_iters"] == int(z["alt_early_iters"])
+    x, y, a, b = d64(z, "x", "y", "a", "b_normalised")
+    s = O.solve_alternating(x, y, a, b, [5.0], 80, threshold=1e-4, check_every=3)
+    assert s["n_iters"] == int(z["alt_early_iters"]) < 80
     assert rel_err(s["f"], z["alt_early_f"]) < 3e-5
 
 
