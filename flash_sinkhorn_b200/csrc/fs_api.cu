@@ -262,6 +262,8 @@ int fs_version(void) { return 100; }
 
 long long fs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int fs_device_error(void) { return tc::read_error_flag(); }
+
 const char* fs_last_error(void) { return g_err; }
 
 int fs_device_arch(void) {

@@ -1,7 +1,583 @@
+// tcgen05 / TMEM / TMA streaming log-sum-exp engine for sm_100a.
+//
+// One CTA owns BM = 128*NHALF rows of the "row" cloud. Its row operand (K-padded, with
+// constant ones in the bias columns) is loaded once by TMA and stays resident in shared
+// memory; column tiles of BN rows of the "column" cloud stream through an NSTAGE ring of
+// TMA-filled buffers. Warp roles (FlashAttention-style specialisation):
+//   warp 0      : TMA producer (one elected lane)
+//   warp 1      : tcgen05.mma issuer (one elected lane); owns the TMEM allocation
+//   warps 2,3   : idle
+//   warps 4..   : one soft-max warpgroup per 128-row half; thread t of a warpgroup owns
+//                 score row t (TMEM lane t), so row max / row sum need no shuffles.
+// Per column tile and half the MMA warp accumulates S = A_half x B_tile^T (M=128, N=BN,
+// K=8 per instruction, kind::tf32) into one of two TMEM buffers of that half, commits to
+// an mbarrier, and the warpgroup drains the other buffer with tcgen05.ld meanwhile.
+// Because the bias sits in the contraction, the drained value is (logit / scale): the
+// warpgroup does max -> one FFMA + one ex2.approx + one FADD per entry.
+//
+// Every wait on an mbarrier is bounded (clock64 budget); a wait that runs out raises a
+// CTA-wide abort flag, the CTA drains its outstanding copies and MMAs (bounded again),
+// frees its TMEM and returns; a device-global error word records the event.
 #include "fs_tc.cuh"
-namespace fs { namespace tc {
-bool supported(int, int, int, int) { return false; }
-size_t staged_bytes(int, int, int, int) { return 0; }
-cudaError_t stage(Staged&, char*, const float*, const float*, int, int, int, int, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t lse(const Staged&, int, const StreamArgs&, const LseEpilogue&, cudaStream_t) { return cudaErrorNotSupported; }
-}}
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+namespace fs {
+namespace tc {
+
+__device__ int g_tc_error = 0;  // non-zero once any bounded wait gave up (read by fs_device_error)
+
+namespace {
+
+constexpr float kMaskBias = -1.2676506e30f;  // -2^100: bias of padded columns (finite: survives the MMA)
+constexpr float kRunInit = -1.0e30f;         // initial running max (above the mask, below any real logit)
+constexpr long long kSpinLimit = 1ll << 32;  // ~2 s of SM cycles per wait
+constexpr int kSmemMin = 120 * 1024;         // force one CTA per SM (TMEM is allocated per CTA)
+constexpr int kSmemMax = 227 * 1024;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and raises *abort_flag) if the budget runs out or another
+// thread of the CTA already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kSpinLimit) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+// Teardown wait: bounded, ignores the abort flag (used to let in-flight copies / MMAs land).
+__device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kSpinLimit) return;
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] x B[smem desc]^T, M=128, N from idesc, K=8 (tf32)
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// Shared-memory matrix descriptor, K-major operand (PTX "tcgen05 matrix descriptor"):
+//   [0,14) start address >> 4, [16,30) leading byte offset >> 4 (unused for swizzled K-major: 1),
+//   [32,46) stride byte offset >> 4 (distance between 8-row groups), [46,48) version = 1,
+//   [61,64) layout: 2 = 128-byte swizzle, 6 = 32-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t sbo_bytes, uint32_t layout) {
+  uint32_t lo = ((saddr & 0x3FFFFu) >> 4) | (1u << 16);
+  uint32_t hi = (sbo_bytes >> 4) | (1u << 14) | (layout << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+
+// Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major, M=128:
+//   [4,6) D format = 1 (f32), [7,10) A format = 2 (tf32), [10,13) B format = 2 (tf32),
+//   [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+struct KernelParams {
+  int nr, nc;        // valid rows / columns
+  int ntiles;        // column tiles of BN
+  int nfull, ntail;  // K blocks: nfull of 32 floats (128B swizzle) + ntail of 8 floats (32B swizzle)
+  int nstage;
+  float scale2;      // 2*cs*log2e/eps: logit = scale2 * S
+  float eps;
+  LseEpilogue ep;
+};
+
+template <int NHALF, int BN>
+__global__ void __launch_bounds__(128 + 128 * NHALF, 1)
+tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constant__ CUtensorMap mapA_tail,
+              const __grid_constant__ CUtensorMap mapB_full, const __grid_constant__ CUtensorMap mapB_tail,
+              const KernelParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = blockIdx.x * (128 * NHALF);
+
+  if (p.ep.ctrl && p.ep.ctrl->converged) {  // solve already stopped: identity step
+    if (p.ep.old && p.ep.out)
+      for (int r = tid; r < 128 * NHALF; r += blockDim.x)
+        if (row0 + r < p.nr) p.ep.out[row0 + r] = p.ep.old[row0 + r];
+    return;
+  }
+
+  // ---- shared memory carve-up (all operand blocks 1024-byte aligned) ----
+  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t a_half_bytes = p.nfull * (128 * 128) + p.ntail * (128 * 32);
+  const uint32_t b_stage_bytes = p.nfull * (BN * 128) + p.ntail * (BN * 32);
+  uint8_t* a_smem = base;
+  uint8_t* b_smem = a_smem + NHALF * a_half_bytes;
+  uint64_t* bars = (uint64_t*)(b_smem + p.nstage * b_stage_bytes);
+  // barrier indices
+  const int B_FULL = 0, B_EMPTY = p.nstage, S_FULL = 2 * p.nstage, S_EMPTY = S_FULL + 2 * NHALF,
+            A_FULL = S_EMPTY + 2 * NHALF, DRAIN = A_FULL + 1, NBARS = DRAIN + 1;
+  uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  constexpr uint32_t kTmemCols = (2 * NHALF * BN) < 32 ? 32 : (2 * NHALF * BN);
+
+  if (tid == 0) {
+    for (int s = 0; s < p.nstage; ++s) {
+      mbar_init(bar(B_FULL + s), 1);
+      mbar_init(bar(B_EMPTY + s), 1);
+    }
+    for (int i = 0; i < 2 * NHALF; ++i) {
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(S_EMPTY + i), 4);  // one arrive per warp of the warpgroup
+    }
+    mbar_init(bar(A_FULL), 1);
+    mbar_init(bar(DRAIN), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      mbar_expect_tx(bar(A_FULL), NHALF * a_half_bytes);
+#pragma unroll 1
+      for (int h = 0; h < NHALF; ++h) {
+        uint32_t dst = smem_u32(a_smem + h * a_half_bytes);
+        for (int kb = 0; kb < p.nfull; ++kb)
+          tma_load_2d(dst + kb * (128 * 128), &mapA_full, kb * 32, row0 + h * 128, bar(A_FULL));
+        for (int t = 0; t < p.ntail; ++t)
+          tma_load_2d(dst + p.nfull * (128 * 128) + t * (128 * 32), &mapA_tail, p.nfull * 32 + t * 8,
+                      row0 + h * 128, bar(A_FULL));
+      }
+      int issued = 0;
+#pragma unroll 1
+      for (int j = 0; j < p.ntiles; ++j) {
+        const int s = j % p.nstage;
+        const uint32_t ph = (j / p.nstage) & 1;
+        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(B_FULL + s), b_stage_bytes);
+        uint32_t dst = smem_u32(b_smem + s * b_stage_bytes);
+        for (int kb = 0; kb < p.nfull; ++kb)
+          tma_load_2d(dst + kb * (BN * 128), &mapB_full, kb * 32, j * BN, bar(B_FULL + s));
+        for (int t = 0; t < p.ntail; ++t)
+          tma_load_2d(dst + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, j * BN,
+                      bar(B_FULL + s));
+        issued = j + 1;
+      }
+      if (*abort_flag) {  // let every copy we issued land before the CTA goes away
+        mbar_wait_quiet(bar(A_FULL), 0);
+        for (int j = (issued > p.nstage ? issued - p.nstage : 0); j < issued; ++j)
+          mbar_wait_quiet(bar(B_FULL + j % p.nstage), (j / p.nstage) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag);
+      tc_fence_after();
+#pragma unroll 1
+      for (int j = 0; ok && j < p.ntiles; ++j) {
+        const int s = j % p.nstage;
+        const uint32_t ph = (j / p.nstage) & 1;
+        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t b_addr = smem_u32(b_smem + s * b_stage_bytes);
+        const int buf = j & 1;
+        const uint32_t sph = (j >> 1) & 1;
+#pragma unroll 1
+        for (int h = 0; h < NHALF; ++h) {
+          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(a_smem + h * a_half_bytes);
+          const uint32_t d_tmem = tmem_base + (uint32_t)((h * 2 + buf) * BN);
+          uint32_t acc = 0;
+          for (int kb = 0; kb < p.nfull; ++kb) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              uint64_t ad = make_desc(a_addr + kb * (128 * 128) + ks * 32, 1024, 2);
+              uint64_t bd = make_desc(b_addr + kb * (BN * 128) + ks * 32, 1024, 2);
+              umma_tf32(d_tmem, ad, bd, idesc, acc);
+              acc = 1;
+            }
+          }
+          for (int t = 0; t < p.ntail; ++t) {
+            uint64_t ad = make_desc(a_addr + p.nfull * (128 * 128) + t * (128 * 32), 256, 6);
+            uint64_t bd = make_desc(b_addr + p.nfull * (BN * 128) + t * (BN * 32), 256, 6);
+            umma_tf32(d_tmem, ad, bd, idesc, acc);
+            acc = 1;
+          }
+          umma_commit(bar(S_FULL + h * 2 + buf));
+        }
+        if (!ok) break;
+        umma_commit(bar(B_EMPTY + s));
+      }
+      if (*abort_flag) {  // wait (bounded) for every MMA issued so far before TMEM is freed
+        umma_commit(bar(DRAIN));
+        mbar_wait_quiet(bar(DRAIN), 0);
+      }
+    }
+  } else if (warp >= 4) {
+    // ===================== soft-max warpgroups =====================
+    const int h = (warp - 4) >> 2;
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const float scale = p.scale2;
+    float m_run = kRunInit, s_run = 0.f;
+    bool ok = true;
+#pragma unroll 1
+    for (int j = 0; j < p.ntiles; ++j) {
+      const int buf = j & 1;
+      const uint32_t sph = (j >> 1) & 1;
+      if (!mbar_wait(bar(S_FULL + h * 2 + buf), sph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = lane_addr + (uint32_t)((h * 2 + buf) * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        tmem_ld32(taddr + c * 32, v);
+        if (c == BN / 32 - 1) {  // buffer fully read: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(S_EMPTY + h * 2 + buf));
+        }
+        float t[11];
+#pragma unroll
+        for (int i = 0; i < 10; ++i) t[i] = max3(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+        t[10] = fmaxf(v[30], v[31]);
+        float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
+        float cm = fmaxf(max3(u0, u1, u2), fmaxf(t[9], t[10]));
+        const float m_new = fmaxf(m_run, cm);
+        const float nms = -scale * m_new;
+        float s0 = s_run * ex2(fmaf(m_run, scale, nms)), s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          s0 += ex2(fmaf(v[i], scale, nms));
+          s1 += ex2(fmaf(v[i + 1], scale, nms));
+          s2 += ex2(fmaf(v[i + 2], scale, nms));
+          s3 += ex2(fmaf(v[i + 3], scale, nms));
+        }
+        s_run = (s0 + s1) + (s2 + s3);
+        m_run = m_new;
+      }
+    }
+    const int r = row0 + h * 128 + q * 32 + lane;
+    if (ok && r < p.nr) {
+      const LseEpilogue& ep = p.ep;
+      float lse2 = fmaf(m_run, scale, log2f(fmaxf(s_run, 1e-40f)));
+      if (ep.lse2) ep.lse2[r] = lse2;
+      if (ep.out) {
+        float cand = -p.eps * ep.damping * (lse2 * kLn2);
+        float o = ep.w * cand;
+        if (ep.old) o += (1.0f - ep.w) * ep.old[r];
+        if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
+        if (ep.addvec) o += ep.addcoef * ep.addvec[r];
+        ep.out[r] = o;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (tid == 0 && *abort_flag) atomicExch(&g_tc_error, 1);
+}
+
+// ------------------------------------------------------------------ staging kernels
+// opA/opB for one cloud. Column layout (kp floats per row):
+//   TF32 mode : [ x (d) | aug (3) | 0 ... ]                       A-role aug = 1,1,1 ; B-role aug = bias split
+//   FP32 mode : A-role [ xh (d) | xh (d) | xl (d) | aug | 0 ...]   B-role [ yh | yl | yh | aug | 0 ... ]
+// so that sum_k A_k B_k = xh.yh + xh.yl + xl.yh + bias  (the dropped xl.yl term is ~2^-22 relative).
+__global__ void stage_kernel(const float* __restrict__ src, int rows, int rows_pad, int d, int kc, int kp, int prec,
+                             float* __restrict__ opA, float* __restrict__ opB) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t total = (size_t)rows_pad * kp;
+  if (idx >= total) return;
+  int r = (int)(idx / kp), k = (int)(idx % kp);
+  float va = 0.f, vb = 0.f;
+  if (k < kc) {
+    if (r < rows) {
+      int part = k / d, c = k % d;
+      float x = src[(size_t)r * d + c];
+      float hi = to_tf32(x);
+      float lo = to_tf32(x - hi);
+      if (prec == 0) { va = hi; vb = hi; }
+      else { va = (part == 2) ? lo : hi; vb = (part == 1) ? lo : hi; }
+    }
+  } else if (k < kc + 3) {
+    va = 1.f;
+    vb = (k == kc && r >= rows) ? kMaskBias : 0.f;  // padded rows are masked for good
+  }
+  opA[idx] = va;
+  opB[idx] = vb;
+}
+
+// Writes the bias of a pass, divided by the logit scale and split into 3 TF32 pieces, into opB's aug columns.
+__global__ void bias_kernel(float* __restrict__ opB, int rows, int kc, int kp, const float* __restrict__ pot,
+                            const float* __restrict__ logw, float inv_eps, float inv_scale2, const Ctrl* ctrl) {
+  if (ctrl && ctrl->converged) return;
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  // bias in log2 units, same association as the reference kernels, then / scale2
+  float b2 = logw ? (pot[r] * (inv_eps * kLog2e) + logw[r] * kLog2e) : pot[r] * kLog2e;
+  float b = b2 * inv_scale2;
+  float hi = to_tf32(b);
+  float r1 = b - hi;
+  float mid = to_tf32(r1);
+  float lo = to_tf32(r1 - mid);
+  float* row = opB + (size_t)r * kp + kc;
+  row[0] = hi; row[1] = mid; row[2] = lo;
+}
+
+// ------------------------------------------------------------------ host side
+PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+  });
+  return fn;
+}
+
+// 2-D fp32 tensor [rows, kp] (kp contiguous), box = [box_k floats, box_rows rows].
+bool encode_map(CUtensorMap* map, const float* base, int rows, int kp, int box_k, int box_rows,
+                CUtensorMapSwizzle swz) {
+  auto enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)kp * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)box_k, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct Shape {
+  int kc, kp, nfull, ntail, nhalf, bn, nstage;
+  size_t smem;
+  bool ok;
+};
+
+Shape plan_shape(int d, int prec) {
+  Shape s{};
+  s.kc = (prec == 0) ? d : 3 * d;
+  s.kp = (s.kc + 3 + 7) & ~7;
+  s.nfull = s.kp / 32;
+  s.ntail = (s.kp % 32) / 8;
+  const size_t row_bytes = (size_t)s.kp * 4;
+  const size_t budget = kSmemMax - 2048;  // barriers + alignment slack
+  s.ok = false;
+  const int cand[3][2] = {{2, 128}, {1, 128}, {1, 64}};
+  for (auto& c : cand) {
+    size_t a = (size_t)c[0] * 128 * row_bytes, b = (size_t)c[1] * row_bytes;
+    if (a + 2 * b > budget) continue;
+    int ns = (int)((budget - a) / b);
+    if (ns > 4) ns = 4;
+    s.nhalf = c[0]; s.bn = c[1]; s.nstage = ns;
+    s.smem = a + ns * b + 2048;
+    if (s.smem < (size_t)kSmemMin) s.smem = kSmemMin;
+    s.ok = true;
+    break;
+  }
+  return s;
+}
+
+template <int NHALF, int BN>
+cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUtensorMap& mb_f,
+                   const CUtensorMap& mb_t, const KernelParams& kp, int grid, size_t smem, cudaStream_t st) {
+  auto kern = tc_lse_kernel<NHALF, BN>;
+  // Per device (context) attribute; cheap enough to set on every launch.
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, 128 + 128 * NHALF, smem, st>>>(ma_f, ma_t, mb_f, mb_t, kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool supported(int n, int m, int d, int prec) {
+  if (prec != 0 && prec != 1) return false;
+  if (n <= 0 || m <= 0 || d <= 0) return false;
+  return plan_shape(d, prec).ok;
+}
+
+static inline int pad256(int r) { return (r + 255) & ~255; }
+
+size_t staged_bytes(int n, int m, int d, int prec) {
+  Shape s = plan_shape(d, prec);
+  if (!s.ok) return 0;
+  size_t per_row = (size_t)s.kp * sizeof(float);
+  size_t b = 0;
+  b += 2 * (((size_t)pad256(n) * per_row + 1023) & ~size_t(1023));
+  b += 2 * (((size_t)pad256(m) * per_row + 1023) & ~size_t(1023));
+  return b + 1024;
+}
+
+cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
+                  cudaStream_t st) {
+  Shape sh = plan_shape(d, prec);
+  if (!sh.ok) return cudaErrorNotSupported;
+  s.d = d; s.kc = sh.kc; s.kp = sh.kp; s.prec = prec;
+  char* p = (char*)(((uintptr_t)buf + 1023) & ~(uintptr_t)1023);
+  const float* src[2] = {x, y};
+  const int rows[2] = {n, m};
+  for (int c = 0; c < 2; ++c) {
+    CloudOps& o = s.cloud[c];
+    o.rows = rows[c];
+    o.rows_pad = pad256(rows[c]);
+    size_t bytes = (((size_t)o.rows_pad * sh.kp * sizeof(float)) + 1023) & ~size_t(1023);
+    o.opA = reinterpret_cast<float*>(p); p += bytes;
+    o.opB = reinterpret_cast<float*>(p); p += bytes;
+    size_t total = (size_t)o.rows_pad * sh.kp;
+    stage_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src[c], o.rows, o.rows_pad, d, sh.kc, sh.kp, prec,
+                                                                  o.opA, o.opB);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st) {
+  Shape sh = plan_shape(s.d, s.prec);
+  if (!sh.ok) return cudaErrorNotSupported;
+  const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
+  const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
+  const float scale2 = (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;
+  bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, sh.kc, sh.kp, a.pot, a.logw,
+                                                       1.0f / a.eps, 1.0f / scale2, e.ctrl);
+  CUtensorMap ma_f, ma_t, mb_f, mb_t;
+  // A tensor map boxes are 128 rows; B boxes BN rows. When a K-block class is absent its map
+  // still has to be a valid object: encode it over the first columns (never used by the kernel).
+  bool ok = true;
+  ok &= encode_map(&ma_f, rowc.opA, rowc.rows_pad, sh.kp, sh.nfull ? 32 : 8, 128,
+                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&ma_t, rowc.opA, rowc.rows_pad, sh.kp, 8, 128, CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&mb_f, colc.opB, colc.rows_pad, sh.kp, sh.nfull ? 32 : 8, sh.bn,
+                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&mb_t, colc.opB, colc.rows_pad, sh.kp, 8, sh.bn, CU_TENSOR_MAP_SWIZZLE_32B);
+  if (!ok) return cudaErrorInvalidValue;
+  KernelParams kp;
+  kp.nr = a.nr; kp.nc = a.nc;
+  kp.ntiles = (a.nc + sh.bn - 1) / sh.bn;
+  kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nstage = sh.nstage;
+  kp.scale2 = scale2; kp.eps = a.eps; kp.ep = e;
+  const int bm = 128 * sh.nhalf;
+  const int grid = (a.nr + bm - 1) / bm;
+  if (sh.nhalf == 2) return launch<2, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  if (sh.bn == 128) return launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  return launch<1, 64>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+}
+
+int read_error_flag() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace tc
+}  // namespace fs

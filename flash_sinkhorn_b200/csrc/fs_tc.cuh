@@ -30,5 +30,8 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
 // One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st);
 
+// Value of the device-global error word (non-zero once a bounded wait gave up); synchronises.
+int read_error_flag();
+
 }  // namespace tc
 }  // namespace fs

@@ -72,6 +72,11 @@ int fs_device_arch(void);
  * verify that its work ran on the GPU path: difference two readings around a call. */
 long long fs_launch_count(void);
 
+/* Device-side health word of the current device: 0 = fine, 1 = some kernel of this
+ * library gave up a bounded wait (its outputs are then invalid), negative = CUDA error
+ * while reading it. SYNCHRONISES the device; meant for tests and post-mortems. */
+int fs_device_error(void);
+
 /* Scratch bytes needed by `op` (one of FS_OP_*) at these sizes. */
 size_t fs_workspace_bytes(int op, int n, int m, int d, int prec);
 
