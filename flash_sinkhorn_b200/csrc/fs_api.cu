@@ -191,8 +191,13 @@ struct Problem {
   cudaError_t pv(int side, const float* pot, const float* logw, float eps, const PvArgs& p) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
     g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (use_tc && !p.rows2 && !s.tile_row_ptr && pv_scratch && tc::pv_supported(d, prec, p.dv) &&
+        tc::pv_scratch_bytes(s.nc, d, prec, p.dv) <= pv_scratch_bytes)
+      return tc::pv(staged, side, s, p, pv_scratch, st);
     return simt_pv(s, p, st);
   }
+  char* pv_scratch = nullptr;  // transposed copy of V for the tensor-core matrix pass
+  size_t pv_scratch_bytes = 0;
 };
 
 int check_common(const void* x, const void* y, int n, int m, int d, float eps, float cost_scale, int prec) {
@@ -215,7 +220,7 @@ int check_device() {
 // Sets up `p` (engine choice + staged tcgen05 operands carved from ws).
 // `lse_only` is true for ops that only run LSE passes.
 int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int m, int d, float cs, int prec,
-                 cudaStream_t st, bool measure_only) {
+                 cudaStream_t st, bool measure_only, int pv_dv = 0) {
   p.x = x; p.y = y; p.n = n; p.m = m; p.d = d; p.cs = cs; p.prec = prec; p.st = st;
   p.use_tc = (prec != FS_PREC_SIMT) && tc::supported(n, m, d, prec);
   if (p.use_tc) {
@@ -225,6 +230,11 @@ int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int 
       if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
       cudaError_t e = tc::stage(p.staged, buf, x, y, n, m, d, prec, st);
       if (e != cudaSuccess) return fail(FS_ERR_CUDA, "staging tcgen05 operands failed: %s", cudaGetErrorString(e));
+    }
+    if (pv_dv > 0 && tc::pv_supported(d, prec, pv_dv)) {
+      p.pv_scratch_bytes = tc::pv_scratch_bytes(n > m ? n : m, d, prec, pv_dv);
+      p.pv_scratch = ws.take<char>(p.pv_scratch_bytes);
+      if (!measure_only && ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
     }
   }
   return FS_OK;
@@ -279,7 +289,8 @@ size_t fs_workspace_bytes(int op, int n, int m, int d, int prec) {
   if (n <= 0 || m <= 0 || d <= 0) return 0;
   Ws ws(nullptr, 0);
   Problem p;
-  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true);
+  const bool matrix_op = (op == FS_OP_APPLY_MAT || op == FS_OP_GRAD);
+  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true, matrix_op ? d : 0);
   size_t nm = (size_t)(n > m ? n : m);
   switch (op) {
     case FS_OP_LSE:
@@ -545,7 +556,7 @@ int fs_apply_mat(const float* x, const float* y, int n, int m, int d, const floa
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, dv <= d ? dv : 0));
   const int side = axis == 1 ? 0 : 1;
   const int nr = side == 0 ? n : m;
   float* R = ws.take<float>(n > m ? n : m);
@@ -575,7 +586,9 @@ int fs_grad(const float* x, const float* y, int n, int m, int d, const float* a,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, d));
+  // The normaliser R and the weights must come from the same engine (bit-identical scores).
+  if (p.use_tc && !p.pv_scratch) p.use_tc = false;
   float* fh = ws.take<float>(n);
   float* gh = ws.take<float>(m);
   float* Rn = ws.take<float>(n);

@@ -35,7 +35,7 @@ namespace {
 
 constexpr float kMaskBias = -1.2676506e30f;  // -2^100: bias of padded columns (finite: survives the MMA)
 constexpr float kRunInit = -1.0e30f;         // initial running max (above the mask, below any real logit)
-constexpr long long kSpinLimit = 1ll << 32;  // ~2 s of SM cycles per wait
+constexpr long long kSpinLimit = 1ll << 28;  // ~0.14 s of SM cycles per wait (a tile takes microseconds)
 constexpr int kSmemMin = 120 * 1024;         // force one CTA per SM (TMEM is allocated per CTA)
 constexpr int kSmemMax = 227 * 1024;
 
@@ -327,6 +327,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       const int buf = j & 1;
       const uint32_t sph = (j >> 1) & 1;
       if (!mbar_wait(bar(S_FULL + h * 2 + buf), sph, abort_flag)) { ok = false; break; }
+      __syncwarp();  // lanes leave the poll loop at different times; tcgen05.ld below is .sync.aligned
       tc_fence_after();
       const uint32_t taddr = lane_addr + (uint32_t)((h * 2 + buf) * BN);
 #pragma unroll 1
@@ -382,6 +383,312 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (tid == 0 && *abort_flag) atomicExch(&g_tc_error, 1);
+}
+
+// ------------------------------------------------------------------ plan-times-matrix kernel
+// out = epilogue( sum_j 2^(logit_ij - R_i) * V_j ) with a known per-row offset R (the exact
+// log2-normaliser from an LSE pass over the SAME staged operands, so the scores are
+// bit-identical to the ones the potentials were fitted to). FlashAttention-style second GEMM:
+//   MMA1 : S = A x B_tile^T           -> TMEM buffer (as in the LSE kernel)
+//   warpgroup: W = 2^(scale*S - R), rounded to TF32, stored back over S with tcgen05.st
+//   MMA2 : O += W x Vt_tile^T         (A operand from TMEM, B = V^T tile, K-major, in smem)
+// No running max and no rescaling of O: R makes every W <= ~1. In SPLIT mode (exact fp32)
+// W = Wh + Wl and V = Vh + Vl and MMA2 is issued three times (Wh.Vh + Wl.Vh + Wh.Vl).
+// One CTA = 128 rows; TMEM columns: [0, 2*WCOLS) two S/W buffers, then DV_PAD columns of O.
+struct PvKernelParams {
+  int nr, nc, ntiles, nfull, ntail, nstage;
+  int dv, dv_pad, dv0;   // real width, padded slice width (multiple of 32, <= 256), first column of this slice
+  int ld_out;            // row pitch of out (= full dv of the problem)
+  float scale2, eps;
+  const float* R;
+  int epilogue;          // PvEpilogue
+  const float* rowpot; const float* rowlogw; const float* roww; const float* gs; float coef;
+  const float* rows_raw; int ld_rows;   // original row cloud (GRAD epilogue: x_i - O_i)
+  float* out;
+};
+
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+
+template <int BN, bool SPLIT>
+__global__ void __launch_bounds__(256, 1)
+tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constant__ CUtensorMap mapA_tail,
+             const __grid_constant__ CUtensorMap mapB_full, const __grid_constant__ CUtensorMap mapB_tail,
+             const __grid_constant__ CUtensorMap mapV_hi, const __grid_constant__ CUtensorMap mapV_lo,
+             const PvKernelParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = blockIdx.x * 128;
+  constexpr int WCOLS = SPLIT ? 2 * BN : BN;  // TMEM columns per S/W buffer (Wl lives right after Wh)
+  constexpr int NV = SPLIT ? 2 : 1;
+
+  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t a_bytes = p.nfull * (128 * 128) + p.ntail * (128 * 32);
+  const uint32_t b_bytes = p.nfull * (BN * 128) + p.ntail * (BN * 32);
+  const uint32_t v_blk = (uint32_t)p.dv_pad * 128;        // one 32-column K block of V^T: dv_pad rows x 128 B
+  const uint32_t v_bytes = (BN / 32) * v_blk;             // per hi/lo part
+  const uint32_t stage_bytes = b_bytes + NV * v_bytes;
+  uint8_t* a_smem = base;
+  uint8_t* st_smem = a_smem + a_bytes;
+  uint64_t* bars = (uint64_t*)(st_smem + p.nstage * stage_bytes);
+  const int B_FULL = 0, B_EMPTY = p.nstage, S_FULL = 2 * p.nstage, W_FULL = S_FULL + 2, A_FULL = W_FULL + 2,
+            O_FULL = A_FULL + 1, NBARS = O_FULL + 1;
+  uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+  constexpr uint32_t kTmemCols = 512;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.nstage; ++s) {
+      mbar_init(bar(B_FULL + s), 1);
+      mbar_init(bar(B_EMPTY + s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(W_FULL + i), 4);
+    }
+    mbar_init(bar(A_FULL), 1);
+    mbar_init(bar(O_FULL), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t o_tmem = tmem_base + 2 * WCOLS;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(A_FULL), a_bytes);
+      uint32_t dst = smem_u32(a_smem);
+      for (int kb = 0; kb < p.nfull; ++kb) tma_load_2d(dst + kb * (128 * 128), &mapA_full, kb * 32, row0, bar(A_FULL));
+      for (int t = 0; t < p.ntail; ++t)
+        tma_load_2d(dst + p.nfull * (128 * 128) + t * (128 * 32), &mapA_tail, p.nfull * 32 + t * 8, row0, bar(A_FULL));
+      int issued = 0;
+#pragma unroll 1
+      for (int j = 0; j < p.ntiles; ++j) {
+        const int s = j % p.nstage;
+        const uint32_t ph = (j / p.nstage) & 1;
+        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(B_FULL + s), stage_bytes);
+        uint32_t d0 = smem_u32(st_smem + s * stage_bytes);
+        for (int kb = 0; kb < p.nfull; ++kb)
+          tma_load_2d(d0 + kb * (BN * 128), &mapB_full, kb * 32, j * BN, bar(B_FULL + s));
+        for (int t = 0; t < p.ntail; ++t)
+          tma_load_2d(d0 + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, j * BN,
+                      bar(B_FULL + s));
+        uint32_t dv_dst = d0 + b_bytes;
+        for (int kb = 0; kb < BN / 32; ++kb) {
+          tma_load_2d(dv_dst + kb * v_blk, &mapV_hi, j * BN + kb * 32, p.dv0, bar(B_FULL + s));
+          if (SPLIT) tma_load_2d(dv_dst + v_bytes + kb * v_blk, &mapV_lo, j * BN + kb * 32, p.dv0, bar(B_FULL + s));
+        }
+        issued = j + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait_quiet(bar(A_FULL), 0);
+        for (int j = (issued > p.nstage ? issued - p.nstage : 0); j < issued; ++j)
+          mbar_wait_quiet(bar(B_FULL + j % p.nstage), (j / p.nstage) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc1 = make_idesc(BN);
+      const uint32_t idesc2 = make_idesc(p.dv_pad);
+      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag);
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(a_smem);
+      uint32_t o_acc = 0;
+      // Second GEMM of tile jj (its W is ready when the warpgroup says so); frees the stage afterwards.
+      auto mma2 = [&](int jj) -> bool {
+        const int s = jj % p.nstage;
+        const int buf = jj & 1;
+        if (!mbar_wait(bar(W_FULL + buf), (jj >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t w_tmem = tmem_base + buf * WCOLS;
+        const uint32_t v_addr = smem_u32(st_smem + s * stage_bytes) + b_bytes;
+#pragma unroll 1
+        for (int part = 0; part < (SPLIT ? 3 : 1); ++part) {
+          // part 0: Wh.Vh   part 1: Wl.Vh   part 2: Wh.Vl
+          const uint32_t wa = w_tmem + ((part == 1) ? BN : 0);
+          const uint32_t va = v_addr + ((part == 2) ? v_bytes : 0);
+          for (int kb = 0; kb < BN / 32; ++kb) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              uint64_t bd = make_desc(va + kb * v_blk + ks * 32, 1024, 2);
+              umma_tf32_ts(o_tmem, wa + kb * 32 + ks * 8, bd, idesc2, o_acc);
+              o_acc = 1;
+            }
+          }
+        }
+        umma_commit(bar(B_EMPTY + s));
+        return true;
+      };
+#pragma unroll 1
+      for (int j = 0; ok && j < p.ntiles; ++j) {
+        const int s = j % p.nstage;
+        const uint32_t ph = (j / p.nstage) & 1;
+        // With a single stage the previous tile's second GEMM must retire before its buffers are refilled.
+        if (p.nstage == 1 && j > 0) { if (!mma2(j - 1)) { ok = false; break; } }
+        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t b_addr = smem_u32(st_smem + s * stage_bytes);
+        const uint32_t d_tmem = tmem_base + (j & 1) * WCOLS;
+        // The S/W buffer (j&1) was last read by MMA2(j-2), issued earlier by this same thread: in order.
+        uint32_t acc = 0;
+        for (int kb = 0; kb < p.nfull; ++kb) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            umma_tf32(d_tmem, make_desc(a_addr + kb * (128 * 128) + ks * 32, 1024, 2),
+                      make_desc(b_addr + kb * (BN * 128) + ks * 32, 1024, 2), idesc1, acc);
+            acc = 1;
+          }
+        }
+        for (int t = 0; t < p.ntail; ++t) {
+          umma_tf32(d_tmem, make_desc(a_addr + p.nfull * (128 * 128) + t * (128 * 32), 256, 6),
+                    make_desc(b_addr + p.nfull * (BN * 128) + t * (BN * 32), 256, 6), idesc1, acc);
+          acc = 1;
+        }
+        umma_commit(bar(S_FULL + (j & 1)));
+        if (p.nstage > 1 && j > 0) { if (!mma2(j - 1)) { ok = false; break; } }
+      }
+      if (ok) ok = mma2(p.ntiles - 1);
+      umma_commit(bar(O_FULL));
+      if (*abort_flag) mbar_wait_quiet(bar(O_FULL), 0);
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int r = row0 + q * 32 + lane;
+    const float scale = p.scale2;
+    const float negR = (r < p.nr) ? -p.R[r] : 0.f;
+    bool ok = true;
+#pragma unroll 1
+    for (int j = 0; j < p.ntiles; ++j) {
+      const int buf = j & 1;
+      if (!mbar_wait(bar(S_FULL + buf), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      const uint32_t taddr = lane_addr + buf * WCOLS;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        tmem_ld32(taddr + c * 32, v);
+        if (SPLIT) {
+          float lo[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float w = ex2(fmaf(v[i], scale, negR));
+            float hi = to_tf32(w);
+            lo[i] = to_tf32(w - hi);
+            v[i] = hi;
+          }
+          tmem_st32(taddr + BN + c * 32, lo);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = to_tf32(ex2(fmaf(v[i], scale, negR)));
+        }
+        tmem_st32(taddr + c * 32, v);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(W_FULL + buf));
+    }
+    if (ok) ok = mbar_wait(bar(O_FULL), 0, abort_flag);
+    __syncwarp();
+    tc_fence_after();
+    // `ok` is warp-uniform (every lane polls the same barrier). tcgen05.ld is .sync.aligned: all 32
+    // lanes must execute it together, so rows beyond nr load too and only their stores are masked.
+    if (ok) {
+      const bool valid = r < p.nr;
+      const int rr = valid ? r : 0;
+      const float inv_eps = 1.0f / p.eps;
+      float fac;
+      if (p.epilogue == PV_GRAD) {
+        fac = p.coef * (p.gs ? __ldg(p.gs) : 1.f) * __ldg(p.roww + rr);
+      } else {
+        float rt = (__ldg(p.rowpot + rr) * inv_eps + (p.rowlogw ? __ldg(p.rowlogw + rr) : 0.f)) * kLog2e;
+        fac = p.coef * ex2(rt - negR);
+      }
+      float* orow = p.out + (size_t)rr * p.ld_out + p.dv0;
+#pragma unroll 1
+      for (int c = 0; c < p.dv_pad / 32; ++c) {
+        float o[32];
+        tmem_ld32(lane_addr + 2 * WCOLS + c * 32, o);
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            int col = c * 32 + i;
+            if (p.dv0 + col < p.dv) {
+              float val = o[i];
+              if (p.epilogue == PV_GRAD) val = __ldg(p.rows_raw + (size_t)rr * p.ld_rows + p.dv0 + col) - val;
+              orow[col] = fac * val;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (tid == 0 && *abort_flag) atomicExch(&g_tc_error, 1);
+}
+
+// V^T staging: vt[c][j] = tf32(V[j][c] * colscale_j) (hi) and the tf32 residual (lo), zero padded
+// to [dv_rows_pad, cols_pad]. One thread per output element, reads along j are strided by dv
+// (the matrices involved are O((n+m) d), negligible next to the n*m pass).
+__global__ void stage_vt_kernel(const float* __restrict__ V, int nc, int dv, const float* __restrict__ colscale,
+                                int rows_pad, int cols_pad, float* __restrict__ vt_hi, float* __restrict__ vt_lo) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t total = (size_t)rows_pad * cols_pad;
+  if (idx >= total) return;
+  int c = (int)(idx / cols_pad), j = (int)(idx % cols_pad);
+  float v = 0.f;
+  if (c < dv && j < nc) {
+    v = V[(size_t)j * dv + c];
+    if (colscale) v *= colscale[j];
+  }
+  float hi = to_tf32(v);
+  vt_hi[idx] = hi;
+  if (vt_lo) vt_lo[idx] = to_tf32(v - hi);
 }
 
 // ------------------------------------------------------------------ staging kernels
@@ -571,6 +878,104 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
   if (sh.nhalf == 2) return launch<2, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   if (sh.bn == 128) return launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   return launch<1, 64>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+}
+
+// ---- plan-times-matrix host side ----
+namespace {
+
+struct PvShape {
+  int bn, dv_pad, nslices, nstage, cols_pad_mult;
+  size_t smem;
+  bool split, ok;
+};
+
+PvShape plan_pv(int d, int prec, int dv) {
+  PvShape s{};
+  Shape sh = plan_shape(d, prec);
+  s.ok = false;
+  if (!sh.ok || dv <= 0) return s;
+  s.split = (prec == 1);
+  s.bn = s.split ? 64 : 128;
+  const int w = dv < 256 ? dv : 256;
+  s.dv_pad = (w + 31) & ~31;
+  s.nslices = (dv + 255) / 256;
+  const size_t a = (size_t)128 * sh.kp * 4;
+  const size_t stage = (size_t)s.bn * sh.kp * 4 + (size_t)(s.split ? 2 : 1) * (s.bn / 32) * s.dv_pad * 128;
+  const size_t budget = kSmemMax - 2048;
+  if (a + stage > budget) return s;
+  int ns = (int)((budget - a) / stage);
+  s.nstage = ns > 3 ? 3 : ns;
+  s.smem = a + s.nstage * stage + 2048;
+  if (s.smem < (size_t)kSmemMin) s.smem = kSmemMin;
+  s.ok = true;
+  return s;
+}
+
+template <int BN, bool SPLIT>
+cudaError_t launch_pv(const CUtensorMap* maps, const PvKernelParams& kp, int grid, size_t smem, cudaStream_t st) {
+  auto kern = tc_pv_kernel<BN, SPLIT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, 256, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool pv_supported(int d, int prec, int dv) { return (prec == 0 || prec == 1) && plan_pv(d, prec, dv).ok; }
+
+size_t pv_scratch_bytes(int nc, int d, int prec, int dv) {
+  PvShape s = plan_pv(d, prec, dv);
+  if (!s.ok) return 0;
+  size_t one = (size_t)s.nslices * s.dv_pad * pad256(nc) * sizeof(float);
+  return (s.split ? 2 : 1) * ((one + 1023) & ~size_t(1023)) + 1024;
+}
+
+cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa, char* scratch, cudaStream_t st) {
+  Shape sh = plan_shape(s.d, s.prec);
+  PvShape ps = plan_pv(s.d, s.prec, pa.dv);
+  if (!sh.ok || !ps.ok || pa.rows2) return cudaErrorNotSupported;
+  const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
+  const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
+  const float scale2 = (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;
+  bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, sh.kc, sh.kp, a.pot, a.logw,
+                                                       1.0f / a.eps, 1.0f / scale2, nullptr);
+  // V^T (hi / lo), [nslices*dv_pad, cols_pad]
+  const int vrows = ps.nslices * ps.dv_pad, vcols = colc.rows_pad;
+  char* p = (char*)(((uintptr_t)scratch + 1023) & ~(uintptr_t)1023);
+  float* vt_hi = reinterpret_cast<float*>(p);
+  size_t one = (((size_t)vrows * vcols * sizeof(float)) + 1023) & ~size_t(1023);
+  float* vt_lo = ps.split ? reinterpret_cast<float*>(p + one) : nullptr;
+  size_t total = (size_t)vrows * vcols;
+  stage_vt_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(pa.V, a.nc, pa.dv, pa.colscale, vrows, vcols,
+                                                                   vt_hi, vt_lo);
+  CUtensorMap maps[6];
+  bool ok = true;
+  ok &= encode_map(&maps[0], rowc.opA, rowc.rows_pad, sh.kp, sh.nfull ? 32 : 8, 128,
+                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&maps[1], rowc.opA, rowc.rows_pad, sh.kp, 8, 128, CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&maps[2], colc.opB, colc.rows_pad, sh.kp, sh.nfull ? 32 : 8, ps.bn,
+                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&maps[3], colc.opB, colc.rows_pad, sh.kp, 8, ps.bn, CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&maps[4], vt_hi, vrows, vcols, 32, ps.dv_pad, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok &= encode_map(&maps[5], ps.split ? vt_lo : vt_hi, vrows, vcols, 32, ps.dv_pad, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return cudaErrorInvalidValue;
+  PvKernelParams kp;
+  kp.nr = a.nr; kp.nc = a.nc;
+  kp.ntiles = (a.nc + ps.bn - 1) / ps.bn;
+  kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nstage = ps.nstage;
+  kp.dv = pa.dv; kp.dv_pad = ps.dv_pad; kp.ld_out = pa.dv;
+  kp.scale2 = scale2; kp.eps = a.eps; kp.R = pa.R; kp.epilogue = pa.epilogue;
+  kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.roww = pa.roww; kp.gs = pa.gs; kp.coef = pa.coef;
+  kp.rows_raw = a.rows; kp.ld_rows = a.d; kp.out = pa.out;
+  const int grid = (a.nr + 127) / 128;
+  for (int sl = 0; sl < ps.nslices; ++sl) {
+    kp.dv0 = sl * ps.dv_pad;
+    cudaError_t e = ps.split ? launch_pv<64, true>(maps, kp, grid, ps.smem, st)
+                             : launch_pv<128, false>(maps, kp, grid, ps.smem, st);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 int read_error_flag() {

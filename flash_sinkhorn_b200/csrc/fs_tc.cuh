@@ -30,6 +30,12 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
 // One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st);
 
+// Plan-times-matrix pass on the tensor cores (same staged operands, hence bit-identical scores
+// to the LSE passes). `scratch` holds the transposed, TF32-split copy of V (pv_scratch_bytes).
+bool pv_supported(int d, int prec, int dv);
+size_t pv_scratch_bytes(int nc, int d, int prec, int dv);
+cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, char* scratch, cudaStream_t st);
+
 // Value of the device-global error word (non-zero once a bounded wait gave up); synchronises.
 int read_error_flag();
 
