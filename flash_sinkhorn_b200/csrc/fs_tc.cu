@@ -24,6 +24,7 @@
 #include <cudaTypedefs.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace fs {
@@ -129,9 +130,43 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  // the wait takes r[] as read-write operands: no use of the data can be scheduled above it
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Same load without the wait: the caller overlaps it with arithmetic and calls tmem_ld_wait() before use.
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// Wait for the outstanding TMEM loads. The destination registers are passed through the asm as
+// read-write operands so that no use of them can be scheduled above the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -175,6 +210,12 @@ struct KernelParams {
   float scale2;      // 2*cs*log2e/eps: logit = scale2 * S
   float eps;
   LseEpilogue ep;
+  // Column split: blockIdx.y owns tiles [y*tiles_per_chunk, ...). With gridDim.y > 1 every CTA writes
+  // its partial (scale2*max, sum) pair per row and lse_combine_kernel finishes the update.
+  int tiles_per_chunk;
+  float* part_m;
+  float* part_s;
+  int part_stride;
 };
 
 template <int NHALF, int BN>
@@ -185,9 +226,12 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * (128 * NHALF);
+  const int t0 = blockIdx.y * p.tiles_per_chunk;
+  const int nt = (p.ntiles - t0 < p.tiles_per_chunk) ? (p.ntiles - t0) : p.tiles_per_chunk;
+  const bool split = gridDim.y > 1;
 
   if (p.ep.ctrl && p.ep.ctrl->converged) {  // solve already stopped: identity step
-    if (p.ep.old && p.ep.out)
+    if (!split && p.ep.old && p.ep.out)     // (with a column split the combine kernel does the copy)
       for (int r = tid; r < 128 * NHALF; r += blockDim.x)
         if (row0 + r < p.nr) p.ep.out[row0 + r] = p.ep.old[row0 + r];
     return;
@@ -248,16 +292,17 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       }
       int issued = 0;
 #pragma unroll 1
-      for (int j = 0; j < p.ntiles; ++j) {
+      for (int j = 0; j < nt; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
         if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag)) break;
         mbar_expect_tx(bar(B_FULL + s), b_stage_bytes);
         uint32_t dst = smem_u32(b_smem + s * b_stage_bytes);
+        const int col0 = (t0 + j) * BN;
         for (int kb = 0; kb < p.nfull; ++kb)
-          tma_load_2d(dst + kb * (BN * 128), &mapB_full, kb * 32, j * BN, bar(B_FULL + s));
+          tma_load_2d(dst + kb * (BN * 128), &mapB_full, kb * 32, col0, bar(B_FULL + s));
         for (int t = 0; t < p.ntail; ++t)
-          tma_load_2d(dst + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, j * BN,
+          tma_load_2d(dst + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, col0,
                       bar(B_FULL + s));
         issued = j + 1;
       }
@@ -274,7 +319,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       bool ok = mbar_wait(bar(A_FULL), 0, abort_flag);
       tc_fence_after();
 #pragma unroll 1
-      for (int j = 0; ok && j < p.ntiles; ++j) {
+      for (int j = 0; ok && j < nt; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
         if (!mbar_wait(bar(B_FULL + s), ph, abort_flag)) break;
@@ -320,57 +365,95 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const float scale = p.scale2;
-    float m_run = kRunInit, s_run = 0.f;
+    // off_run is the fp32 exponent offset all terms of s_run are relative to: sum = s_run * 2^off_run.
+    // It is carried as the ROUNDED value scale*max (not recomputed from the max), so that rescaling by
+    // 2^(off_old - off_new) and the final off_run + log2(s_run) are exact identities in fp32.
+    float m_run = kRunInit, off_run = kRunInit * scale, s_run = 0.f;
     bool ok = true;
-#pragma unroll 1
-    for (int j = 0; j < p.ntiles; ++j) {
-      const int buf = j & 1;
-      const uint32_t sph = (j >> 1) & 1;
-      if (!mbar_wait(bar(S_FULL + h * 2 + buf), sph, abort_flag)) { ok = false; break; }
-      __syncwarp();  // lanes leave the poll loop at different times; tcgen05.ld below is .sync.aligned
-      tc_fence_after();
-      const uint32_t taddr = lane_addr + (uint32_t)((h * 2 + buf) * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld32(taddr + c * 32, v);
-        if (c == BN / 32 - 1) {  // buffer fully read: hand it back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(S_EMPTY + h * 2 + buf));
-        }
-        float t[11];
+    constexpr int CH = BN / 32;  // 32-column chunks per tile (even)
+    const int total = nt * CH;
+    // One online-softmax update with the 32 scores of a chunk (this thread's row).
+    auto consume = [&](const uint32_t (&r)[32]) {
+      float v[32];
 #pragma unroll
-        for (int i = 0; i < 10; ++i) t[i] = max3(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
-        t[10] = fmaxf(v[30], v[31]);
-        float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
-        float cm = fmaxf(max3(u0, u1, u2), fmaxf(t[9], t[10]));
-        const float m_new = fmaxf(m_run, cm);
-        const float nms = -scale * m_new;
-        float s0 = s_run * ex2(fmaf(m_run, scale, nms)), s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      float t[11];
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          s0 += ex2(fmaf(v[i], scale, nms));
-          s1 += ex2(fmaf(v[i + 1], scale, nms));
-          s2 += ex2(fmaf(v[i + 2], scale, nms));
-          s3 += ex2(fmaf(v[i + 3], scale, nms));
-        }
-        s_run = (s0 + s1) + (s2 + s3);
-        m_run = m_new;
+      for (int i = 0; i < 10; ++i) t[i] = max3(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+      t[10] = fmaxf(v[30], v[31]);
+      float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
+      float cm = fmaxf(max3(u0, u1, u2), fmaxf(t[9], t[10]));
+      const float m_new = fmaxf(m_run, cm);
+      const float off_new = scale * m_new;
+      const float nms = -off_new;
+      float s0 = s_run * ex2(off_run - off_new), s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        s0 += ex2(fmaf(v[i], scale, nms));
+        s1 += ex2(fmaf(v[i + 1], scale, nms));
+        s2 += ex2(fmaf(v[i + 2], scale, nms));
+        s3 += ex2(fmaf(v[i + 3], scale, nms));
       }
+      s_run = (s0 + s1) + (s2 + s3);
+      m_run = m_new;
+      off_run = off_new;
+    };
+    // Issue the TMEM load of chunk g (first waits for its tile if g starts one). No wait for the data.
+    auto issue = [&](int g, uint32_t (&r)[32]) -> bool {
+      const int j = g / CH, c = g % CH;
+      const int buf = j & 1;
+      if (c == 0) {
+        if (!mbar_wait(bar(S_FULL + h * 2 + buf), (j >> 1) & 1, abort_flag)) return false;
+        __syncwarp();  // lanes leave the poll loop at different times; tcgen05.ld is .sync.aligned
+        tc_fence_after();
+      }
+      tmem_ld32_nowait(lane_addr + (uint32_t)((h * 2 + buf) * BN) + c * 32, r);
+      return true;
+    };
+    // The load of chunk g has landed (tcgen05.wait::ld): if it was the last chunk of its tile,
+    // hand the TMEM buffer back to the MMA warp.
+    auto landed = [&](int g, uint32_t (&r)[32]) {
+      tmem_ld_wait(r);
+      if (g % CH == CH - 1) {
+        const int j = g / CH;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(S_EMPTY + h * 2 + (j & 1)));
+      }
+    };
+    // Software pipeline, two register buffers: the load of chunk g+1 is in flight while chunk g is consumed.
+    uint32_t ra[32], rb[32];
+    ok = issue(0, ra);
+#pragma unroll 1
+    for (int g = 0; ok && g < total; g += 2) {
+      landed(g, ra);
+      ok = issue(g + 1, rb);  // total is even: g + 1 always exists
+      if (!ok) break;
+      consume(ra);
+      landed(g + 1, rb);
+      if (g + 2 < total) {
+        ok = issue(g + 2, ra);
+        if (!ok) break;
+      }
+      consume(rb);
     }
     const int r = row0 + h * 128 + q * 32 + lane;
     if (ok && r < p.nr) {
-      const LseEpilogue& ep = p.ep;
-      float lse2 = fmaf(m_run, scale, log2f(fmaxf(s_run, 1e-40f)));
-      if (ep.lse2) ep.lse2[r] = lse2;
-      if (ep.out) {
-        float cand = -p.eps * ep.damping * (lse2 * kLn2);
-        float o = ep.w * cand;
-        if (ep.old) o += (1.0f - ep.w) * ep.old[r];
-        if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
-        if (ep.addvec) o += ep.addcoef * ep.addvec[r];
-        ep.out[r] = o;
+      if (split) {
+        p.part_m[(size_t)blockIdx.y * p.part_stride + r] = off_run;
+        p.part_s[(size_t)blockIdx.y * p.part_stride + r] = s_run;
+      } else {
+        const LseEpilogue& ep = p.ep;
+        float lse2 = off_run + log2f(fmaxf(s_run, 1e-40f));
+        if (ep.lse2) ep.lse2[r] = lse2;
+        if (ep.out) {
+          float cand = -p.eps * ep.damping * (lse2 * kLn2);
+          float o = ep.w * cand;
+          if (ep.old) o += (1.0f - ep.w) * ep.old[r];
+          if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
+          if (ep.addvec) o += ep.addcoef * ep.addvec[r];
+          ep.out[r] = o;
+        }
       }
     }
   }
@@ -798,13 +881,65 @@ Shape plan_shape(int d, int prec) {
 
 template <int NHALF, int BN>
 cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUtensorMap& mb_f,
-                   const CUtensorMap& mb_t, const KernelParams& kp, int grid, size_t smem, cudaStream_t st) {
+                   const CUtensorMap& mb_t, const KernelParams& kp, dim3 grid, size_t smem, cudaStream_t st) {
   auto kern = tc_lse_kernel<NHALF, BN>;
   // Per device (context) attribute; cheap enough to set on every launch.
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
   if (e != cudaSuccess) return e;
   kern<<<grid, 128 + 128 * NHALF, smem, st>>>(ma_f, ma_t, mb_f, mb_t, kp);
   return cudaGetLastError();
+}
+
+// Merges the per-chunk (scaled max, sum) pairs of a column-split LSE pass and applies the epilogue.
+__global__ void lse_combine_kernel(int nr, int nchunk, const float* __restrict__ pm, const float* __restrict__ ps,
+                                   int stride, float eps, LseEpilogue ep) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= nr) return;
+  if (ep.ctrl && ep.ctrl->converged) {
+    if (ep.old && ep.out) ep.out[r] = ep.old[r];
+    return;
+  }
+  float M = pm[r];
+  for (int c = 1; c < nchunk; ++c) M = fmaxf(M, pm[(size_t)c * stride + r]);
+  float S = 0.f;
+  for (int c = 0; c < nchunk; ++c) S += ps[(size_t)c * stride + r] * ex2(pm[(size_t)c * stride + r] - M);
+  float lse2 = M + log2f(fmaxf(S, 1e-40f));
+  if (ep.lse2) ep.lse2[r] = lse2;
+  if (ep.out) {
+    float cand = -eps * ep.damping * (lse2 * kLn2);
+    float o = ep.w * cand;
+    if (ep.old) o += (1.0f - ep.w) * ep.old[r];
+    if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
+    if (ep.addvec) o += ep.addcoef * ep.addvec[r];
+    ep.out[r] = o;
+  }
+}
+
+constexpr int kMaxChunks = 16;
+constexpr int kNumSMs = 148;
+
+// Column chunks per row block: fill whole waves of the 148 SMs without making CTAs too short.
+int pick_chunks(int nblk, int ntiles) {
+  if (const char* env = getenv("FLASH_SINKHORN_B200_CHUNKS")) {  // diagnostics: force the column split
+    int c = atoi(env);
+    if (c >= 1 && c <= kMaxChunks && c <= ntiles) {
+      int tpc = (ntiles + c - 1) / c;
+      return (ntiles + tpc - 1) / tpc;
+    }
+  }
+  int best = 1;
+  double best_score = -1.0;
+  for (int c = 1; c <= kMaxChunks && c <= ntiles; ++c) {
+    int tpc = (ntiles + c - 1) / c;
+    int ce = (ntiles + tpc - 1) / tpc;  // chunks that actually get tiles
+    if (ce != c) continue;
+    long items = (long)nblk * ce;
+    long waves = (items + kNumSMs - 1) / kNumSMs;
+    double eff = (double)items / (double)(waves * kNumSMs);
+    double score = eff - 0.004 * c - (tpc < 4 ? 0.1 : 0.0);  // per-CTA set-up cost; avoid tiny chunks
+    if (score > best_score) { best_score = score; best = c; }
+  }
+  return best;
 }
 
 }  // namespace
@@ -824,6 +959,7 @@ size_t staged_bytes(int n, int m, int d, int prec) {
   size_t b = 0;
   b += 2 * (((size_t)pad256(n) * per_row + 1023) & ~size_t(1023));
   b += 2 * (((size_t)pad256(m) * per_row + 1023) & ~size_t(1023));
+  b += 2 * (size_t)kMaxChunks * pad256(n > m ? n : m) * sizeof(float);  // column-split partials
   return b + 1024;
 }
 
@@ -846,6 +982,9 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
     stage_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src[c], o.rows, o.rows_pad, d, sh.kc, sh.kp, prec,
                                                                   o.opA, o.opB);
   }
+  s.part_stride = pad256(n > m ? n : m);
+  s.part_m = reinterpret_cast<float*>(p);
+  s.part_s = s.part_m + (size_t)kMaxChunks * s.part_stride;
   return cudaGetLastError();
 }
 
@@ -874,10 +1013,18 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
   kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nstage = sh.nstage;
   kp.scale2 = scale2; kp.eps = a.eps; kp.ep = e;
   const int bm = 128 * sh.nhalf;
-  const int grid = (a.nr + bm - 1) / bm;
-  if (sh.nhalf == 2) return launch<2, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  if (sh.bn == 128) return launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  return launch<1, 64>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  const int nblk = (a.nr + bm - 1) / bm;
+  const int chunks = pick_chunks(nblk, kp.ntiles);
+  kp.tiles_per_chunk = (kp.ntiles + chunks - 1) / chunks;
+  kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride;
+  dim3 grid(nblk, chunks);
+  cudaError_t err;
+  if (sh.nhalf == 2) err = launch<2, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  else if (sh.bn == 128) err = launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  else err = launch<1, 64>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  if (err != cudaSuccess || chunks == 1) return err;
+  lse_combine_kernel<<<(a.nr + 255) / 256, 256, 0, st>>>(a.nr, chunks, s.part_m, s.part_s, s.part_stride, a.eps, e);
+  return cudaGetLastError();
 }
 
 // ---- plan-times-matrix host side ----

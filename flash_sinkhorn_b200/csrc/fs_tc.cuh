@@ -21,6 +21,9 @@ struct CloudOps {
 struct Staged {
   CloudOps cloud[2];  // 0 = x, 1 = y
   int d = 0, kc = 0, kp = 0, prec = 0;
+  float* part_m = nullptr;  // [chunks, part_stride] partial scaled maxima of a column-split pass
+  float* part_s = nullptr;  // [chunks, part_stride] partial sums
+  int part_stride = 0;
 };
 
 bool supported(int n, int m, int d, int prec);

@@ -216,12 +216,12 @@ def test_config1_matches_reference_golden(allow_tf32):
     val = loss(x, y)
     (gx,) = torch.autograd.grad(val, x)
     assert abs(val.item() - float(z["loss"])) <= 1e-4 * abs(float(z["loss"]))
-    # Gradient as a whole (Frobenius norm): rel 1e-3 in both modes. Single entries at eps = 0.01 are
-    # ill-conditioned (logit = cost/eps amplifies every rounding of x.y by 100): the tensor-core
-    # accumulators truncate, which shows up as a few 1e-2 of the largest entry in both modes.
+    # Gradient as a whole (Frobenius norm): rel 1e-3 in both modes. Single entries: 1e-3 of the largest
+    # entry in exact-fp32 (3xTF32) mode. In TF32 mode single entries at eps = 0.01 are ill-conditioned
+    # for ANY TF32 implementation: rounding x, y to 11 bits moves each logit (= cost/eps) by ~0.3.
     assert abs(gx.norm().item() - float(z["grad_x_norm"])) <= 1e-3 * float(z["grad_x_norm"])
-    assert rel(host(gx[:16]), z["grad_x_head"]) < 6e-2
-    assert rel(host(gx.sum(dim=1)), z["grad_x_rowsum"]) < 1e-1
+    assert rel(host(gx[:16]), z["grad_x_head"]) < (6e-2 if allow_tf32 else 1e-3)
+    assert rel(host(gx.sum(dim=1)), z["grad_x_rowsum"]) < (1e-1 if allow_tf32 else 1e-3)
 
 
 def test_marginals_at_scale_property():
@@ -236,11 +236,13 @@ def test_marginals_at_scale_property():
     y = (0.5 + torch.randn(m, 64, generator=gen)).cuda()
     a, b = torch.full((n,), 1.0 / n).cuda(), torch.full((m,), 1.0 / m).cuda()
     eps = 0.5
-    # exact-fp32 products on both sides: the identity only holds when solve and plan use the same scores
-    f, g = sinkhorn_flashstyle_alternating(x, y, a, b, eps=eps, n_iters=3, allow_tf32=False)
+    # Solve and plan application both run on the tensor-core engine over the same staged operands, so the
+    # scores are bit-identical and the identity holds to the TF32 rounding of the weights (2^-12, averaged).
+    from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_mat_flashstyle
+    f, g = sinkhorn_flashstyle_alternating(x, y, a, b, eps=eps, n_iters=3, allow_tf32=True)
     fh, gh = f - (x**2).sum(1), g - (y**2).sum(1)
-    col = apply_plan_vec_flashstyle(x, y, fh, gh, log_weights(a), log_weights(b), torch.ones(n).cuda(), eps=eps,
-                                    axis=0, allow_tf32=False)
+    col = apply_plan_mat_flashstyle(x, y, fh, gh, log_weights(a), log_weights(b), torch.ones(n, 64).cuda(), eps=eps,
+                                    axis=0, allow_tf32=True)[:, 0].contiguous()
     assert torch.isfinite(col).all()
-    assert (col / b - 1).abs().max().item() < 2e-3
+    assert (col / b - 1).abs().max().item() < 5e-3
     assert abs(col.sum().item() - 1.0) < 1e-3
