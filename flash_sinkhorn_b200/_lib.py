@@ -73,6 +73,10 @@ SIGNATURES = {
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_float, c_int, c_float,
          c_int, _P, c_size_t, _P],
     ),
+    "fs_apply_mat_static": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_float, c_int, c_float, _P],
+    ),
     "fs_grad": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float,

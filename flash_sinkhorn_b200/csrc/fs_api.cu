@@ -264,6 +264,11 @@ inline double dampening(double eps, double rho) {
 }  // namespace
 }  // namespace fs
 
+namespace fs {
+// Lets the other translation units of the library record an error for fs_last_error().
+int report_error(int code, const char* msg) { return fail(code, "%s", msg); }
+}  // namespace fs
+
 using namespace fs;
 
 extern "C" {

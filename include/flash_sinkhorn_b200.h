@@ -170,6 +170,22 @@ int fs_apply_mat(const float* x, const float* y, int n, int m, int d,
                  float eps, int axis, float cost_scale,
                  int prec, void* ws, size_t ws_bytes, void* stream);
 
+/* fs_apply_mat for callers that must not allocate. It has no counterpart in the reference.
+ * Same result as fs_apply_mat(..., FS_PREC_SIMT, ...) but takes no workspace: its one scratch
+ * vector lives in a 256 KiB static device array inside the library (held by every GPU that
+ * loads it, until exit). Meant for hosts that cannot provide scratch memory: operator
+ * callbacks that may not re-enter their framework's allocator, fixed-memory real-time loops,
+ * plug-ins that only ever see their input and output buffers.
+ *   - the output row count (n for axis 1, m for axis 0) must be <= 65536, else FS_ERR_BAD_ARG;
+ *   - calls that overlap on one GPU race on the shared array: serialise them;
+ *   - the first call on a device looks up the array's device address; make that call outside
+ *     any stream capture. Nothing in the array needs clearing between calls. */
+int fs_apply_mat_static(const float* x, const float* y, int n, int m, int d,
+                        const float* f_hat, const float* g_hat,
+                        const float* log_a, const float* log_b,
+                        const float* mat, int dv, const float* scale, float* out,
+                        float eps, int axis, float cost_scale, void* stream);
+
 /* Analytic gradient of the OT cost (barycentric form), standard potentials f, g:
  *   grad_x_i = 2cs*gs*a_i*( x_i - sum_j w_ij y_j / max(sum_j w_ij, 1e-40) ),
  *   w_ij = exp( (g_j - C_ij)/eps + log_b_j );  grad_y symmetric with f, a.
