@@ -104,6 +104,8 @@ def main():
     ap.add_argument("--no-debias", action="store_true")
     ap.add_argument("--fp32", action="store_true", help="3xTF32 exact-fp32 mode instead of TF32")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only time the dominant kernels (one LSE pass, one gradient pass); small, for profilers")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -152,6 +154,34 @@ def main():
     gx_host = torch.empty(n, d).pin_memory()
     loss_fn = SamplesLoss("sinkhorn", blur=0.1, use_epsilon_scaling=False, eps=eps, n_iters=iters,
                           half_cost=False, debias=debias, allow_tf32=not args.fp32)
+
+    if args.kernel_only:
+        from flash_sinkhorn_b200.kernels.grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid
+        from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse_fused
+        x_dev, y_dev = x_host.to(dev), y_host.to(dev)
+        gh = -(y_dev**2).sum(1)
+        a_w = torch.full((n,), 1.0 / n, device=dev)
+        b_w = torch.full((m,), 1.0 / m, device=dev)
+        lb = b_w.log()
+        res = {}
+        for name, fn in (("lse_pass", lambda: flashsinkhorn_lse_fused(x_dev, y_dev, gh, lb, eps, allow_tf32=not args.fp32)),
+                         ("grad_x_pass", lambda: sinkhorn_geomloss_online_grad_sqeuclid(
+                             x_dev, y_dev, a_w, b_w, torch.zeros(n, device=dev), gh + (y_dev**2).sum(1), eps=eps,
+                             allow_tf32=not args.fp32, compute_grad_y=False))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record()
+            for _ in range(5):
+                fn()
+            k1.record()
+            torch.cuda.synchronize()
+            res[name + "_ms"] = k0.elapsed_time(k1) / 5
+            res[name + "_entries_per_s"] = n * m / (res[name + "_ms"] * 1e-3)
+        print(json.dumps({"kernel_only": True, "n": n, "m": m, "d": d, "eps": eps,
+                          "mode": "fp32(3xTF32)" if args.fp32 else "tf32", **res}))
+        return 0
 
     def step_resident(x, y):
         xs = x.detach().requires_grad_(True)
