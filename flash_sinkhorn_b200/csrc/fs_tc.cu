@@ -65,10 +65,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait. Returns false (and raises *abort_flag) if the budget runs out or another
 // thread of the CTA already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// `backoff_ns` > 0 puts the polling thread to sleep between polls: the single-thread producer / MMA roles
+// spend most of their time waiting and must not steal issue slots from the soft-max warps of their scheduler.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
+    if (backoff_ns) __nanosleep(backoff_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kSpinLimit) {
@@ -195,6 +199,17 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t sbo_bytes
   return ((uint64_t)hi << 32) | lo;
 }
 
+// Same descriptor assembled from a running low word (address >> 4, leading-offset field = 1) and a
+// constant high word; lets the MMA-issuing lane advance operands with one integer add.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+constexpr uint32_t kDescHi128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8-row groups 1024 B apart, 128 B swizzle
+constexpr uint32_t kDescHi32 = (256u >> 4) | (1u << 14) | (6u << 29);    // 8-row groups 256 B apart, 32 B swizzle
+
 // Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major, M=128:
 //   [4,6) D format = 1 (f32), [7,10) A format = 2 (tf32), [10,13) B format = 2 (tf32),
 //   [17,23) N >> 3, [24,29) M >> 4.
@@ -218,8 +233,12 @@ struct KernelParams {
   int part_stride;
 };
 
+// Soft-max warpgroups per 128-row half: each takes half of every tile's 32-column chunks (more warps per
+// scheduler to hide the fixed latencies around the chunk max / rescale); their partials merge at the end.
+constexpr int kParts = 2;
+
 template <int NHALF, int BN>
-__global__ void __launch_bounds__(128 + 128 * NHALF, 1)
+__global__ void __launch_bounds__(128 + 128 * NHALF * kParts, 1)
 tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constant__ CUtensorMap mapA_tail,
               const __grid_constant__ CUtensorMap mapB_full, const __grid_constant__ CUtensorMap mapB_tail,
               const KernelParams p) {
@@ -249,6 +268,8 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
             A_FULL = S_EMPTY + 2 * NHALF, DRAIN = A_FULL + 1, NBARS = DRAIN + 1;
   uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  float* merge_off = (float*)(tmem_slot + 4);        // [NHALF*128] partials of the second column part
+  float* merge_sum = merge_off + NHALF * 128;
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
   constexpr uint32_t kTmemCols = (2 * NHALF * BN) < 32 ? 32 : (2 * NHALF * BN);
@@ -260,7 +281,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     }
     for (int i = 0; i < 2 * NHALF; ++i) {
       mbar_init(bar(S_FULL + i), 1);
-      mbar_init(bar(S_EMPTY + i), 4);  // one arrive per warp of the warpgroup
+      mbar_init(bar(S_EMPTY + i), 4 * kParts);  // one arrive per soft-max warp reading the buffer
     }
     mbar_init(bar(A_FULL), 1);
     mbar_init(bar(DRAIN), 1);
@@ -295,7 +316,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       for (int j = 0; j < nt; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag)) break;
+        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 64)) break;
         mbar_expect_tx(bar(B_FULL + s), b_stage_bytes);
         uint32_t dst = smem_u32(b_smem + s * b_stage_bytes);
         const int col0 = (t0 + j) * BN;
@@ -316,41 +337,66 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // ===================== MMA issuer =====================
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BN);
-      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag);
+      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 64);
       tc_fence_after();
+      const uint32_t a_lo0 = desc_lo(smem_u32(a_smem));
+      const uint32_t a_half_units = a_half_bytes >> 4;
 #pragma unroll 1
       for (int j = 0; ok && j < nt; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag)) break;
+        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 64)) break;
         tc_fence_after();
         const uint32_t b_addr = smem_u32(b_smem + s * b_stage_bytes);
         const int buf = j & 1;
         const uint32_t sph = (j >> 1) & 1;
+        // Both halves' accumulators must be free, then their K chains are interleaved: consecutive MMAs
+        // into the same accumulator are dependent (each waits for the previous one to retire), two
+        // independent chains keep the tensor pipe busy.
 #pragma unroll 1
         for (int h = 0; h < NHALF; ++h) {
-          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(a_smem + h * a_half_bytes);
-          const uint32_t d_tmem = tmem_base + (uint32_t)((h * 2 + buf) * BN);
-          uint32_t acc = 0;
-          for (int kb = 0; kb < p.nfull; ++kb) {
+          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 64)) { ok = false; break; }
+        }
+        if (!ok) break;
+        tc_fence_after();
+        // The issuing thread is a single lane: every integer instruction it spends per MMA is exposed
+        // latency (~5 cycles each). Descriptors are therefore advanced incrementally: the low word holds
+        // (address >> 4), the high word (stride, version, swizzle) is a constant per block class.
+        const uint32_t d_tmem0 = tmem_base + (uint32_t)(buf * BN);
+        uint32_t al = a_lo0, bl = desc_lo(b_addr);
+        uint32_t acc = 0;
+#pragma unroll 1
+        for (int kb = 0; kb < p.nfull; ++kb) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              uint64_t ad = make_desc(a_addr + kb * (128 * 128) + ks * 32, 1024, 2);
-              uint64_t bd = make_desc(b_addr + kb * (BN * 128) + ks * 32, 1024, 2);
-              umma_tf32(d_tmem, ad, bd, idesc, acc);
-              acc = 1;
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t bd = pack_desc(bl + 2 * ks, kDescHi128);
+#pragma unroll
+            for (int h = 0; h < NHALF; ++h) {
+#ifndef FS_EXP_SKIP_MMA
+              umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units + 2 * ks, kDescHi128), bd,
+                        idesc, acc);
+#endif
             }
-          }
-          for (int t = 0; t < p.ntail; ++t) {
-            uint64_t ad = make_desc(a_addr + p.nfull * (128 * 128) + t * (128 * 32), 256, 6);
-            uint64_t bd = make_desc(b_addr + p.nfull * (BN * 128) + t * (BN * 32), 256, 6);
-            umma_tf32(d_tmem, ad, bd, idesc, acc);
             acc = 1;
           }
-          umma_commit(bar(S_FULL + h * 2 + buf));
+          al += (128 * 128) >> 4;
+          bl += (BN * 128) >> 4;
         }
+#pragma unroll 1
+        for (int t = 0; t < p.ntail; ++t) {
+          const uint64_t bd = pack_desc(bl, kDescHi32);
+#pragma unroll
+          for (int h = 0; h < NHALF; ++h) {
+#ifndef FS_EXP_SKIP_MMA
+            umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units, kDescHi32), bd, idesc, acc);
+#endif
+          }
+          acc = 1;
+          al += (128 * 32) >> 4;
+          bl += (BN * 32) >> 4;
+        }
+#pragma unroll
+        for (int h = 0; h < NHALF; ++h) umma_commit(bar(S_FULL + h * 2 + buf));
         if (!ok) break;
         umma_commit(bar(B_EMPTY + s));
       }
@@ -361,19 +407,25 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     }
   } else if (warp >= 4) {
     // ===================== soft-max warpgroups =====================
-    const int h = (warp - 4) >> 2;
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int wg = (warp - 4) >> 2;      // warpgroup index
+    const int h = wg / kParts;           // 128-row half
+    const int part = wg % kParts;        // which half of each tile's chunks
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const float scale = p.scale2;
     // off_run is the fp32 exponent offset all terms of s_run are relative to: sum = s_run * 2^off_run.
     // It is carried as the ROUNDED value scale*max (not recomputed from the max), so that rescaling by
     // 2^(off_old - off_new) and the final off_run + log2(s_run) are exact identities in fp32.
-    float m_run = kRunInit, off_run = kRunInit * scale, s_run = 0.f;
+    float m_run = kRunInit, off_run = __fmul_rn(scale, kRunInit), s_run = 0.f;
     bool ok = true;
-    constexpr int CH = BN / 32;  // 32-column chunks per tile (even)
+    constexpr int CH = BN / 32 / kParts;  // 32-column chunks of a tile owned by this warpgroup
     const int total = nt * CH;
+    const int c_base = part * CH;
     // One online-softmax update with the 32 scores of a chunk (this thread's row).
     auto consume = [&](const uint32_t (&r)[32]) {
+#ifdef FS_EXP_SKIP_SOFTMAX
+      s_run += __uint_as_float(r[0]); return;
+#endif
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -384,7 +436,9 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
       float cm = fmaxf(max3(u0, u1, u2), fmaxf(t[9], t[10]));
       const float m_new = fmaxf(m_run, cm);
-      const float off_new = scale * m_new;
+      // __fmul_rn: must not be contracted into an FMA with the subtraction below (the residual of the
+      // product would leak into the exponent; with the huge init/mask magnitudes it even overflows).
+      const float off_new = __fmul_rn(scale, m_new);
       const float nms = -off_new;
       float s0 = s_run * ex2(off_run - off_new), s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
@@ -407,7 +461,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         __syncwarp();  // lanes leave the poll loop at different times; tcgen05.ld is .sync.aligned
         tc_fence_after();
       }
-      tmem_ld32_nowait(lane_addr + (uint32_t)((h * 2 + buf) * BN) + c * 32, r);
+      tmem_ld32_nowait(lane_addr + (uint32_t)((h * 2 + buf) * BN) + (c_base + c) * 32, r);
       return true;
     };
     // The load of chunk g has landed (tcgen05.wait::ld): if it was the last chunk of its tile,
@@ -427,9 +481,12 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
 #pragma unroll 1
     for (int g = 0; ok && g < total; g += 2) {
       landed(g, ra);
-      ok = issue(g + 1, rb);  // total is even: g + 1 always exists
-      if (!ok) break;
+      if (g + 1 < total) {
+        ok = issue(g + 1, rb);
+        if (!ok) break;
+      }
       consume(ra);
+      if (g + 1 >= total) break;
       landed(g + 1, rb);
       if (g + 2 < total) {
         ok = issue(g + 2, ra);
@@ -438,7 +495,19 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       consume(rb);
     }
     const int r = row0 + h * 128 + q * 32 + lane;
-    if (ok && r < p.nr) {
+    // Second column part parks its partial in shared memory; the first part merges after the barrier.
+    if (part == 1) {
+      merge_off[h * 128 + q * 32 + lane] = ok ? off_run : kRunInit;
+      merge_sum[h * 128 + q * 32 + lane] = ok ? s_run : 0.f;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");  // soft-max warps only
+    if (part == 0) {
+      const float o2 = merge_off[h * 128 + q * 32 + lane], s2 = merge_sum[h * 128 + q * 32 + lane];
+      const float on = fmaxf(off_run, o2);
+      s_run = s_run * ex2(off_run - on) + s2 * ex2(o2 - on);
+      off_run = on;
+    }
+    if (ok && part == 0 && r < p.nr) {
       if (split) {
         p.part_m[(size_t)blockIdx.y * p.part_stride + r] = off_run;
         p.part_s[(size_t)blockIdx.y * p.part_stride + r] = s_run;
@@ -584,7 +653,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       for (int j = 0; j < p.ntiles; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag)) break;
+        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 64)) break;
         mbar_expect_tx(bar(B_FULL + s), stage_bytes);
         uint32_t d0 = smem_u32(st_smem + s * stage_bytes);
         for (int kb = 0; kb < p.nfull; ++kb)
@@ -609,7 +678,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc1 = make_idesc(BN);
       const uint32_t idesc2 = make_idesc(p.dv_pad);
-      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag);
+      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 64);
       tc_fence_after();
       const uint32_t a_addr = smem_u32(a_smem);
       uint32_t o_acc = 0;
@@ -617,7 +686,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       auto mma2 = [&](int jj) -> bool {
         const int s = jj % p.nstage;
         const int buf = jj & 1;
-        if (!mbar_wait(bar(W_FULL + buf), (jj >> 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(W_FULL + buf), (jj >> 1) & 1, abort_flag, 64)) return false;
         tc_fence_after();
         const uint32_t w_tmem = tmem_base + buf * WCOLS;
         const uint32_t v_addr = smem_u32(st_smem + s * stage_bytes) + b_bytes;
@@ -626,13 +695,15 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
           // part 0: Wh.Vh   part 1: Wl.Vh   part 2: Wh.Vl
           const uint32_t wa = w_tmem + ((part == 1) ? BN : 0);
           const uint32_t va = v_addr + ((part == 2) ? v_bytes : 0);
+          uint32_t vl = desc_lo(va);
+#pragma unroll 1
           for (int kb = 0; kb < BN / 32; ++kb) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              uint64_t bd = make_desc(va + kb * v_blk + ks * 32, 1024, 2);
-              umma_tf32_ts(o_tmem, wa + kb * 32 + ks * 8, bd, idesc2, o_acc);
+              umma_tf32_ts(o_tmem, wa + kb * 32 + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
               o_acc = 1;
             }
+            vl += v_blk >> 4;
           }
         }
         umma_commit(bar(B_EMPTY + s));
@@ -644,24 +715,29 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
         const uint32_t ph = (j / p.nstage) & 1;
         // With a single stage the previous tile's second GEMM must retire before its buffers are refilled.
         if (p.nstage == 1 && j > 0) { if (!mma2(j - 1)) { ok = false; break; } }
-        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 64)) { ok = false; break; }
         tc_fence_after();
         const uint32_t b_addr = smem_u32(st_smem + s * stage_bytes);
         const uint32_t d_tmem = tmem_base + (j & 1) * WCOLS;
         // The S/W buffer (j&1) was last read by MMA2(j-2), issued earlier by this same thread: in order.
         uint32_t acc = 0;
+        uint32_t al = desc_lo(a_addr), bl = desc_lo(b_addr);
+#pragma unroll 1
         for (int kb = 0; kb < p.nfull; ++kb) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            umma_tf32(d_tmem, make_desc(a_addr + kb * (128 * 128) + ks * 32, 1024, 2),
-                      make_desc(b_addr + kb * (BN * 128) + ks * 32, 1024, 2), idesc1, acc);
+            umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1, acc);
             acc = 1;
           }
+          al += (128 * 128) >> 4;
+          bl += (BN * 128) >> 4;
         }
+#pragma unroll 1
         for (int t = 0; t < p.ntail; ++t) {
-          umma_tf32(d_tmem, make_desc(a_addr + p.nfull * (128 * 128) + t * (128 * 32), 256, 6),
-                    make_desc(b_addr + p.nfull * (BN * 128) + t * (BN * 32), 256, 6), idesc1, acc);
+          umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc1, acc);
           acc = 1;
+          al += (128 * 32) >> 4;
+          bl += (BN * 32) >> 4;
         }
         umma_commit(bar(S_FULL + (j & 1)));
         if (p.nstage > 1 && j > 0) { if (!mma2(j - 1)) { ok = false; break; } }
@@ -858,11 +934,15 @@ struct Shape {
 Shape plan_shape(int d, int prec) {
   Shape s{};
   s.kc = (prec == 0) ? d : 3 * d;
+#ifdef FS_EXP_NOAUG
+  s.kp = (s.kc + 7) & ~7;
+#else
   s.kp = (s.kc + 3 + 7) & ~7;
+#endif
   s.nfull = s.kp / 32;
   s.ntail = (s.kp % 32) / 8;
   const size_t row_bytes = (size_t)s.kp * 4;
-  const size_t budget = kSmemMax - 2048;  // barriers + alignment slack
+  const size_t budget = kSmemMax - 4096;  // barriers, merge buffers, alignment slack
   s.ok = false;
   const int cand[3][2] = {{2, 128}, {1, 128}, {1, 64}};
   for (auto& c : cand) {
@@ -871,7 +951,7 @@ Shape plan_shape(int d, int prec) {
     int ns = (int)((budget - a) / b);
     if (ns > 4) ns = 4;
     s.nhalf = c[0]; s.bn = c[1]; s.nstage = ns;
-    s.smem = a + ns * b + 2048;
+    s.smem = a + ns * b + 4096;
     if (s.smem < (size_t)kSmemMin) s.smem = kSmemMin;
     s.ok = true;
     break;
@@ -886,7 +966,7 @@ cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUten
   // Per device (context) attribute; cheap enough to set on every launch.
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
   if (e != cudaSuccess) return e;
-  kern<<<grid, 128 + 128 * NHALF, smem, st>>>(ma_f, ma_t, mb_f, mb_t, kp);
+  kern<<<grid, 128 + 128 * NHALF * kParts, smem, st>>>(ma_f, ma_t, mb_f, mb_t, kp);
   return cudaGetLastError();
 }
 

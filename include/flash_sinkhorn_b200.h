@@ -77,6 +77,12 @@ long long fs_launch_count(void);
  * while reading it. SYNCHRONISES the device; meant for tests and post-mortems. */
 int fs_device_error(void);
 
+/* Measurement aid (no reference counterpart): ex2 evaluations per second that this GPU sustains,
+ * mode 0 = ex2.approx alone, mode 1 = the soft-max inner loop (max + FFMA + ex2 + FADD per entry) on
+ * register data, with `warps_per_sm` resident warps per SM. Used by bench.py as the measured
+ * transcendental-pipe peak of the roofline. Allocates 4 bytes and synchronises; < 0 on error. */
+double fs_micro_exp_rate(int mode, int warps_per_sm);
+
 /* Scratch bytes needed by `op` (one of FS_OP_*) at these sizes. */
 size_t fs_workspace_bytes(int op, int n, int m, int d, int prec);
 
