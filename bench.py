@@ -7,8 +7,9 @@ iterations, debiased, forward + analytic grad_x) on N B200 GPUs of one node.
 A "step" is one full SamplesLoss forward + backward on one synthetic problem. Prints ONE JSON line
 (rank 0). `value` = cost-matrix entries evaluated per second over all ranks with inputs resident in
 HBM; `e2e` = same metric through the public API with pinned HOST buffers, copies included.
-Multi-GPU: every rank solves its own independent problem of the same shape ("weak" scaling, no
-data-path collective); see DESIGN.md for why the row-sharded all-gather variant is not wired yet.
+Multi-GPU (torchrun, one rank per GPU): the SAME problem is solved by all ranks together - rows of every
+potential update and of the gradient are sharded over the ranks and all-gathered over NCCL after each
+half-step ("strong" scaling: total work fixed, `value` counts every entry once).
 """
 import argparse
 import json
@@ -131,7 +132,7 @@ def main():
         cb["value"] = ent / dt
         line = {"impl": "reference", "metric": "cost_entries_per_sec", "value": ent / dt, "unit": "entries/s",
                 "n_gpus": 0, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic", "config": {"workload": workload, "note": "each step = bounded sample: " + cb["sample"]},
                 "cpu_baseline": cb,
                 "e2e": {"value": ent / dt, "unit": "entries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -148,12 +149,13 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
 
-    gen = torch.Generator().manual_seed(1 + rank)
+    group = dist.group.WORLD if world > 1 else None
+    gen = torch.Generator().manual_seed(1)  # identical inputs on every rank (replicated clouds)
     x_host = torch.randn(n, d, generator=gen).pin_memory()
     y_host = (0.5 + torch.randn(m, d, generator=gen)).pin_memory()
     gx_host = torch.empty(n, d).pin_memory()
     loss_fn = SamplesLoss("sinkhorn", blur=0.1, use_epsilon_scaling=False, eps=eps, n_iters=iters,
-                          half_cost=False, debias=debias, allow_tf32=not args.fp32)
+                          half_cost=False, debias=debias, allow_tf32=not args.fp32, process_group=group)
 
     if args.kernel_only:
         from flash_sinkhorn_b200.kernels.grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid
@@ -256,21 +258,26 @@ def main():
         except OSError:
             pass
         sm_mhz = clocks.get("sm_mhz") or 1965.0
-        # exp roofline: 16 ex2/clk/SM x 148 SMs at the SM clock seen during the run;
+        # exp roofline: ex2 issue rate MEASURED on this GPU by the library's micro-benchmark (all SMs, 32
+        # warps/SM, register data only); nominal 16 ex2/clk/SM x 148 SMs x sampled clock kept for context.
         # tensor roofline: TF32 dense = half the measured bf16 rate, 2*d flops per entry (x3 in 3xTF32 mode)
-        exp_peak = 16 * 148 * sm_mhz * 1e6
+        exp_nominal = 16 * 148 * sm_mhz * 1e6
+        exp_measured = float(lib.fs_micro_exp_rate(0, 32))
+        softmax_loop_rate = float(lib.fs_micro_exp_rate(1, 16))
+        exp_peak = exp_measured if exp_measured > 0 else exp_nominal
         bf16 = peaks.get("bf16_tflops_sustained", 1400.0) * 1e12
         tc_peak = (bf16 / 2) / (2 * d * (3 if args.fp32 else 1))
         peak = min(exp_peak, tc_peak)
         achieved = n * m / (kernel_ms * 1e-3)
-        total = per_step * args.steps * world
+        total = per_step * args.steps  # strong scaling: the ranks share one problem
         line = {
             "metric": "cost_entries_per_sec", "value": total / (ms * 1e-3), "unit": "entries/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 (3xTF32 products)" if args.fp32 else "tf32 products, f32 accumulate/exp",
             "data": "synthetic",
-            "config": {"workload": workload, "entries_per_step": per_step, "l2": "inputs 25.6 MB < L2; the pass is "
+            "config": {"workload": workload, "entries_per_step": per_step, "parallelism": (f"rows sharded over {world} GPUs, all-gather per half-step" if world > 1 else "single GPU"),
+                       "l2": "inputs 25.6 MB < L2; the pass is "
                        "compute-bound (one exp + 2d flops per entry), L2 is not flushed between steps",
                        "ms_per_100iter_solve": ms / args.steps * (2 * (iters + 2) * n * m) / per_step},
             "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "entries/s", "ms_per_step": ms_e2e / args.steps,
@@ -281,9 +288,11 @@ def main():
             "roofline": {"bound": "exp" if exp_peak <= tc_peak else "tensor", "achieved": achieved, "peak": peak,
                          "unit": "entries/s", "frac": achieved / peak, "traffic": None,
                          "kernel": "row soft-min pass (fs_lse), n*m entries per launch", "kernel_ms": kernel_ms,
-                         "exp_peak": exp_peak, "tensor_peak": tc_peak,
-                         "peak_source": "16 ex2/clk/SM x 148 SM x sampled SM clock; tensor = measured bf16 "
-                                        "(MEASURED_PEAKS.json, sustained)/2 for TF32"},
+                         "exp_peak": exp_peak, "exp_peak_nominal": exp_nominal, "tensor_peak": tc_peak,
+                         "softmax_loop_rate": softmax_loop_rate,
+                         "peak_source": "of measured: ex2.approx rate from fs_micro_exp_rate(0,32) on this GPU; "
+                                        "tensor = measured bf16 (MEASURED_PEAKS.json, sustained)/2 for TF32; "
+                                        "nominal = 16 ex2/clk/SM x 148 SM x sampled SM clock"},
             "loss": loss_val,
         }
         if not args.skip_cpu and world == 1:

@@ -57,6 +57,8 @@ class _SinkhornConfig:
     lambda_y: float
     threshold: Optional[float]
     inner_iterations: int
+    # Extension: torch.distributed group for row-sharded multi-GPU solves (None = single GPU).
+    process_group: object = None
 
 
 class _SinkhornGradFn(torch.autograd.Function):
@@ -69,6 +71,7 @@ class _SinkhornGradFn(torch.autograd.Function):
             x, y, a, b, f_grad, g_grad,
             eps=float(eps), allow_tf32=config.allow_tf32, grad_scale=grad_scale,
             compute_grad_x=bool(want_x), compute_grad_y=bool(want_y), cost_scale=config.cost_scale,
+            process_group=config.process_group,
         )
         ctx.save_for_backward(x, y, a, b, f_grad, g_grad, grad_scale)
         ctx.eps = float(eps)
@@ -126,6 +129,7 @@ class _SinkhornCostFn(torch.autograd.Function):
                 eps=config.eps, n_iters=config.n_iters, allow_tf32=config.allow_tf32,
                 cost_scale=config.cost_scale, rho_x=config.rho_x, rho_y=config.rho_y,
                 threshold=config.threshold, check_every=config.inner_iterations,
+                process_group=config.process_group,
             )
             if config.last_extrapolation:
                 f_cost, g_cost, f_grad, g_grad = sinkhorn_flashstyle_symmetric(

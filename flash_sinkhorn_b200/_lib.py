@@ -55,6 +55,16 @@ SIGNATURES = {
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
          c_float, c_float, c_float, c_float, c_float, c_int, _P, c_size_t, _P],
     ),
+    "fs_symmetric_step_range": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
+         c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P],
+    ),
+    "fs_grad_range": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float,
+         c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P],
+    ),
     "fs_solve_symmetric": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_float, c_double, c_double,

@@ -174,8 +174,13 @@ struct Problem {
     s.cost_scale = cs;
     s.tile_row_ptr = csr_rp[side];
     s.tile_col_idx = csr_ci[side];
+    s.row_begin = row_lo[side];
+    if (row_hi[side] >= 0 && row_hi[side] < s.nr) s.nr = row_hi[side];
     return s;
   }
+  // Row sharding: side `s` only produces rows [row_lo[s], row_hi[s]) (row_hi < 0: to the end).
+  int row_lo[2] = {0, 0};
+  int row_hi[2] = {-1, -1};
 
   cudaError_t lse(int side, const float* pot, const float* logw, float eps, const LseEpilogue& ep) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
@@ -220,7 +225,7 @@ int check_device() {
 // Sets up `p` (engine choice + staged tcgen05 operands carved from ws).
 // `lse_only` is true for ops that only run LSE passes.
 int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int m, int d, float cs, int prec,
-                 cudaStream_t st, bool measure_only, int pv_dv = 0) {
+                 cudaStream_t st, bool measure_only, int pv_dv = 0, bool run_staging = true) {
   p.x = x; p.y = y; p.n = n; p.m = m; p.d = d; p.cs = cs; p.prec = prec; p.st = st;
   p.use_tc = (prec != FS_PREC_SIMT) && tc::supported(n, m, d, prec);
   if (p.use_tc) {
@@ -228,7 +233,7 @@ int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int 
     char* buf = ws.take<char>(bytes);
     if (!measure_only) {
       if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
-      cudaError_t e = tc::stage(p.staged, buf, x, y, n, m, d, prec, st);
+      cudaError_t e = tc::stage(p.staged, buf, x, y, n, m, d, prec, st, run_staging);
       if (e != cudaSuccess) return fail(FS_ERR_CUDA, "staging tcgen05 operands failed: %s", cudaGetErrorString(e));
     }
     if (pv_dv > 0 && tc::pv_supported(d, prec, pv_dv)) {
@@ -659,6 +664,84 @@ int fs_mat5(const float* x, const float* y, int n, int m, int d, const float* f_
 }
 
 }  // extern "C"
+
+extern "C" int fs_symmetric_step_range(const float* x, const float* y, int n, int m, int d, const float* f_hat,
+                                       const float* g_hat, const float* log_a, const float* log_b, float* f_out,
+                                       float* g_out, const float* alpha_x, const float* beta_y, float eps, float w,
+                                       float damp_f, float damp_g, float cost_scale, int f_begin, int f_end,
+                                       int g_begin, int g_end, int restage, int prec, void* wsp, size_t ws_bytes,
+                                       void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!f_hat || !g_hat || !log_a || !log_b || !f_out || !g_out)
+    return fail(FS_ERR_BAD_ARG, "potentials, log-weights and outputs must be non-null");
+  if (f_out == f_hat || g_out == g_hat) return fail(FS_ERR_BAD_ARG, "outputs must not alias the inputs (Jacobi step)");
+  if (f_begin < 0 || f_end > n || g_begin < 0 || g_end > m || f_begin > f_end || g_begin > g_end)
+    return fail(FS_ERR_BAD_ARG, "row ranges must satisfy 0 <= begin <= end <= rows");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, 0, restage != 0));
+  p.row_lo[0] = f_begin; p.row_hi[0] = f_end;
+  p.row_lo[1] = g_begin; p.row_hi[1] = g_end;
+  LseEpilogue ef;
+  ef.damping = damp_f; ef.old = f_hat; ef.w = w; ef.out = f_out;
+  if (alpha_x && damp_f < 1.f) { ef.shift = alpha_x; ef.shiftcoef = w * (1.f - damp_f); }
+  LseEpilogue eg;
+  eg.damping = damp_g; eg.old = g_hat; eg.w = w; eg.out = g_out;
+  if (beta_y && damp_g < 1.f) { eg.shift = beta_y; eg.shiftcoef = w * (1.f - damp_g); }
+  if (f_end > f_begin) FS_CUDA(p.lse(0, g_hat, log_b, eps, ef));
+  if (g_end > g_begin) FS_CUDA(p.lse(1, f_hat, log_a, eps, eg));
+  return FS_OK;
+}
+
+extern "C" int fs_grad_range(const float* x, const float* y, int n, int m, int d, const float* a, const float* b,
+                             const float* log_a, const float* log_b, const float* f, const float* g,
+                             const float* grad_scale, float* grad_x, float* grad_y, float eps, float cost_scale,
+                             int x_begin, int x_end, int y_begin, int y_end, int prec, void* wsp, size_t ws_bytes,
+                             void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!a || !b || !log_a || !log_b || !f || !g) return fail(FS_ERR_BAD_ARG, "null argument");
+  if (x_begin < 0 || x_end > n || y_begin < 0 || y_end > m || x_begin > x_end || y_begin > y_end)
+    return fail(FS_ERR_BAD_ARG, "row ranges must satisfy 0 <= begin <= end <= rows");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, d));
+  if (p.use_tc && !p.pv_scratch) p.use_tc = false;
+  p.row_lo[0] = x_begin; p.row_hi[0] = x_end;
+  p.row_lo[1] = y_begin; p.row_hi[1] = y_end;
+  float* fh = ws.take<float>(n);
+  float* gh = ws.take<float>(m);
+  float* Rn = ws.take<float>(n);
+  float* Rm = ws.take<float>(m);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+  if (grad_x && x_end > x_begin) {
+    sqnorm_kernel<<<g1(m * 32), 256, 0, st>>>(y, m, d, cost_scale, Rm);
+    axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, g, -1.f, Rm, gh);
+    LseEpilogue ep;
+    ep.lse2 = Rn;
+    FS_CUDA(p.lse(0, gh, log_b, eps, ep));
+    PvArgs pa;
+    pa.R = Rn; pa.V = y; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = a; pa.gs = grad_scale;
+    pa.coef = 2.f * cost_scale; pa.out = grad_x;
+    FS_CUDA(p.pv(0, gh, log_b, eps, pa));
+  }
+  if (grad_y && y_end > y_begin) {
+    sqnorm_kernel<<<g1(n * 32), 256, 0, st>>>(x, n, d, cost_scale, Rn);
+    axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, f, -1.f, Rn, fh);
+    LseEpilogue ep;
+    ep.lse2 = Rm;
+    FS_CUDA(p.lse(1, fh, log_a, eps, ep));
+    PvArgs pa;
+    pa.R = Rm; pa.V = x; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = b; pa.gs = grad_scale;
+    pa.coef = 2.f * cost_scale; pa.out = grad_y;
+    FS_CUDA(p.pv(1, fh, log_a, eps, pa));
+  }
+  FS_CUDA(cudaGetLastError());
+  return FS_OK;
+}
 
 // ---------------------------------------------------------------------------
 // Device-resident conjugate gradient on the Schur complement

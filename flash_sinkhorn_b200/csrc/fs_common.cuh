@@ -29,6 +29,7 @@ struct StreamArgs {
   const float* rows = nullptr;  // [nr, d]
   const float* cols = nullptr;  // [nc, d]
   int nr = 0, nc = 0, d = 0;
+  int row_begin = 0;            // only rows [row_begin, nr) are produced (row sharding); nr = end of the range
   const float* pot = nullptr;   // [nc]
   const float* logw = nullptr;  // [nc] or nullptr
   float eps = 1.f, cost_scale = 1.f;

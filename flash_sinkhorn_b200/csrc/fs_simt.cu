@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(NT) simt_stream_kernel(StreamArgs s, LseEpilog
   __shared__ float vec_s[TN];
 
   const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
-  const int row0 = blockIdx.x * TM;
+  const int row0 = s.row_begin + blockIdx.x * TM;
 
   if (MODE == MODE_LSE && ep.ctrl && ep.ctrl->converged) {
     // Identity step: the solve already stopped; keep buffers consistent.
@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(NT) simt_pv_kernel(StreamArgs s, PvArgs p) {
   __shared__ float cs_s[TN];
 
   const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
-  const int row0 = blockIdx.x * TM;
+  const int row0 = s.row_begin + blockIdx.x * TM;
   const int dv0 = blockIdx.y * 64;
 
   const float inv_eps = 1.0f / s.eps;
@@ -321,22 +321,22 @@ __global__ void __launch_bounds__(NT) simt_pv_kernel(StreamArgs s, PvArgs p) {
 }  // namespace
 
 cudaError_t simt_lse(const StreamArgs& s, const LseEpilogue& e, cudaStream_t st) {
-  if (s.nr <= 0) return cudaSuccess;
-  dim3 grid((s.nr + TM - 1) / TM);
+  if (s.nr - s.row_begin <= 0) return cudaSuccess;
+  dim3 grid((s.nr - s.row_begin + TM - 1) / TM);
   simt_stream_kernel<MODE_LSE><<<grid, NT, 0, st>>>(s, e, VecArgs{});
   return cudaGetLastError();
 }
 
 cudaError_t simt_vec(const StreamArgs& s, const VecArgs& v, cudaStream_t st) {
-  if (s.nr <= 0) return cudaSuccess;
-  dim3 grid((s.nr + TM - 1) / TM);
+  if (s.nr - s.row_begin <= 0) return cudaSuccess;
+  dim3 grid((s.nr - s.row_begin + TM - 1) / TM);
   simt_stream_kernel<MODE_VEC><<<grid, NT, 0, st>>>(s, LseEpilogue{}, v);
   return cudaGetLastError();
 }
 
 cudaError_t simt_pv(const StreamArgs& s, const PvArgs& p, cudaStream_t st) {
-  if (s.nr <= 0 || p.dv <= 0) return cudaSuccess;
-  dim3 grid((s.nr + TM - 1) / TM, (p.dv + 63) / 64);
+  if (s.nr - s.row_begin <= 0 || p.dv <= 0) return cudaSuccess;
+  dim3 grid((s.nr - s.row_begin + TM - 1) / TM, (p.dv + 63) / 64);
   if (p.rows2)
     simt_pv_kernel<true><<<grid, NT, 0, st>>>(s, p);
   else

@@ -218,7 +218,8 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
 }
 
 struct KernelParams {
-  int nr, nc;        // valid rows / columns
+  int nr, nc;        // end of the row range / valid columns
+  int row_begin;     // first row of the range (row sharding)
   int ntiles;        // column tiles of BN
   int nfull, ntail;  // K blocks: nfull of 32 floats (128B swizzle) + ntail of 8 floats (32B swizzle)
   int nstage;
@@ -244,7 +245,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
               const KernelParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = blockIdx.x * (128 * NHALF);
+  const int row0 = p.row_begin + blockIdx.x * (128 * NHALF);
   const int t0 = blockIdx.y * p.tiles_per_chunk;
   const int nt = (p.ntiles - t0 < p.tiles_per_chunk) ? (p.ntiles - t0) : p.tiles_per_chunk;
   const bool split = gridDim.y > 1;
@@ -549,6 +550,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
 // One CTA = 128 rows; TMEM columns: [0, 2*WCOLS) two S/W buffers, then DV_PAD columns of O.
 struct PvKernelParams {
   int nr, nc, ntiles, nfull, ntail, nstage;
+  int row_begin;         // rows [row_begin, nr) are produced
   int dv, dv_pad, dv0;   // real width, padded slice width (multiple of 32, <= 256), first column of this slice
   int ld_out;            // row pitch of out (= full dv of the problem)
   float scale2, eps;
@@ -596,7 +598,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
              const PvKernelParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = blockIdx.x * 128;
+  const int row0 = p.row_begin + blockIdx.x * 128;
   constexpr int WCOLS = SPLIT ? 2 * BN : BN;  // TMEM columns per S/W buffer (Wl lives right after Wh)
   constexpr int NV = SPLIT ? 2 : 1;
 
@@ -971,9 +973,9 @@ cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUten
 }
 
 // Merges the per-chunk (scaled max, sum) pairs of a column-split LSE pass and applies the epilogue.
-__global__ void lse_combine_kernel(int nr, int nchunk, const float* __restrict__ pm, const float* __restrict__ ps,
-                                   int stride, float eps, LseEpilogue ep) {
-  int r = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void lse_combine_kernel(int row_begin, int nr, int nchunk, const float* __restrict__ pm,
+                                   const float* __restrict__ ps, int stride, float eps, LseEpilogue ep) {
+  int r = row_begin + blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= nr) return;
   if (ep.ctrl && ep.ctrl->converged) {
     if (ep.old && ep.out) ep.out[r] = ep.old[r];
@@ -1044,7 +1046,7 @@ size_t staged_bytes(int n, int m, int d, int prec) {
 }
 
 cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
-                  cudaStream_t st) {
+                  cudaStream_t st, bool run_kernels) {
   Shape sh = plan_shape(d, prec);
   if (!sh.ok) return cudaErrorNotSupported;
   s.d = d; s.kc = sh.kc; s.kp = sh.kp; s.prec = prec;
@@ -1059,8 +1061,9 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
     o.opA = reinterpret_cast<float*>(p); p += bytes;
     o.opB = reinterpret_cast<float*>(p); p += bytes;
     size_t total = (size_t)o.rows_pad * sh.kp;
-    stage_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src[c], o.rows, o.rows_pad, d, sh.kc, sh.kp, prec,
-                                                                  o.opA, o.opB);
+    if (run_kernels)
+      stage_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src[c], o.rows, o.rows_pad, d, sh.kc, sh.kp, prec,
+                                                                    o.opA, o.opB);
   }
   s.part_stride = pad256(n > m ? n : m);
   s.part_m = reinterpret_cast<float*>(p);
@@ -1088,12 +1091,13 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
   ok &= encode_map(&mb_t, colc.opB, colc.rows_pad, sh.kp, 8, sh.bn, CU_TENSOR_MAP_SWIZZLE_32B);
   if (!ok) return cudaErrorInvalidValue;
   KernelParams kp;
-  kp.nr = a.nr; kp.nc = a.nc;
+  kp.nr = a.nr; kp.nc = a.nc; kp.row_begin = a.row_begin;
   kp.ntiles = (a.nc + sh.bn - 1) / sh.bn;
   kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nstage = sh.nstage;
   kp.scale2 = scale2; kp.eps = a.eps; kp.ep = e;
   const int bm = 128 * sh.nhalf;
-  const int nblk = (a.nr + bm - 1) / bm;
+  const int nblk = (a.nr - a.row_begin + bm - 1) / bm;
+  if (nblk <= 0) return cudaSuccess;
   const int chunks = pick_chunks(nblk, kp.ntiles);
   kp.tiles_per_chunk = (kp.ntiles + chunks - 1) / chunks;
   kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride;
@@ -1103,7 +1107,8 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
   else if (sh.bn == 128) err = launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   else err = launch<1, 64>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   if (err != cudaSuccess || chunks == 1) return err;
-  lse_combine_kernel<<<(a.nr + 255) / 256, 256, 0, st>>>(a.nr, chunks, s.part_m, s.part_s, s.part_stride, a.eps, e);
+  lse_combine_kernel<<<(a.nr - a.row_begin + 255) / 256, 256, 0, st>>>(a.row_begin, a.nr, chunks, s.part_m, s.part_s,
+                                                                       s.part_stride, a.eps, e);
   return cudaGetLastError();
 }
 
@@ -1188,14 +1193,15 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa,
   ok &= encode_map(&maps[5], ps.split ? vt_lo : vt_hi, vrows, vcols, 32, ps.dv_pad, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return cudaErrorInvalidValue;
   PvKernelParams kp;
-  kp.nr = a.nr; kp.nc = a.nc;
+  kp.nr = a.nr; kp.nc = a.nc; kp.row_begin = a.row_begin;
   kp.ntiles = (a.nc + ps.bn - 1) / ps.bn;
   kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nstage = ps.nstage;
   kp.dv = pa.dv; kp.dv_pad = ps.dv_pad; kp.ld_out = pa.dv;
   kp.scale2 = scale2; kp.eps = a.eps; kp.R = pa.R; kp.epilogue = pa.epilogue;
   kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.roww = pa.roww; kp.gs = pa.gs; kp.coef = pa.coef;
   kp.rows_raw = a.rows; kp.ld_rows = a.d; kp.out = pa.out;
-  const int grid = (a.nr + 127) / 128;
+  const int grid = (a.nr - a.row_begin + 127) / 128;
+  if (grid <= 0) return cudaSuccess;
   for (int sl = 0; sl < ps.nslices; ++sl) {
     kp.dv0 = sl * ps.dv_pad;
     cudaError_t e = ps.split ? launch_pv<64, true>(maps, kp, grid, ps.smem, st)

@@ -28,8 +28,10 @@ struct Staged {
 
 bool supported(int n, int m, int d, int prec);
 size_t staged_bytes(int n, int m, int d, int prec);
+// run_kernels = false only lays out the pointers inside `buf` (operands staged there by an earlier call
+// with the same sizes are re-used: row-sharded solvers stage once and step many times).
 cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
-                  cudaStream_t st);
+                  cudaStream_t st, bool run_kernels = true);
 // One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st);
 

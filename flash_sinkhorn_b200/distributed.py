@@ -1,0 +1,169 @@
+"""Row-sharded (multi-GPU) symmetric Sinkhorn: one process per GPU, ``torch.distributed`` collectives.
+
+The reference package is single-GPU. Here every rank holds the full clouds, weights and potentials
+(they are O((n+m) d)); the n x m work of every step is split by rows: rank r produces rows
+``[r*shard_f, (r+1)*shard_f)`` of the new f and the matching slice of the new g, then the slices are
+all-gathered (two in-place all-gathers of n resp. m floats per step, NCCL over NVLink on GPUs).
+Because every rank then holds identical full vectors, early-stop decisions are identical everywhere
+without a further collective, and results are bit-identical to the single-GPU engine (same kernels,
+same per-row arithmetic).
+
+The loop itself (:func:`run_symmetric_sharded`) is engine-agnostic - it gets the step and the gather
+as callables - so it is unit-tested on CPU with ``gloo`` against the dense oracle.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Callable, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+SHARD_ALIGN = 256  # rows; keeps every shard on the kernels' row-block grid
+
+
+def shard_layout(rows: int, world: int, align: int = SHARD_ALIGN) -> int:
+    """Rows per rank (same on all ranks, multiple of ``align``; the last shards may be short or empty)."""
+    per = -(-rows // world)
+    return -(-per // align) * align
+
+
+def shard_range(rows: int, world: int, rank: int, align: int = SHARD_ALIGN) -> Tuple[int, int]:
+    shard = shard_layout(rows, world, align)
+    return min(rows, rank * shard), min(rows, (rank + 1) * shard)
+
+
+def run_symmetric_sharded(
+    n: int,
+    m: int,
+    f_hat0: torch.Tensor,
+    g_hat0: torch.Tensor,
+    eps_list: Sequence[float],
+    *,
+    last_extrapolation: bool,
+    threshold: Optional[float],
+    check_every: int,
+    world: int,
+    rank: int,
+    step_fn: Callable,
+    gather_fn: Callable,
+):
+    """Symmetric schedule (init step, averaged loop, optional extrapolation) over sharded steps.
+
+    ``step_fn(f_old, g_old, f_new, g_new, eps, w, (f_lo, f_hi, g_lo, g_hi))`` must fill rows
+    ``[f_lo, f_hi)`` of ``f_new`` and ``[g_lo, g_hi)`` of ``g_new`` from the full old potentials.
+    ``gather_fn(buf, shard)`` all-gathers ``buf`` in place (rank r owns ``buf[r*shard:(r+1)*shard]``).
+    Buffers are padded to ``world*shard`` entries. Returns ``(f_hat, g_hat, f_hat_pre, g_hat_pre, steps)``.
+    """
+    sf, sg = shard_layout(n, world), shard_layout(m, world)
+    f_lo, f_hi = shard_range(n, world, rank)
+    g_lo, g_hi = shard_range(m, world, rank)
+    mk = lambda size, src: torch.zeros(size, dtype=src.dtype, device=src.device)
+    f = [mk(world * sf, f_hat0), mk(world * sf, f_hat0)]
+    g = [mk(world * sg, g_hat0), mk(world * sg, g_hat0)]
+    f[0][:n].copy_(f_hat0)
+    g[0][:m].copy_(g_hat0)
+    cur = 0
+
+    def step(eps, w):
+        nonlocal cur
+        step_fn(f[cur], g[cur], f[cur ^ 1], g[cur ^ 1], float(eps), float(w), (f_lo, f_hi, g_lo, g_hi))
+        gather_fn(f[cur ^ 1], sf)
+        gather_fn(g[cur ^ 1], sg)
+        cur ^= 1
+
+    steps = 0
+    step(eps_list[0], 1.0)
+    steps += 1
+    prev = None
+    for i, eps in enumerate(eps_list):
+        step(eps, 0.5)
+        steps += 1
+        if threshold is not None and (i + 1) % check_every == 0:
+            if prev is None:
+                prev = (f[cur][:n].clone(), g[cur][:m].clone())
+            else:
+                change = max(float((f[cur][:n] - prev[0]).abs().max()), float((g[cur][:m] - prev[1]).abs().max()))
+                if change < threshold:  # identical on all ranks: the vectors are
+                    break
+                prev[0].copy_(f[cur][:n])
+                prev[1].copy_(g[cur][:m])
+    f_pre = g_pre = None
+    if last_extrapolation:
+        f_pre, g_pre = f[cur][:n].clone(), g[cur][:m].clone()
+        step(eps_list[-1], 1.0)
+        steps += 1
+    return f[cur][:n].clone(), g[cur][:m].clone(), f_pre, g_pre, steps
+
+
+def _gather_inplace(group):
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+
+    def gather(buf: torch.Tensor, shard: int):
+        dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard], group=group)
+
+    return gather, world, rank
+
+
+def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, rho_y, last_extrapolation,
+                            threshold, check_every, f_init, g_init, prec, group):
+    """CUDA engine behind :func:`run_symmetric_sharded`. Returns standard potentials like the 1-GPU solver."""
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels._common import dampening
+
+    n, d = x.shape
+    m = y.shape[0]
+    dev = x.device
+    alpha = cost_scale * x.pow(2).sum(dim=1)
+    beta = cost_scale * y.pow(2).sum(dim=1)
+    f0 = (f_init.float() - alpha) if f_init is not None else -alpha
+    g0 = (g_init.float() - beta) if g_init is not None else -beta
+    ws = _lib.workspace(_lib.OP_STEP, n, m, d, prec, dev)
+    state = {"staged": False}
+    gather, world, rank = _gather_inplace(group)
+
+    def step_fn(f_old, g_old, f_new, g_new, eps, w, rng):
+        df, dg = dampening(eps, rho_x), dampening(eps, rho_y)
+        _lib.call(
+            "fs_symmetric_step_range", dev,
+            _lib.ptr(x), _lib.ptr(y), n, m, d, _lib.ptr(f_old), _lib.ptr(g_old), _lib.ptr(log_a), _lib.ptr(log_b),
+            _lib.ptr(f_new), _lib.ptr(g_new), _lib.ptr(alpha), _lib.ptr(beta),
+            eps, w, df, dg, float(cost_scale), rng[0], rng[1], rng[2], rng[3], 0 if state["staged"] else 1,
+            prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+        )
+        state["staged"] = True
+
+    fh, gh, fp, gp, steps = run_symmetric_sharded(
+        n, m, f0, g0, eps_list, last_extrapolation=last_extrapolation, threshold=threshold,
+        check_every=check_every, world=world, rank=rank, step_fn=step_fn, gather_fn=gather)
+    out_pre = (None, None) if fp is None else (fp + alpha, gp + beta)
+    return fh + alpha, gh + beta, out_pre[0], out_pre[1], steps
+
+
+def grad_sharded(x, y, a, b, log_a, log_b, f, g, grad_scale, eps, cost_scale, prec, want_x, want_y, group):
+    """Row-sharded analytic gradient: each rank computes its rows, slices are all-gathered."""
+    from flash_sinkhorn_b200 import _lib
+
+    n, d = x.shape
+    m = y.shape[0]
+    dev = x.device
+    gather, world, rank = _gather_inplace(group)
+    sx, sy = shard_layout(n, world), shard_layout(m, world)
+    x_lo, x_hi = shard_range(n, world, rank)
+    y_lo, y_hi = shard_range(m, world, rank)
+    gx = torch.zeros((world * sx, d), device=dev, dtype=torch.float32) if want_x else None
+    gy = torch.zeros((world * sy, d), device=dev, dtype=torch.float32) if want_y else None
+    ws = _lib.workspace(_lib.OP_GRAD, n, m, d, prec, dev)
+    _lib.call(
+        "fs_grad_range", dev,
+        _lib.ptr(x), _lib.ptr(y), n, m, d, _lib.ptr(a), _lib.ptr(b), _lib.ptr(log_a), _lib.ptr(log_b),
+        _lib.ptr(f), _lib.ptr(g), _lib.ptr(grad_scale), _lib.ptr(gx), _lib.ptr(gy),
+        float(eps), float(cost_scale), x_lo, x_hi, y_lo, y_hi, prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+    )
+    if want_x:
+        gather(gx.view(-1), sx * d)
+        gx = gx[:n]
+    if want_y:
+        gather(gy.view(-1), sy * d)
+        gy = gy[:m]
+    return gx, gy

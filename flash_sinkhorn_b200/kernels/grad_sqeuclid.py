@@ -40,6 +40,7 @@ def sinkhorn_geomloss_online_grad_sqeuclid(
     label_cost_matrix: Optional[torch.Tensor] = None,
     lambda_x: float = 1.0,
     lambda_y: float = 0.0,
+    process_group=None,
 ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
     """``grad_x_i = 2*cs*grad_scale*a_i*(x_i - ybar_i)`` and the symmetric ``grad_y``.
 
@@ -79,6 +80,10 @@ def sinkhorn_geomloss_online_grad_sqeuclid(
             raise ValueError("grad_scale must be on the same device as x.")
         gs = _lib.f32c(grad_scale.detach().reshape(1))
     prec = _lib.precision_id(allow_tf32)
+    if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
+        from flash_sinkhorn_b200.distributed import grad_sharded  # rows sharded over the ranks, then all-gathered
+        return grad_sharded(x32, y32, a32, b32, la, lb, f32, g32, gs, float(eps), float(cost_scale), prec,
+                            bool(compute_grad_x), bool(compute_grad_y), process_group)
     gx = torch.empty((n, d), device=dev, dtype=torch.float32) if compute_grad_x else None
     gy = torch.empty((m, d), device=dev, dtype=torch.float32) if compute_grad_y else None
     ws = _lib.workspace(_lib.OP_GRAD, n, m, d, prec, dev)

@@ -160,6 +160,7 @@ class SamplesLoss(torch.nn.Module):
         threshold: Optional[float] = None,
         inner_iterations: int = 10,
         use_flashstyle: Optional[bool] = None,
+        process_group=None,
     ):
         super().__init__()
         if use_flashstyle is not None and not use_flashstyle:
@@ -230,6 +231,9 @@ class SamplesLoss(torch.nn.Module):
         self.lambda_x, self.lambda_y = float(lambda_x), float(lambda_y)
         self.threshold = None if threshold is None else float(threshold)
         self.inner_iterations = int(inner_iterations)
+        # Extension (no reference counterpart): torch.distributed group, one rank per GPU; the symmetric
+        # solver and the gradient shard their rows over it. Every rank must call with the same inputs.
+        self.process_group = process_group
 
     def _make_config(self) -> _SinkhornConfig:
         return _SinkhornConfig(
@@ -243,7 +247,7 @@ class SamplesLoss(torch.nn.Module):
             hvp_cg_stabilise_every=self.hvp_cg_stabilise_every, hvp_preconditioner=self.hvp_preconditioner,
             hvp_precond_terms=self.hvp_precond_terms, hvp_use_preconditioner=self.hvp_use_preconditioner,
             lambda_x=self.lambda_x, lambda_y=self.lambda_y, threshold=self.threshold,
-            inner_iterations=self.inner_iterations,
+            inner_iterations=self.inner_iterations, process_group=self.process_group,
         )
 
     def _eps_list_for_inputs(self, x: torch.Tensor, y: torch.Tensor) -> Sequence[float]:
@@ -275,7 +279,7 @@ class SamplesLoss(torch.nn.Module):
             rho_x=self.rho_x, rho_y=self.rho_y, last_extrapolation=self.last_extrapolation,
             label_x=label_x, label_y=label_y, label_cost_matrix=self.label_cost_matrix,
             lambda_x=self.lambda_x, lambda_y=self.lambda_y,
-            threshold=self.threshold, check_every=self.inner_iterations,
+            threshold=self.threshold, check_every=self.inner_iterations, process_group=self.process_group,
         )
 
     def forward(self, *args, label_x: Optional[torch.Tensor] = None, label_y: Optional[torch.Tensor] = None):

@@ -172,8 +172,15 @@ def sinkhorn_flashstyle_symmetric(
     label_cost_matrix: Optional[torch.Tensor] = None,
     lambda_x: float = 1.0,
     lambda_y: float = 0.0,
+    process_group=None,
 ):
     """GeomLoss-style symmetric Sinkhorn (Jacobi steps averaged with weight 1/2).
+
+    ``process_group`` (extension, no reference counterpart): a ``torch.distributed`` group with one
+    rank per GPU. Every rank passes the same full inputs; the rows of each step are sharded over
+    the ranks and all-gathered (see :mod:`flash_sinkhorn_b200.distributed`). Results are identical
+    on all ranks.
+
 
     Step sequence: one full step at ``eps_list[0]``, one averaged step per schedule entry,
     and (``last_extrapolation``) one full step at the last eps. Returns standard potentials
@@ -209,6 +216,20 @@ def sinkhorn_flashstyle_symmetric(
     fi = None if f_init is None else _lib.f32c(f_init)
     gi = None if g_init is None else _lib.f32c(g_init)
     prec = _lib.precision_id(allow_tf32)
+
+    if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
+        from flash_sinkhorn_b200.distributed import symmetric_solve_sharded
+
+        f, g, f_pre, g_pre, steps = symmetric_solve_sharded(
+            x32, y32, log_a, log_b, list(eps_list), cost_scale=float(cost_scale), rho_x=rho_x, rho_y=rho_y,
+            last_extrapolation=bool(last_extrapolation), threshold=threshold, check_every=int(check_every),
+            f_init=fi, g_init=gi, prec=prec, group=process_group)
+        out = (f, g)
+        if return_prelast and last_extrapolation:
+            out = out + (f_pre, g_pre)
+        if return_n_iters:
+            out = out + (int(steps),)
+        return out
 
     f = torch.empty((n,), device=dev, dtype=torch.float32)
     g = torch.empty((m,), device=dev, dtype=torch.float32)

@@ -114,6 +114,29 @@ int fs_symmetric_step(const float* x, const float* y, int n, int m, int d,
                       float eps, float w, float damp_f, float damp_g, float cost_scale,
                       int prec, void* ws, size_t ws_bytes, void* stream);
 
+/* Row-sharded form of fs_symmetric_step for multi-GPU solves (no reference counterpart: the
+ * reference is single-GPU). Only rows [f_begin, f_end) of f_out and [g_begin, g_end) of g_out are
+ * computed; all inputs are full-size and replicated on every rank, the caller all-gathers the
+ * produced slices. `restage` = 0 re-uses the tensor-core operands that an earlier call with the
+ * same (x, y, n, m, d, prec) staged into the SAME workspace (x, y constant over a solve), so a
+ * step costs only the two streaming passes. */
+int fs_symmetric_step_range(const float* x, const float* y, int n, int m, int d,
+                            const float* f_hat, const float* g_hat,
+                            const float* log_a, const float* log_b,
+                            float* f_out, float* g_out,
+                            const float* alpha_x, const float* beta_y,
+                            float eps, float w, float damp_f, float damp_g, float cost_scale,
+                            int f_begin, int f_end, int g_begin, int g_end, int restage,
+                            int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* Row-sharded form of fs_grad: rows [x_begin, x_end) of grad_x and [y_begin, y_end) of grad_y. */
+int fs_grad_range(const float* x, const float* y, int n, int m, int d,
+                  const float* a, const float* b, const float* log_a, const float* log_b,
+                  const float* f, const float* g, const float* grad_scale,
+                  float* grad_x, float* grad_y, float eps, float cost_scale,
+                  int x_begin, int x_end, int y_begin, int y_end,
+                  int prec, void* ws, size_t ws_bytes, void* stream);
+
 /* Whole symmetric (GeomLoss-style) solve, enqueued without host synchronisation.
  * Schedule: one step with weight 1 at eps_list[0]; one step with weight 1/2 per
  * entry of eps_list; if last_extrapolation, one more step with weight 1 at
