@@ -9,7 +9,7 @@ without a further collective, and results are bit-identical to the single-GPU en
 same per-row arithmetic).
 
 The loop itself (:func:`run_symmetric_sharded`) is engine-agnostic - it gets the step and the gather
-as callables - so it is unit-tested on CPU with ``gloo`` against the dense oracle.
+as callables - so it is unit-tested on CPU with ``gloo`` and a dense CPU step function.
 """
 from __future__ import annotations
 
