@@ -60,6 +60,8 @@ def test_sharded_two_gpu_equals_single_gpu(tmp_path):
         for r in range(world):
             z = np.load(tmp_path / f"r{r}_{int(tf32)}.npz")
             assert abs(float(z["loss"]) - val.item()) <= 1e-5 * abs(val.item())
-            assert np.abs(z["gx"] - want).max() <= 1e-4 * np.abs(want).max()
+            # same kernels, but the column split (hence the merge order of partial sums) depends on the
+            # number of row blocks per rank: agreement is to rounding, amplified by the solve
+            assert np.abs(z["gx"] - want).max() <= (2e-3 if tf32 else 2e-4) * np.abs(want).max()
         z0, z1 = (np.load(tmp_path / f"r{r}_{int(tf32)}.npz") for r in range(2))
         assert np.array_equal(z0["gx"], z1["gx"])  # all ranks hold identical results
