@@ -51,8 +51,11 @@ def run_symmetric_sharded(
     """Symmetric schedule (init step, averaged loop, optional extrapolation) over sharded steps.
 
     ``step_fn(f_old, g_old, f_new, g_new, eps, w, (f_lo, f_hi, g_lo, g_hi))`` must fill rows
-    ``[f_lo, f_hi)`` of ``f_new`` and ``[g_lo, g_hi)`` of ``g_new`` from the full old potentials.
-    ``gather_fn(buf, shard)`` all-gathers ``buf`` in place (rank r owns ``buf[r*shard:(r+1)*shard]``).
+    ``[f_lo, f_hi)`` of ``f_new`` and ``[g_lo, g_hi)`` of ``g_new`` from the full old potentials; it is
+    called twice per step, first with an empty g range, then with an empty f range, so that the
+    gather of the new f slices can overlap the g half (both halves read only OLD potentials).
+    ``gather_fn(buf, shard)`` all-gathers ``buf`` in place (rank r owns ``buf[r*shard:(r+1)*shard]``)
+    and may return a callable that waits for completion (asynchronous gather) or None.
     Buffers are padded to ``world*shard`` entries. Returns ``(f_hat, g_hat, f_hat_pre, g_hat_pre, steps)``.
     """
     sf, sg = shard_layout(n, world), shard_layout(m, world)
@@ -64,13 +67,30 @@ def run_symmetric_sharded(
     f[0][:n].copy_(f_hat0)
     g[0][:m].copy_(g_hat0)
     cur = 0
+    pending = {"f": None, "g": None}  # waits for the (asynchronous) gathers that fill f[cur] / g[cur]
+    parity = 0
+
+    def settle(*sides):
+        for sd in sides:
+            if pending[sd] is not None:
+                pending[sd]()
+                pending[sd] = None
 
     def step(eps, w):
-        nonlocal cur
-        step_fn(f[cur], g[cur], f[cur ^ 1], g[cur ^ 1], float(eps), float(w), (f_lo, f_hi, g_lo, g_hi))
-        gather_fn(f[cur ^ 1], sf)
-        gather_fn(g[cur ^ 1], sg)
+        # The half that produces new f needs the complete current g and vice versa. Alternating which
+        # half goes first lets BOTH gathers hide behind a compute half: the gather launched last in one
+        # step is only needed by the second half of the next step.
+        nonlocal cur, parity
+        launched = {}
+        for side in (("f", "g") if parity == 0 else ("g", "f")):
+            settle("g" if side == "f" else "f")
+            rng = (f_lo, f_hi, g_lo, g_lo) if side == "f" else (f_lo, f_lo, g_lo, g_hi)
+            step_fn(f[cur], g[cur], f[cur ^ 1], g[cur ^ 1], float(eps), float(w), rng)
+            launched[side] = gather_fn(f[cur ^ 1], sf) if side == "f" else gather_fn(g[cur ^ 1], sg)
+        settle("f", "g")  # nothing should be left; keeps the invariant obvious
+        pending.update(launched)
         cur ^= 1
+        parity ^= 1
 
     steps = 0
     step(eps_list[0], 1.0)
@@ -80,6 +100,7 @@ def run_symmetric_sharded(
         step(eps, 0.5)
         steps += 1
         if threshold is not None and (i + 1) % check_every == 0:
+            settle("f", "g")
             if prev is None:
                 prev = (f[cur][:n].clone(), g[cur][:m].clone())
             else:
@@ -90,17 +111,34 @@ def run_symmetric_sharded(
                 prev[1].copy_(g[cur][:m])
     f_pre = g_pre = None
     if last_extrapolation:
+        settle("f", "g")
         f_pre, g_pre = f[cur][:n].clone(), g[cur][:m].clone()
         step(eps_list[-1], 1.0)
         steps += 1
+    settle("f", "g")
     return f[cur][:n].clone(), g[cur][:m].clone(), f_pre, g_pre, steps
 
 
-def _gather_inplace(group):
+def _gather_inplace(group, overlap: bool = False):
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    side = torch.cuda.Stream() if overlap else None
 
     def gather(buf: torch.Tensor, shard: int):
-        dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard], group=group)
+        if side is None:
+            dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard], group=group)
+            return None
+        # Run the collective on a side stream ordered after the kernels enqueued so far; the caller's
+        # stream only waits for it when the returned callable is invoked.
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard], group=group)
+            done = torch.cuda.Event()
+            done.record(side)
+        buf.record_stream(side)
+        return lambda: main.wait_event(done)
 
     return gather, world, rank
 
@@ -120,7 +158,7 @@ def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, 
     g0 = (g_init.float() - beta) if g_init is not None else -beta
     ws = _lib.workspace(_lib.OP_STEP, n, m, d, prec, dev)
     state = {"staged": False}
-    gather, world, rank = _gather_inplace(group)
+    gather, world, rank = _gather_inplace(group, overlap=True)
 
     def step_fn(f_old, g_old, f_new, g_new, eps, w, rng):
         df, dg = dampening(eps, rho_x), dampening(eps, rho_y)
