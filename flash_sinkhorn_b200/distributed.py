@@ -19,7 +19,7 @@ from typing import Callable, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-SHARD_ALIGN = 256  # rows; keeps every shard on the kernels' row-block grid
+SHARD_ALIGN = 128  # rows; shards start on the kernels' 128-row half-block grid
 
 
 def shard_layout(rows: int, world: int, align: int = SHARD_ALIGN) -> int:
@@ -122,6 +122,9 @@ def run_symmetric_sharded(
 def _gather_inplace(group, overlap: bool = False):
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     side = torch.cuda.Stream() if overlap else None
+    # a small ring of re-used events (at most two gathers are in flight at any time)
+    events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in range(8)] if overlap else []
+    state = {"i": 0}
 
     def gather(buf: torch.Tensor, shard: int):
         if side is None:
@@ -130,14 +133,13 @@ def _gather_inplace(group, overlap: bool = False):
         # Run the collective on a side stream ordered after the kernels enqueued so far; the caller's
         # stream only waits for it when the returned callable is invoked.
         main = torch.cuda.current_stream()
-        ready = torch.cuda.Event()
+        ready, done = events[state["i"] % len(events)]
+        state["i"] += 1
         ready.record(main)
+        side.wait_event(ready)
         with torch.cuda.stream(side):
-            side.wait_event(ready)
             dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard], group=group)
-            done = torch.cuda.Event()
-            done.record(side)
-        buf.record_stream(side)
+        done.record(side)
         return lambda: main.wait_event(done)
 
     return gather, world, rank
