@@ -188,10 +188,23 @@ struct Problem {
     if (use_tc) return tc::lse(staged, side, s, ep, st);
     return simt_lse(s, ep, st);
   }
-  cudaError_t vec(int side, const float* pot, const float* logw, float eps, const VecArgs& v) const {
+  // Weighted pass. With a row normaliser R (log2 LSE of the same scores, from lse()) and the tensor-core
+  // engine available it runs as a one-column matrix pass on tcgen05; otherwise on the CUDA-core engine.
+  cudaError_t vec(int side, const float* pot, const float* logw, float eps, const VecArgs& v,
+                  const float* R = nullptr) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
     g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (vec_on_tc() && R) {
+      PvArgs pa;
+      pa.R = R; pa.V = v.v; pa.dv = 1; pa.epilogue = PV_APPLY;
+      pa.rowpot = v.rowpot; pa.rowlogw = v.rowlogw; pa.out = v.out; pa.skip = v.skip;
+      return tc::pv(staged, side, s, pa, pv_scratch, st);
+    }
     return simt_vec(s, v, st);
+  }
+  bool vec_on_tc() const {
+    return use_tc && pv_scratch && !csr_rp[0] && tc::pv_supported(d, prec, 1) &&
+           tc::pv_scratch_bytes(n > m ? n : m, d, prec, 1) <= pv_scratch_bytes;
   }
   cudaError_t pv(int side, const float* pot, const float* logw, float eps, const PvArgs& p) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
@@ -300,7 +313,8 @@ size_t fs_workspace_bytes(int op, int n, int m, int d, int prec) {
   Ws ws(nullptr, 0);
   Problem p;
   const bool matrix_op = (op == FS_OP_APPLY_MAT || op == FS_OP_GRAD);
-  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true, matrix_op ? d : 0);
+  const bool vector_op = (op == FS_OP_APPLY_VEC || op == FS_OP_SCHUR);
+  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true, matrix_op ? d : (vector_op ? 1 : 0));
   size_t nm = (size_t)(n > m ? n : m);
   switch (op) {
     case FS_OP_LSE:
@@ -332,6 +346,8 @@ size_t fs_workspace_bytes(int op, int n, int m, int d, int prec) {
       ws.take<float>(16);
       for (int i = 0; i < 3; ++i) ws.take<float>(m);
       ws.take<float>(n);
+      ws.take<float>(n);
+      ws.take<float>(m);
       break;
     default:
       return 0;
@@ -541,16 +557,24 @@ int fs_apply_vec(const float* x, const float* y, int n, int m, int d, const floa
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, 1));
+  float* R = ws.take<float>(n > m ? n : m);
+  if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
   VecArgs v;
   v.v = vec; v.out = out;
-  if (axis == 1) {
-    v.rowpot = f_hat; v.rowlogw = log_a;
-    FS_CUDA(p.vec(0, g_hat, log_b, eps, v));
-  } else {
-    v.rowpot = g_hat; v.rowlogw = log_b;
-    FS_CUDA(p.vec(1, f_hat, log_a, eps, v));
+  const int side = axis == 1 ? 0 : 1;
+  const float* cpot = side == 0 ? g_hat : f_hat;
+  const float* clw = side == 0 ? log_b : log_a;
+  v.rowpot = side == 0 ? f_hat : g_hat;
+  v.rowlogw = side == 0 ? log_a : log_b;
+  const float* Rp = nullptr;
+  if (p.vec_on_tc()) {  // normaliser pass first, then the weighted pass re-uses the same scores
+    LseEpilogue ep;
+    ep.lse2 = R;
+    FS_CUDA(p.lse(side, cpot, clw, eps, ep));
+    Rp = R;
   }
+  FS_CUDA(p.vec(side, cpot, clw, eps, v, Rp));
   return FS_OK;
 }
 
@@ -862,22 +886,32 @@ extern "C" int fs_schur_cg(const float* x, const float* y, int n, int m, int d, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, 1));
   CgState* s = reinterpret_cast<CgState*>(ws.take<float>(16));
   float* r = ws.take<float>(m);
   float* pv = ws.take<float>(m);
   float* q = ws.take<float>(m);
   float* t = ws.take<float>(n);
+  float* R_row = ws.take<float>(n);
+  float* R_col = ws.take<float>(m);
   if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+  const bool on_tc = p.vec_on_tc();
+  if (on_tc) {  // the potentials are fixed during CG: both normalisers are computed once
+    LseEpilogue e0, e1;
+    e0.lse2 = R_row;
+    e1.lse2 = R_col;
+    FS_CUDA(p.lse(0, g_hat, log_b, eps, e0));
+    FS_CUDA(p.lse(1, f_hat, log_a, eps, e1));
+  }
   cg_init_kernel<<<1, 1024, 0, st>>>(m, rhs, z, r, pv, s, rtol, atol);
   for (int it = 0; it < max_iter; ++it) {
     VecArgs v1;
     v1.v = pv; v1.rowpot = f_hat; v1.rowlogw = log_a; v1.out = t; v1.skip = &s->done;
-    FS_CUDA(p.vec(0, g_hat, log_b, eps, v1));
+    FS_CUDA(p.vec(0, g_hat, log_b, eps, v1, on_tc ? R_row : nullptr));
     cg_div_kernel<<<g1(n), 256, 0, st>>>(n, t, diag_x, t, s);
     VecArgs v0;
     v0.v = t; v0.rowpot = g_hat; v0.rowlogw = log_b; v0.out = q; v0.skip = &s->done;
-    FS_CUDA(p.vec(1, f_hat, log_a, eps, v0));
+    FS_CUDA(p.vec(1, f_hat, log_a, eps, v0, on_tc ? R_col : nullptr));
     cg_update_kernel<<<1, 1024, 0, st>>>(m, denom, q, z, r, pv, s, it);
   }
   cg_finish_kernel<<<1, 1, 0, st>>>(s, info, max_iter);

@@ -85,6 +85,7 @@ struct PvArgs {
   const float* gs = nullptr;       // device scalar or nullptr
   float coef = 1.f;
   float* out = nullptr;            // [nr, dv]
+  const int* skip = nullptr;       // device flag: non-zero => the pass is a no-op (finished CG)
 };
 
 // --- CUDA-core engine (fs_simt.cu) ---

@@ -63,17 +63,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or about
+// `ns` nanoseconds pass, so a waiting single-lane role neither burns issue slots nor wakes up late.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait. Returns false (and raises *abort_flag) if the budget runs out or another
-// thread of the CTA already aborted.
-// `backoff_ns` > 0 puts the polling thread to sleep between polls: the single-thread producer / MMA roles
-// spend most of their time waiting and must not steal issue slots from the soft-max warps of their scheduler.
+// thread of the CTA already aborted. `park_ns` > 0 selects the parking form of try_wait (producer / MMA
+// lanes, which spend most of their time waiting and share a scheduler with soft-max warps).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned backoff_ns = 0) {
+                                          unsigned park_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    if (backoff_ns) __nanosleep(backoff_ns);
-    if (mbar_try_wait(bar, parity)) return true;
+    if (park_ns ? mbar_try_wait_hint(bar, parity, park_ns) : mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kSpinLimit) {
       *abort_flag = 1;
@@ -317,7 +328,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       for (int j = 0; j < nt; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 64)) break;
+        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
         mbar_expect_tx(bar(B_FULL + s), b_stage_bytes);
         uint32_t dst = smem_u32(b_smem + s * b_stage_bytes);
         const int col0 = (t0 + j) * BN;
@@ -338,7 +349,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // ===================== MMA issuer =====================
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BN);
-      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 64);
+      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 2000);
       tc_fence_after();
       const uint32_t a_lo0 = desc_lo(smem_u32(a_smem));
       const uint32_t a_half_units = a_half_bytes >> 4;
@@ -346,7 +357,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       for (int j = 0; ok && j < nt; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 64)) break;
+        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) break;
         tc_fence_after();
         const uint32_t b_addr = smem_u32(b_smem + s * b_stage_bytes);
         const int buf = j & 1;
@@ -356,7 +367,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         // independent chains keep the tensor pipe busy.
 #pragma unroll 1
         for (int h = 0; h < NHALF; ++h) {
-          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 64)) { ok = false; break; }
+          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000)) { ok = false; break; }
         }
         if (!ok) break;
         tc_fence_after();
@@ -559,6 +570,7 @@ struct PvKernelParams {
   const float* rowpot; const float* rowlogw; const float* roww; const float* gs; float coef;
   const float* rows_raw; int ld_rows;   // original row cloud (GRAD epilogue: x_i - O_i)
   float* out;
+  const int* skip;       // device flag: non-zero => whole launch is a no-op
 };
 
 __device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -599,6 +611,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = p.row_begin + blockIdx.x * 128;
+  if (p.skip && *p.skip) return;  // uniform across the grid (set by an earlier kernel of the stream)
   constexpr int WCOLS = SPLIT ? 2 * BN : BN;  // TMEM columns per S/W buffer (Wl lives right after Wh)
   constexpr int NV = SPLIT ? 2 : 1;
 
@@ -655,7 +668,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       for (int j = 0; j < p.ntiles; ++j) {
         const int s = j % p.nstage;
         const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 64)) break;
+        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
         mbar_expect_tx(bar(B_FULL + s), stage_bytes);
         uint32_t d0 = smem_u32(st_smem + s * stage_bytes);
         for (int kb = 0; kb < p.nfull; ++kb)
@@ -680,7 +693,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc1 = make_idesc(BN);
       const uint32_t idesc2 = make_idesc(p.dv_pad);
-      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 64);
+      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 2000);
       tc_fence_after();
       const uint32_t a_addr = smem_u32(a_smem);
       uint32_t o_acc = 0;
@@ -688,7 +701,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       auto mma2 = [&](int jj) -> bool {
         const int s = jj % p.nstage;
         const int buf = jj & 1;
-        if (!mbar_wait(bar(W_FULL + buf), (jj >> 1) & 1, abort_flag, 64)) return false;
+        if (!mbar_wait(bar(W_FULL + buf), (jj >> 1) & 1, abort_flag, 2000)) return false;
         tc_fence_after();
         const uint32_t w_tmem = tmem_base + buf * WCOLS;
         const uint32_t v_addr = smem_u32(st_smem + s * stage_bytes) + b_bytes;
@@ -717,7 +730,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
         const uint32_t ph = (j / p.nstage) & 1;
         // With a single stage the previous tile's second GEMM must retire before its buffers are refilled.
         if (p.nstage == 1 && j > 0) { if (!mma2(j - 1)) { ok = false; break; } }
-        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 64)) { ok = false; break; }
+        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
         tc_fence_after();
         const uint32_t b_addr = smem_u32(st_smem + s * stage_bytes);
         const uint32_t d_tmem = tmem_base + (j & 1) * WCOLS;
@@ -1199,7 +1212,7 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa,
   kp.dv = pa.dv; kp.dv_pad = ps.dv_pad; kp.ld_out = pa.dv;
   kp.scale2 = scale2; kp.eps = a.eps; kp.R = pa.R; kp.epilogue = pa.epilogue;
   kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.roww = pa.roww; kp.gs = pa.gs; kp.coef = pa.coef;
-  kp.rows_raw = a.rows; kp.ld_rows = a.d; kp.out = pa.out;
+  kp.rows_raw = a.rows; kp.ld_rows = a.d; kp.out = pa.out; kp.skip = pa.skip;
   const int grid = (a.nr - a.row_begin + 127) / 128;
   if (grid <= 0) return cudaSuccess;
   for (int sl = 0; sl < ps.nslices; ++sl) {
