@@ -2,6 +2,7 @@
 // the issue rate of ex2.approx (the transcendental pipe) alone, and of the soft-max inner loop
 // (FFMA + ex2 + FADD + half a 3-input max per entry) with no memory traffic at all.
 #include "../../include/flash_sinkhorn_b200.h"
+#include "fs_tc.cuh"
 #include <cuda_runtime.h>
 
 namespace {
@@ -89,4 +90,9 @@ extern "C" double fs_micro_exp_rate(int mode, int warps_per_sm) {
   cudaFree(out);
   if (cudaGetLastError() != cudaSuccess || ms <= 0.f) return -1.0;
   return (double)sms * threads * 32.0 * iters / (ms * 1e-3);
+}
+
+// Cycles per tensor-core instruction of the engine's shape family, measured on the current device.
+extern "C" double fs_micro_mma_cycles(int n_cols, int a_in_tmem) {
+  return fs::tc::micro_mma_cycles(n_cols, a_in_tmem != 0);
 }

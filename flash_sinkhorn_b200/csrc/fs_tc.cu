@@ -384,10 +384,8 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
             const uint64_t bd = pack_desc(bl + 2 * ks, kDescHi128);
 #pragma unroll
             for (int h = 0; h < NHALF; ++h) {
-#ifndef FS_EXP_SKIP_MMA
               umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units + 2 * ks, kDescHi128), bd,
                         idesc, acc);
-#endif
             }
             acc = 1;
           }
@@ -399,9 +397,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           const uint64_t bd = pack_desc(bl, kDescHi32);
 #pragma unroll
           for (int h = 0; h < NHALF; ++h) {
-#ifndef FS_EXP_SKIP_MMA
             umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units, kDescHi32), bd, idesc, acc);
-#endif
           }
           acc = 1;
           al += (128 * 32) >> 4;
@@ -435,9 +431,6 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     const int c_base = part * CH;
     // One online-softmax update with the 32 scores of a chunk (this thread's row).
     auto consume = [&](const uint32_t (&r)[32]) {
-#ifdef FS_EXP_SKIP_SOFTMAX
-      s_run += __uint_as_float(r[0]); return;
-#endif
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -558,11 +551,12 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
 //   MMA2 : O += W x Vt_tile^T         (A operand from TMEM, B = V^T tile, K-major, in smem)
 // No running max and no rescaling of O: R makes every W <= ~1. In SPLIT mode (exact fp32)
 // W = Wh + Wl and V = Vh + Vl and MMA2 is issued three times (Wh.Vh + Wl.Vh + Wh.Vl).
-// One CTA = 128 rows; TMEM columns: [0, 2*WCOLS) two S/W buffers, then DV_PAD columns of O.
+// One CTA = 128 rows; TMEM columns: [0, 3*WCOLS) three S/W buffers, then DV_PAD columns of O.
 struct PvKernelParams {
-  int nr, nc, ntiles, nfull, ntail, nstage;
+  int nr, nc, ntiles, nfull, ntail;
+  int nb, nv;            // ring depths: column-operand tiles (freed after the score GEMM) and V tiles
   int row_begin;         // rows [row_begin, nr) are produced
-  int dv, dv_pad, dv0;   // real width, padded slice width (multiple of 32, <= 256), first column of this slice
+  int dv, dv_pad, dv0;   // real width, padded slice width (multiple of 32, <= 128), first column of this slice
   int ld_out;            // row pitch of out (= full dv of the problem)
   float scale2, eps;
   const float* R;
@@ -581,6 +575,13 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, u
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// Round-to-nearest (ties away) onto the 10-bit TF32 mantissa with two integer operations; the conversion
+// instruction shares the quarter-rate pipe with ex2, which the weights already saturate. Works on the
+// magnitude, so it is valid for either sign; the inputs here are finite weights in [0, ~1].
+__device__ __forceinline__ float round_tf32_pos(float w) {
+  return __uint_as_float((__float_as_uint(w) + 0x1000u) & 0xffffe000u);
 }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
@@ -602,8 +603,10 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
       : "memory");
 }
 
+constexpr int kNSW = 3;  // S/W buffers of the plan-times-matrix kernel
+
 template <int BN, bool SPLIT>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(128 + 128 * kParts, 1)
 tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constant__ CUtensorMap mapA_tail,
              const __grid_constant__ CUtensorMap mapB_full, const __grid_constant__ CUtensorMap mapB_tail,
              const __grid_constant__ CUtensorMap mapV_hi, const __grid_constant__ CUtensorMap mapV_lo,
@@ -620,28 +623,39 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
   const uint32_t b_bytes = p.nfull * (BN * 128) + p.ntail * (BN * 32);
   const uint32_t v_blk = (uint32_t)p.dv_pad * 128;        // one 32-column K block of V^T: dv_pad rows x 128 B
   const uint32_t v_bytes = (BN / 32) * v_blk;             // per hi/lo part
-  const uint32_t stage_bytes = b_bytes + NV * v_bytes;
+  const uint32_t v_stage = NV * v_bytes;
   uint8_t* a_smem = base;
-  uint8_t* st_smem = a_smem + a_bytes;
-  uint64_t* bars = (uint64_t*)(st_smem + p.nstage * stage_bytes);
-  const int B_FULL = 0, B_EMPTY = p.nstage, S_FULL = 2 * p.nstage, W_FULL = S_FULL + 2, A_FULL = W_FULL + 2,
-            O_FULL = A_FULL + 1, NBARS = O_FULL + 1;
+  uint8_t* b_smem = a_smem + a_bytes;
+  uint8_t* v_smem = b_smem + p.nb * b_bytes;
+  uint64_t* bars = (uint64_t*)(v_smem + p.nv * v_stage);
+  // Two independent rings: a column-operand tile is released as soon as its score GEMM retires, a V tile
+  // only after the second GEMM, a whole soft-max later; sharing one ring would serialise TMA latency
+  // behind the soft-max.
+  const int B_FULL = 0, B_EMPTY = p.nb, V_FULL = 2 * p.nb, V_EMPTY = V_FULL + p.nv, S_FULL = V_EMPTY + p.nv,
+            W_FULL = S_FULL + kNSW, W_FREE = W_FULL + kNSW, A_FULL = W_FREE + kNSW, O_FULL = A_FULL + 1,
+            DRAIN = O_FULL + 1, NBARS = DRAIN + 1;
   uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   auto bar = [&](int i) { return smem_u32(bars + i); };
   constexpr uint32_t kTmemCols = 512;
 
   if (tid == 0) {
-    for (int s = 0; s < p.nstage; ++s) {
+    for (int s = 0; s < p.nb; ++s) {
       mbar_init(bar(B_FULL + s), 1);
       mbar_init(bar(B_EMPTY + s), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int s = 0; s < p.nv; ++s) {
+      mbar_init(bar(V_FULL + s), 1);
+      mbar_init(bar(V_EMPTY + s), 1);
+    }
+    for (int i = 0; i < kNSW; ++i) {
       mbar_init(bar(S_FULL + i), 1);
-      mbar_init(bar(W_FULL + i), 4);
+      mbar_init(bar(W_FULL + i), 4 * kParts);
+      mbar_init(bar(W_FREE + i), 1);
     }
     mbar_init(bar(A_FULL), 1);
     mbar_init(bar(O_FULL), 1);
+    mbar_init(bar(DRAIN), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -654,7 +668,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t o_tmem = tmem_base + 2 * WCOLS;
+  const uint32_t o_tmem = tmem_base + kNSW * WCOLS;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -666,77 +680,63 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       int issued = 0;
 #pragma unroll 1
       for (int j = 0; j < p.ntiles; ++j) {
-        const int s = j % p.nstage;
-        const uint32_t ph = (j / p.nstage) & 1;
+        const int s = j % p.nb;
+        const uint32_t ph = (j / p.nb) & 1;
         if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
-        mbar_expect_tx(bar(B_FULL + s), stage_bytes);
-        uint32_t d0 = smem_u32(st_smem + s * stage_bytes);
+        mbar_expect_tx(bar(B_FULL + s), b_bytes);
+        uint32_t d0 = smem_u32(b_smem + s * b_bytes);
         for (int kb = 0; kb < p.nfull; ++kb)
           tma_load_2d(d0 + kb * (BN * 128), &mapB_full, kb * 32, j * BN, bar(B_FULL + s));
         for (int t = 0; t < p.ntail; ++t)
           tma_load_2d(d0 + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, j * BN,
                       bar(B_FULL + s));
-        uint32_t dv_dst = d0 + b_bytes;
-        for (int kb = 0; kb < BN / 32; ++kb) {
-          tma_load_2d(dv_dst + kb * v_blk, &mapV_hi, j * BN + kb * 32, p.dv0, bar(B_FULL + s));
-          if (SPLIT) tma_load_2d(dv_dst + v_bytes + kb * v_blk, &mapV_lo, j * BN + kb * 32, p.dv0, bar(B_FULL + s));
-        }
         issued = j + 1;
       }
       if (*abort_flag) {
         mbar_wait_quiet(bar(A_FULL), 0);
-        for (int j = (issued > p.nstage ? issued - p.nstage : 0); j < issued; ++j)
-          mbar_wait_quiet(bar(B_FULL + j % p.nstage), (j / p.nstage) & 1);
+        for (int j = (issued > p.nb ? issued - p.nb : 0); j < issued; ++j)
+          mbar_wait_quiet(bar(B_FULL + j % p.nb), (j / p.nb) & 1);
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {  // V^T tiles (hi and, in split mode, lo) on their own ring
+      int issued = 0;
+#pragma unroll 1
+      for (int j = 0; j < p.ntiles; ++j) {
+        const int s = j % p.nv;
+        const uint32_t ph = (j / p.nv) & 1;
+        if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
+        mbar_expect_tx(bar(V_FULL + s), v_stage);
+        uint32_t dv_dst = smem_u32(v_smem + s * v_stage);
+        for (int kb = 0; kb < BN / 32; ++kb) {
+          tma_load_2d(dv_dst + kb * v_blk, &mapV_hi, j * BN + kb * 32, p.dv0, bar(V_FULL + s));
+          if (SPLIT) tma_load_2d(dv_dst + v_bytes + kb * v_blk, &mapV_lo, j * BN + kb * 32, p.dv0, bar(V_FULL + s));
+        }
+        issued = j + 1;
+      }
+      if (*abort_flag) {
+        for (int j = (issued > p.nv ? issued - p.nv : 0); j < issued; ++j)
+          mbar_wait_quiet(bar(V_FULL + j % p.nv), (j / p.nv) & 1);
       }
     }
   } else if (warp == 1) {
+    // Score GEMM S_j = A . B_j^T into S/W buffer j%3. Issued by its own lane, the second GEMM by another
+    // warp's lane: a lane sharing its scheduler with soft-max warps sustains one MMA per ~90 cycles, and
+    // the 9 + 16 instructions of a tile would otherwise queue behind each other.
     if (lane == 0) {
       constexpr uint32_t idesc1 = make_idesc(BN);
-      const uint32_t idesc2 = make_idesc(p.dv_pad);
       bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 2000);
       tc_fence_after();
-      const uint32_t a_addr = smem_u32(a_smem);
-      uint32_t o_acc = 0;
-      // Second GEMM of tile jj (its W is ready when the warpgroup says so); frees the stage afterwards.
-      auto mma2 = [&](int jj) -> bool {
-        const int s = jj % p.nstage;
-        const int buf = jj & 1;
-        if (!mbar_wait(bar(W_FULL + buf), (jj >> 1) & 1, abort_flag, 2000)) return false;
-        tc_fence_after();
-        const uint32_t w_tmem = tmem_base + buf * WCOLS;
-        const uint32_t v_addr = smem_u32(st_smem + s * stage_bytes) + b_bytes;
-#pragma unroll 1
-        for (int part = 0; part < (SPLIT ? 3 : 1); ++part) {
-          // part 0: Wh.Vh   part 1: Wl.Vh   part 2: Wh.Vl
-          const uint32_t wa = w_tmem + ((part == 1) ? BN : 0);
-          const uint32_t va = v_addr + ((part == 2) ? v_bytes : 0);
-          uint32_t vl = desc_lo(va);
-#pragma unroll 1
-          for (int kb = 0; kb < BN / 32; ++kb) {
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              umma_tf32_ts(o_tmem, wa + kb * 32 + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
-              o_acc = 1;
-            }
-            vl += v_blk >> 4;
-          }
-        }
-        umma_commit(bar(B_EMPTY + s));
-        return true;
-      };
+      const uint32_t a_lo0 = desc_lo(smem_u32(a_smem));
 #pragma unroll 1
       for (int j = 0; ok && j < p.ntiles; ++j) {
-        const int s = j % p.nstage;
-        const uint32_t ph = (j / p.nstage) & 1;
-        // With a single stage the previous tile's second GEMM must retire before its buffers are refilled.
-        if (p.nstage == 1 && j > 0) { if (!mma2(j - 1)) { ok = false; break; } }
-        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
+        const int s = j % p.nb, buf = j % kNSW;
+        if (!mbar_wait(bar(W_FREE + buf), ((j / kNSW) & 1) ^ 1, abort_flag, 2000)) break;
+        if (!mbar_wait(bar(B_FULL + s), (j / p.nb) & 1, abort_flag, 2000)) break;
         tc_fence_after();
-        const uint32_t b_addr = smem_u32(st_smem + s * stage_bytes);
-        const uint32_t d_tmem = tmem_base + (j & 1) * WCOLS;
-        // The S/W buffer (j&1) was last read by MMA2(j-2), issued earlier by this same thread: in order.
+        const uint32_t d_tmem = tmem_base + buf * WCOLS;
+        uint32_t al = a_lo0, bl = desc_lo(smem_u32(b_smem + s * b_bytes));
         uint32_t acc = 0;
-        uint32_t al = desc_lo(a_addr), bl = desc_lo(b_addr);
 #pragma unroll 1
         for (int kb = 0; kb < p.nfull; ++kb) {
 #pragma unroll
@@ -754,51 +754,120 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
           al += (128 * 32) >> 4;
           bl += (BN * 32) >> 4;
         }
-        umma_commit(bar(S_FULL + (j & 1)));
-        if (p.nstage > 1 && j > 0) { if (!mma2(j - 1)) { ok = false; break; } }
+        umma_commit(bar(S_FULL + buf));
+        umma_commit(bar(B_EMPTY + s));
       }
-      if (ok) ok = mma2(p.ntiles - 1);
+      if (*abort_flag) {  // let every MMA issued by this thread retire before TMEM is freed
+        umma_commit(bar(DRAIN));
+        mbar_wait_quiet(bar(DRAIN), 0);
+      }
+    }
+  } else if (warp == 3) {
+    // Second GEMM O += W_j . V_j (W read from TMEM), once the soft-max warps have written W_j.
+    if (lane == 0) {
+      const uint32_t idesc2 = make_idesc(p.dv_pad);
+      const uint32_t v_blk_units = v_blk >> 4;
+      uint32_t o_acc = 0;
+      bool ok = true;
+#pragma unroll 1
+      for (int j = 0; j < p.ntiles; ++j) {
+        const int sv = j % p.nv, buf = j % kNSW;
+        if (!mbar_wait(bar(V_FULL + sv), (j / p.nv) & 1, abort_flag, 2000)) { ok = false; break; }
+        if (!mbar_wait(bar(W_FULL + buf), (j / kNSW) & 1, abort_flag, 2000)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t w_tmem = tmem_base + buf * WCOLS;
+        const uint32_t v_lo0 = desc_lo(smem_u32(v_smem + sv * v_stage));
+#pragma unroll 1
+        for (int part = 0; part < (SPLIT ? 3 : 1); ++part) {
+          // part 0: Wh.Vh   part 1: Wl.Vh   part 2: Wh.Vl
+          uint32_t wa = w_tmem + ((part == 1) ? BN : 0);
+          uint32_t vl = v_lo0 + ((part == 2) ? (v_bytes >> 4) : 0);
+#pragma unroll 1
+          for (int kb = 0; kb < BN / 32; ++kb) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_tf32_ts(o_tmem, wa + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
+              o_acc = 1;
+            }
+            wa += 32;
+            vl += v_blk_units;
+          }
+        }
+        umma_commit(bar(V_EMPTY + sv));
+        umma_commit(bar(W_FREE + buf));
+      }
+      (void)ok;
       umma_commit(bar(O_FULL));
       if (*abort_flag) mbar_wait_quiet(bar(O_FULL), 0);
     }
   } else if (warp >= 4) {
+    // Two warpgroups share the 128 rows: each takes half of every tile's 32-column chunks.
+    const int part = (warp - 4) >> 2;
     const int q = warp & 3;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const int r = row0 + q * 32 + lane;
     const float scale = p.scale2;
     const float negR = (r < p.nr) ? -p.R[r] : 0.f;
     bool ok = true;
-#pragma unroll 1
-    for (int j = 0; j < p.ntiles; ++j) {
-      const int buf = j & 1;
-      if (!mbar_wait(bar(S_FULL + buf), (j >> 1) & 1, abort_flag)) { ok = false; break; }
-      __syncwarp();
-      tc_fence_after();
-      const uint32_t taddr = lane_addr + buf * WCOLS;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld32(taddr + c * 32, v);
-        if (SPLIT) {
-          float lo[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float w = ex2(fmaf(v[i], scale, negR));
-            float hi = to_tf32(w);
-            lo[i] = to_tf32(w - hi);
-            v[i] = hi;
-          }
-          tmem_st32(taddr + BN + c * 32, lo);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = to_tf32(ex2(fmaf(v[i], scale, negR)));
-        }
-        tmem_st32(taddr + c * 32, v);
+    constexpr int CH = BN / 32 / kParts;
+    const int total = p.ntiles * CH;
+    const int c_base = part * CH;
+    auto issue = [&](int g, uint32_t (&rg)[32]) -> bool {
+      const int j = g / CH, c = g % CH, buf = j % kNSW;
+      if (c == 0) {
+        if (!mbar_wait(bar(S_FULL + buf), (j / kNSW) & 1, abort_flag)) return false;
+        __syncwarp();
+        tc_fence_after();
       }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(W_FULL + buf));
+      tmem_ld32_nowait(lane_addr + buf * WCOLS + (c_base + c) * 32, rg);
+      return true;
+    };
+    // Scores of chunk g have landed in rg: turn them into weights, store them back over the scores.
+    auto weigh = [&](int g, uint32_t (&rg)[32]) {
+      const int j = g / CH, c = g % CH, buf = j % kNSW;
+      const uint32_t taddr = lane_addr + buf * WCOLS + (c_base + c) * 32;
+      float v[32];
+      if (SPLIT) {
+        float lo[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float w = ex2(fmaf(__uint_as_float(rg[i]), scale, negR));
+          float hi = round_tf32_pos(w);
+          lo[i] = round_tf32_pos(w - hi);
+          v[i] = hi;
+        }
+        tmem_st32(taddr + BN, lo);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = round_tf32_pos(ex2(fmaf(__uint_as_float(rg[i]), scale, negR)));
+      }
+      tmem_st32(taddr, v);
+      if (c == CH - 1) {  // this warp's share of the tile is written: tell the MMA lane
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(W_FULL + buf));
+      }
+    };
+    // One pipeline step: chunk g is in `cur`; the load of chunk g+1 goes to `nxt`. Within a tile the next
+    // load is issued before the arithmetic; across tiles only after W_FULL was signalled, so that a warp
+    // never sits on the next tile's barrier while the MMA lane waits for its share of this one.
+    auto pipe = [&](int g, uint32_t (&cur)[32], uint32_t (&nxt)[32]) -> bool {
+      tmem_ld_wait(cur);
+      const bool last = (g % CH) == CH - 1;
+      const bool more = g + 1 < total;
+      if (!last && more && !issue(g + 1, nxt)) return false;
+      weigh(g, cur);
+      if (last && more && !issue(g + 1, nxt)) return false;
+      return true;
+    };
+    uint32_t ra[32], rb[32];
+    ok = issue(0, ra);
+#pragma unroll 1
+    for (int g = 0; ok && g < total; g += 2) {
+      ok = pipe(g, ra, rb);
+      if (!ok || g + 1 >= total) break;
+      ok = pipe(g + 1, rb, ra);
     }
     if (ok) ok = mbar_wait(bar(O_FULL), 0, abort_flag);
     __syncwarp();
@@ -818,9 +887,9 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       }
       float* orow = p.out + (size_t)rr * p.ld_out + p.dv0;
 #pragma unroll 1
-      for (int c = 0; c < p.dv_pad / 32; ++c) {
+      for (int c = part; c < p.dv_pad / 32; c += kParts) {  // the warpgroups split the output chunks
         float o[32];
-        tmem_ld32(lane_addr + 2 * WCOLS + c * 32, o);
+        tmem_ld32(lane_addr + kNSW * WCOLS + c * 32, o);
         if (valid) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -949,11 +1018,7 @@ struct Shape {
 Shape plan_shape(int d, int prec) {
   Shape s{};
   s.kc = (prec == 0) ? d : 3 * d;
-#ifdef FS_EXP_NOAUG
-  s.kp = (s.kc + 7) & ~7;
-#else
-  s.kp = (s.kc + 3 + 7) & ~7;
-#endif
+  s.kp = (s.kc + 3 + 7) & ~7;  // + 3 bias columns, padded to whole K steps of 8
   s.nfull = s.kp / 32;
   s.ntail = (s.kp % 32) / 8;
   const size_t row_bytes = (size_t)s.kp * 4;
@@ -1129,7 +1194,7 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
 namespace {
 
 struct PvShape {
-  int bn, dv_pad, nslices, nstage, cols_pad_mult;
+  int bn, dv_pad, nslices, nb, nv, cols_pad_mult;
   size_t smem;
   bool split, ok;
 };
@@ -1141,16 +1206,23 @@ PvShape plan_pv(int d, int prec, int dv) {
   if (!sh.ok || dv <= 0) return s;
   s.split = (prec == 1);
   s.bn = s.split ? 64 : 128;
-  const int w = dv < 256 ? dv : 256;
+  // TMEM: 3 S/W buffers of 128 columns leave 128 for O, so wider V goes in slices of 128 columns.
+  const int w = dv < 128 ? dv : 128;
   s.dv_pad = (w + 31) & ~31;
-  s.nslices = (dv + 255) / 256;
+  s.nslices = (dv + 127) / 128;
   const size_t a = (size_t)128 * sh.kp * 4;
-  const size_t stage = (size_t)s.bn * sh.kp * 4 + (size_t)(s.split ? 2 : 1) * (s.bn / 32) * s.dv_pad * 128;
+  const size_t b = (size_t)s.bn * sh.kp * 4;
+  const size_t v = (size_t)(s.split ? 2 : 1) * (s.bn / 32) * s.dv_pad * 128;
   const size_t budget = kSmemMax - 2048;
-  if (a + stage > budget) return s;
-  int ns = (int)((budget - a) / stage);
-  s.nstage = ns > 3 ? 3 : ns;
-  s.smem = a + s.nstage * stage + 2048;
+  if (a + b + v > budget) return s;
+  // Grow the rings alternately (V first: its tiles live through a whole soft-max) up to 3 deep each.
+  s.nb = s.nv = 1;
+  for (int round = 0; round < 4; ++round) {
+    int& ring = (round & 1) ? s.nb : s.nv;
+    const size_t unit = (round & 1) ? b : v;
+    if (ring < 3 && a + s.nb * b + s.nv * v + unit <= budget) ++ring;
+  }
+  s.smem = a + s.nb * b + s.nv * v + 2048;
   if (s.smem < (size_t)kSmemMin) s.smem = kSmemMin;
   s.ok = true;
   return s;
@@ -1161,7 +1233,7 @@ cudaError_t launch_pv(const CUtensorMap* maps, const PvKernelParams& kp, int gri
   auto kern = tc_pv_kernel<BN, SPLIT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
   if (e != cudaSuccess) return e;
-  kern<<<grid, 256, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
+  kern<<<grid, 128 + 128 * kParts, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
   return cudaGetLastError();
 }
 
@@ -1208,7 +1280,7 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa,
   PvKernelParams kp;
   kp.nr = a.nr; kp.nc = a.nc; kp.row_begin = a.row_begin;
   kp.ntiles = (a.nc + ps.bn - 1) / ps.bn;
-  kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nstage = ps.nstage;
+  kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nb = ps.nb; kp.nv = ps.nv;
   kp.dv = pa.dv; kp.dv_pad = ps.dv_pad; kp.ld_out = pa.dv;
   kp.scale2 = scale2; kp.eps = a.eps; kp.R = pa.R; kp.epilogue = pa.epilogue;
   kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.roww = pa.roww; kp.gs = pa.gs; kp.coef = pa.coef;
@@ -1222,6 +1294,104 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa,
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
+}
+
+// ---- micro-benchmark: cycles per tcgen05.mma as issued by one lane ----
+namespace {
+
+// One lane issues n_mma MMAs (kind::tf32, M=128, K=8, N columns; operands from zero-filled shared memory,
+// A optionally from TMEM) back to back, walking the four K slices of a 128-byte swizzle row, commits and
+// waits (bounded). out[2*cta] = cycles until the last issue, out[2*cta+1] = cycles until completion.
+template <int N, bool TS>
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int n_mma, long long* out) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint64_t* bars = (uint64_t*)(base + 64 * 1024);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  for (int i = tid; i < 64 * 1024 / 4; i += 128) ((float*)base)[i] = 0.f;  // A: 16 KB at 0, B: 32 KB at 32 KB
+  if (tid == 0) {
+    mbar_init(smem_u32(bars), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t idesc = make_idesc(N);
+  const uint32_t al0 = desc_lo(smem_u32(base)), bl0 = desc_lo(smem_u32(base + 32 * 1024));
+  const uint32_t a_t = tmem_base + 384;  // TMEM operand columns (contents irrelevant for timing)
+  if (warp == 1 && lane == 0) {
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (int i = 0; i < n_mma; i += 8) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = 2 * (ks & 3);
+        if (TS) umma_tf32_ts(tmem_base, a_t + 8 * (ks & 3), pack_desc(bl0 + off, kDescHi128), idesc, 1u);
+        else umma_tf32(tmem_base, pack_desc(al0 + off, kDescHi128), pack_desc(bl0 + off, kDescHi128), idesc, 1u);
+      }
+    }
+    const long long t1 = clock64();
+    umma_commit(smem_u32(bars));
+    mbar_wait(smem_u32(bars), 0, abort_flag, 0);
+    const long long t2 = clock64();
+    out[blockIdx.x * 2] = t1 - t0;
+    out[blockIdx.x * 2 + 1] = t2 - t0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (tid == 0 && *abort_flag) atomicExch(&g_tc_error, 1);
+}
+
+template <int N, bool TS>
+double run_mma_rate(int sms) {
+  const int n_mma = 4096;
+  long long* out = nullptr;
+  if (cudaMalloc(&out, sizeof(long long) * 2 * sms) != cudaSuccess) return -1.0;
+  auto k = mma_rate_kernel<N, TS>;
+  const size_t smem = 64 * 1024 + 2048;
+  double res = -1.0;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
+    k<<<sms, 128, smem>>>(64, out);      // warm-up
+    k<<<sms, 128, smem>>>(n_mma, out);
+    long long* host = new long long[2 * sms];
+    if (cudaMemcpy(host, out, sizeof(long long) * 2 * sms, cudaMemcpyDeviceToHost) == cudaSuccess) {
+      double tot = 0.0;
+      for (int i = 0; i < sms; ++i) tot += (double)host[2 * i + 1];
+      res = tot / sms / n_mma;
+    }
+    delete[] host;
+  }
+  cudaFree(out);
+  return res;
+}
+
+}  // namespace
+
+double micro_mma_cycles(int n_cols, bool a_in_tmem) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1.0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) return -1.0;
+  switch (n_cols) {
+    case 64: return a_in_tmem ? run_mma_rate<64, true>(sms) : run_mma_rate<64, false>(sms);
+    case 128: return a_in_tmem ? run_mma_rate<128, true>(sms) : run_mma_rate<128, false>(sms);
+    case 256: return a_in_tmem ? run_mma_rate<256, true>(sms) : run_mma_rate<256, false>(sms);
+    default: return -1.0;
+  }
 }
 
 int read_error_flag() {

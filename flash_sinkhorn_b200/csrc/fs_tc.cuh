@@ -44,5 +44,10 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, 
 // Value of the device-global error word (non-zero once a bounded wait gave up); synchronises.
 int read_error_flag();
 
+// Average SM cycles per tcgen05.mma (kind::tf32, 128 x n_cols x 8, n_cols in {64,128,256}; A from shared
+// memory or from TMEM) when one lane issues 4096 of them back to back on every SM. Allocates a small
+// buffer and synchronises; < 0 on error. Diagnostic (roofline denominators).
+double micro_mma_cycles(int n_cols, bool a_in_tmem);
+
 }  // namespace tc
 }  // namespace fs

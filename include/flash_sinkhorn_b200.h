@@ -83,6 +83,13 @@ int fs_device_error(void);
  * transcendental-pipe peak of the roofline. Allocates 4 bytes and synchronises; < 0 on error. */
 double fs_micro_exp_rate(int mode, int warps_per_sm);
 
+/* Micro-benchmark (no reference counterpart): average SM cycles per `tcgen05.mma.kind::tf32`
+ * instruction of shape 128 x n_cols x 8 (n_cols in {64, 128, 256}; A operand from shared memory, or from
+ * TMEM when a_in_tmem != 0) when one lane per SM issues 4096 of them back to back. The tensor term of
+ * the roofline follows from it: entries/s = SMs * clock * 128 * n_cols / (cycles * K-steps per entry
+ * tile). Allocates a few KB and synchronises; < 0 on error. */
+double fs_micro_mma_cycles(int n_cols, int a_in_tmem);
+
 /* Scratch bytes needed by `op` (one of FS_OP_*) at these sizes. */
 size_t fs_workspace_bytes(int op, int n, int m, int d, int prec);
 
