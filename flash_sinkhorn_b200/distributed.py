@@ -47,6 +47,7 @@ def run_symmetric_sharded(
     rank: int,
     step_fn: Callable,
     gather_fn: Callable,
+    self_problem: bool = False,
 ):
     """Symmetric schedule (init step, averaged loop, optional extrapolation) over sharded steps.
 
@@ -57,15 +58,23 @@ def run_symmetric_sharded(
     ``gather_fn(buf, shard)`` all-gathers ``buf`` in place (rank r owns ``buf[r*shard:(r+1)*shard]``)
     and may return a callable that waits for completion (asynchronous gather) or None.
     Buffers are padded to ``world*shard`` entries. Returns ``(f_hat, g_hat, f_hat_pre, g_hat_pre, steps)``.
+
+    ``self_problem`` (same cloud, weights, penalties and initial potentials on both sides, ``n == m``):
+    g equals f after every step, so only the f half runs (and is gathered) and g aliases f.
     """
     sf, sg = shard_layout(n, world), shard_layout(m, world)
     f_lo, f_hi = shard_range(n, world, rank)
     g_lo, g_hi = shard_range(m, world, rank)
     mk = lambda size, src: torch.zeros(size, dtype=src.dtype, device=src.device)
     f = [mk(world * sf, f_hat0), mk(world * sf, f_hat0)]
-    g = [mk(world * sg, g_hat0), mk(world * sg, g_hat0)]
     f[0][:n].copy_(f_hat0)
-    g[0][:m].copy_(g_hat0)
+    if self_problem:
+        if n != m:
+            raise ValueError("self_problem needs n == m")
+        g = f
+    else:
+        g = [mk(world * sg, g_hat0), mk(world * sg, g_hat0)]
+        g[0][:m].copy_(g_hat0)
     cur = 0
     pending = {"f": None, "g": None}  # waits for the (asynchronous) gathers that fill f[cur] / g[cur]
     parity = 0
@@ -81,6 +90,12 @@ def run_symmetric_sharded(
         # half goes first lets BOTH gathers hide behind a compute half: the gather launched last in one
         # step is only needed by the second half of the next step.
         nonlocal cur, parity
+        if self_problem:
+            settle("f")
+            step_fn(f[cur], f[cur], f[cur ^ 1], f[cur ^ 1], float(eps), float(w), (f_lo, f_hi, g_lo, g_lo))
+            pending["f"] = gather_fn(f[cur ^ 1], sf)
+            cur ^= 1
+            return
         launched = {}
         for side in (("f", "g") if parity == 0 else ("g", "f")):
             settle("g" if side == "f" else "f")
@@ -173,9 +188,14 @@ def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, 
         )
         state["staged"] = True
 
+    same_init = (f_init is None and g_init is None) or (
+        f_init is not None and g_init is not None and f_init.data_ptr() == g_init.data_ptr())
+    self_problem = (n == m and x.data_ptr() == y.data_ptr() and log_a.data_ptr() == log_b.data_ptr()
+                    and same_init and rho_x == rho_y)
     fh, gh, fp, gp, steps = run_symmetric_sharded(
         n, m, f0, g0, eps_list, last_extrapolation=last_extrapolation, threshold=threshold,
-        check_every=check_every, world=world, rank=rank, step_fn=step_fn, gather_fn=gather)
+        check_every=check_every, world=world, rank=rank, step_fn=step_fn, gather_fn=gather,
+        self_problem=self_problem)
     out_pre = (None, None) if fp is None else (fp + alpha, gp + beta)
     return fh + alpha, gh + beta, out_pre[0], out_pre[1], steps
 

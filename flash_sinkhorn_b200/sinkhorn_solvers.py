@@ -211,10 +211,14 @@ def sinkhorn_flashstyle_symmetric(
         raise ValueError("eps_list must be non-empty")
 
     dev = _lib.require_cuda(x=x, y=y, a=a, b=b, f_init=f_init, g_init=g_init)
-    x32, y32 = _lib.f32c(x), _lib.f32c(y)
-    log_a, log_b = log_weights(a).contiguous(), log_weights(b).contiguous()
+    # A self-transport problem (OT(a,a): the debiasing terms pass the same tensors twice) keeps the same
+    # buffers on both sides; the engine recognises it by pointer equality and runs one soft-min per step.
+    x32 = _lib.f32c(x)
+    y32 = x32 if y is x else _lib.f32c(y)
+    log_a = log_weights(a).contiguous()
+    log_b = log_a if b is a else log_weights(b).contiguous()
     fi = None if f_init is None else _lib.f32c(f_init)
-    gi = None if g_init is None else _lib.f32c(g_init)
+    gi = None if g_init is None else (fi if g_init is f_init else _lib.f32c(g_init))
     prec = _lib.precision_id(allow_tf32)
 
     if process_group is not None and torch.distributed.get_world_size(process_group) > 1:

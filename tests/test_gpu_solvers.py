@@ -246,3 +246,25 @@ def test_marginals_at_scale_property():
     assert torch.isfinite(col).all()
     assert (col / b - 1).abs().max().item() < 5e-3
     assert abs(col.sum().item() - 1.0) < 1e-3
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("threshold", [None, 1e-3])
+def test_self_transport_shortcut_is_bit_exact(monkeypatch, mode, threshold):
+    """OT(a, a) with the same tensors on both sides runs one soft-min per step (g copies f); passing
+    clones forces the two-sided path. Both must agree bit for bit, and f must equal g."""
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_symmetric
+    set_mode(monkeypatch, mode)
+    z = load_golden("solvers_small")
+    x, a = dev(z["x"]), dev(z["a"])
+    kw = dict(use_epsilon_scaling=False, eps=0.5, n_iters=25, threshold=threshold, check_every=4,
+              return_prelast=True, return_n_iters=True)
+    one = sinkhorn_flashstyle_symmetric(x, x, a, a, **kw)
+    two = sinkhorn_flashstyle_symmetric(x, x.clone(), a, a.clone(), **kw)
+    assert one[4] == two[4]
+    for u, v in zip(one[:4], two[:4]):
+        assert torch.equal(u, v)
+    assert torch.equal(one[0], one[1]) and torch.equal(one[2], one[3])
+    want = O.solve_symmetric(z["x"].astype(np.float64), z["x"].astype(np.float64), z["a"].astype(np.float64),
+                             z["a"].astype(np.float64), [0.5] * 25, threshold=threshold, check_every=4)
+    assert rel(host(one[0]), want["f"]) < TOL[mode]

@@ -29,6 +29,8 @@ def _worker(rank, world, port, case, out_dir):
         z = load_golden("solvers_small")
         x, y = z["x"].astype(np.float64), z["y"].astype(np.float64)
         a, b = z["a"].astype(np.float64), z[case["b"]].astype(np.float64)
+        if case.get("self"):
+            y, b = x, a
         n, m = x.shape[0], y.shape[0]
         cs, rx, ry = case["cs"], case["rho_x"], case["rho_y"]
         alpha, beta = cs * O.sqnorm(x), cs * O.sqnorm(y)
@@ -57,7 +59,7 @@ def _worker(rank, world, port, case, out_dir):
         fh, gh, fp, gp, steps = run_symmetric_sharded(
             n, m, torch.from_numpy(-alpha), torch.from_numpy(-beta), case["eps_list"],
             last_extrapolation=True, threshold=case["threshold"], check_every=case["check_every"],
-            world=world, rank=rank, step_fn=step_fn, gather_fn=gather_fn)
+            world=world, rank=rank, step_fn=step_fn, gather_fn=gather_fn, self_problem=bool(case.get("self")))
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), f=fh.numpy() + alpha, g=gh.numpy() + beta,
                  f_pre=fp.numpy() + alpha, g_pre=gp.numpy() + beta, steps=steps)
     finally:
@@ -68,6 +70,9 @@ CASES = {
     "unbalanced_schedule": dict(b="b", cs=1.0, rho_x=1.0, rho_y=4.0, threshold=None, check_every=5, eps_list=None),
     "early_stop": dict(b="b_normalised", cs=1.0, rho_x=None, rho_y=None, threshold=1e-3, check_every=4,
                        eps_list=[5.0] * 60),
+    # OT(a, a): only the f half runs on each rank, g aliases f
+    "self_transport": dict(b="b", cs=1.0, rho_x=None, rho_y=None, threshold=None, check_every=5, eps_list=None,
+                           self=True),
 }
 
 
@@ -81,6 +86,8 @@ def test_two_rank_sharded_loop_equals_unsharded_oracle(tmp_path, name):
     mp.spawn(_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True)
     x, y = z["x"].astype(np.float64), z["y"].astype(np.float64)
     a, b = z["a"].astype(np.float64), z[case["b"]].astype(np.float64)
+    if case.get("self"):
+        y, b = x, a
     want = O.solve_symmetric(x, y, a, b, case["eps_list"], cost_scale=case["cs"], rho_x=case["rho_x"],
                              rho_y=case["rho_y"], threshold=case["threshold"], check_every=case["check_every"])
     ranks = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
