@@ -111,10 +111,16 @@ class _SinkhornCostFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, y, a, b, eps_list: Tuple[float, ...], config: _SinkhornConfig,
-                label_x, label_y, label_cost_matrix):
+                label_x, label_y, label_cost_matrix, presolved=None):
+        # `presolved` (extension): (f_cost, g_cost, f_grad, g_grad) from a solve done elsewhere - the multi-GPU
+        # divergence solves its three problems interleaved before building the three cost nodes.
         if label_cost_matrix is not None and label_x is not None and label_y is not None and config.lambda_y != 0.0:
             raise NotImplementedError("The OTDD label-augmented cost is not implemented in flash_sinkhorn_b200.")
-        if config.backend == "alternating":
+        if presolved is not None:
+            eps = float(eps_list[-1])
+            f_cost, g_cost, f_grad, g_grad = presolved
+            plain_dual = config.backend == "alternating" or config.rho_x is None or config.rho_y is None
+        elif config.backend == "alternating":
             eps = float(eps_list[-1])
             f_cost, g_cost = sinkhorn_flashstyle_alternating(
                 x, y, a, b, eps=eps, n_iters=len(eps_list), cost_scale=config.cost_scale,
@@ -166,4 +172,4 @@ class _SinkhornCostFn(torch.autograd.Function):
             ga = grad_out * f_cost
         if b.requires_grad:
             gb = grad_out * g_cost
-        return gx, gy, ga, gb, None, None, None, None, None
+        return gx, gy, ga, gb, None, None, None, None, None, None

@@ -33,7 +33,7 @@ def shard_range(rows: int, world: int, rank: int, align: int = SHARD_ALIGN) -> T
     return min(rows, rank * shard), min(rows, (rank + 1) * shard)
 
 
-def run_symmetric_sharded(
+def sharded_steps(
     n: int,
     m: int,
     f_hat0: torch.Tensor,
@@ -49,7 +49,11 @@ def run_symmetric_sharded(
     gather_fn: Callable,
     self_problem: bool = False,
 ):
-    """Symmetric schedule (init step, averaged loop, optional extrapolation) over sharded steps.
+    """Generator form of the sharded symmetric schedule (init step, averaged loop, optional extrapolation).
+
+    Yields after the launches of every step and finally returns the result tuple (``StopIteration.value``),
+    so that a caller can interleave the steps of several independent problems: the gathers of one then
+    overlap the compute of the next (see :func:`run_many`). :func:`run_symmetric_sharded` runs one problem.
 
     ``step_fn(f_old, g_old, f_new, g_new, eps, w, (f_lo, f_hi, g_lo, g_hi))`` must fill rows
     ``[f_lo, f_hi)`` of ``f_new`` and ``[g_lo, g_hi)`` of ``g_new`` from the full old potentials; it is
@@ -110,10 +114,12 @@ def run_symmetric_sharded(
     steps = 0
     step(eps_list[0], 1.0)
     steps += 1
+    yield
     prev = None
     for i, eps in enumerate(eps_list):
         step(eps, 0.5)
         steps += 1
+        yield
         if threshold is not None and (i + 1) % check_every == 0:
             settle("f", "g")
             if prev is None:
@@ -130,15 +136,36 @@ def run_symmetric_sharded(
         f_pre, g_pre = f[cur][:n].clone(), g[cur][:m].clone()
         step(eps_list[-1], 1.0)
         steps += 1
+        yield
     settle("f", "g")
     return f[cur][:n].clone(), g[cur][:m].clone(), f_pre, g_pre, steps
+
+
+def run_many(generators):
+    """Round-robin over :func:`sharded_steps` generators until all are exhausted; results in input order."""
+    gens = list(generators)
+    results = [None] * len(gens)
+    live = list(range(len(gens)))
+    while live:
+        for i in list(live):
+            try:
+                next(gens[i])
+            except StopIteration as done:
+                results[i] = done.value
+                live.remove(i)
+    return results
+
+
+def run_symmetric_sharded(*args, **kwargs):
+    """One problem through :func:`sharded_steps` (same arguments and result)."""
+    return run_many([sharded_steps(*args, **kwargs)])[0]
 
 
 def _gather_inplace(group, overlap: bool = False):
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     side = torch.cuda.Stream() if overlap else None
-    # a small ring of re-used events (at most two gathers are in flight at any time)
-    events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in range(8)] if overlap else []
+    # a small ring of re-used events (a few gathers are in flight at any time, also with interleaved problems)
+    events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in range(16)] if overlap else []
     state = {"i": 0}
 
     def gather(buf: torch.Tensor, shard: int):
@@ -160,9 +187,9 @@ def _gather_inplace(group, overlap: bool = False):
     return gather, world, rank
 
 
-def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, rho_y, last_extrapolation,
-                            threshold, check_every, f_init, g_init, prec, group):
-    """CUDA engine behind :func:`run_symmetric_sharded`. Returns standard potentials like the 1-GPU solver."""
+def _cuda_problem(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, rho_y, last_extrapolation,
+                  threshold, check_every, f_init, g_init, prec, gather, world, rank):
+    """(generator, finish) of one problem on the CUDA engine; ``finish(result)`` -> standard potentials."""
     from flash_sinkhorn_b200 import _lib
     from flash_sinkhorn_b200.kernels._common import dampening
 
@@ -175,7 +202,6 @@ def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, 
     g0 = (g_init.float() - beta) if g_init is not None else -beta
     ws = _lib.workspace(_lib.OP_STEP, n, m, d, prec, dev)
     state = {"staged": False}
-    gather, world, rank = _gather_inplace(group, overlap=True)
 
     def step_fn(f_old, g_old, f_new, g_new, eps, w, rng):
         df, dg = dampening(eps, rho_x), dampening(eps, rho_y)
@@ -192,12 +218,34 @@ def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, 
         f_init is not None and g_init is not None and f_init.data_ptr() == g_init.data_ptr())
     self_problem = (n == m and x.data_ptr() == y.data_ptr() and log_a.data_ptr() == log_b.data_ptr()
                     and same_init and rho_x == rho_y)
-    fh, gh, fp, gp, steps = run_symmetric_sharded(
+    gen = sharded_steps(
         n, m, f0, g0, eps_list, last_extrapolation=last_extrapolation, threshold=threshold,
         check_every=check_every, world=world, rank=rank, step_fn=step_fn, gather_fn=gather,
         self_problem=self_problem)
-    out_pre = (None, None) if fp is None else (fp + alpha, gp + beta)
-    return fh + alpha, gh + beta, out_pre[0], out_pre[1], steps
+
+    def finish(result):
+        fh, gh, fp, gp, steps = result
+        out_pre = (None, None) if fp is None else (fp + alpha, gp + beta)
+        return fh + alpha, gh + beta, out_pre[0], out_pre[1], steps
+
+    return gen, finish
+
+
+def symmetric_solve_sharded_many(problems, *, group):
+    """Solve several independent problems with their steps interleaved (each ``problems[i]`` is the keyword
+    set of :func:`symmetric_solve_sharded` without ``group``). While one problem's all-gather is in flight
+    the next problem computes, which hides the exchange even for self-transport problems, whose single
+    half-step per iteration leaves nothing of their own to overlap with."""
+    gather, world, rank = _gather_inplace(group, overlap=True)
+    built = [_cuda_problem(gather=gather, world=world, rank=rank, **pr) for pr in problems]
+    results = run_many([g for g, _ in built])
+    return [fin(res) for (_, fin), res in zip(built, results)]
+
+
+def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, group, **kw):
+    """CUDA engine behind :func:`run_symmetric_sharded`. Returns standard potentials like the 1-GPU solver."""
+    return symmetric_solve_sharded_many([dict(x=x, y=y, log_a=log_a, log_b=log_b, eps_list=eps_list, **kw)],
+                                        group=group)[0]
 
 
 def grad_sharded(x, y, a, b, log_a, log_b, f, g, grad_scale, eps, cost_scale, prec, want_x, want_y, group):

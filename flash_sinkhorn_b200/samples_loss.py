@@ -17,7 +17,11 @@ import torch
 
 from flash_sinkhorn_b200._autograd import _SinkhornConfig, _SinkhornCostFn
 from flash_sinkhorn_b200.kernels._common import epsilon_schedule, max_diameter
-from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating, sinkhorn_flashstyle_symmetric
+from flash_sinkhorn_b200.sinkhorn_solvers import (
+    sinkhorn_flashstyle_alternating,
+    sinkhorn_flashstyle_symmetric,
+    sinkhorn_flashstyle_symmetric_many,
+)
 
 
 @dataclass(frozen=True)
@@ -288,15 +292,34 @@ class SamplesLoss(torch.nn.Module):
             raise ValueError("flash_sinkhorn.SamplesLoss requires CUDA tensors.")
         config = self._make_config()
 
-        def ot(xs, ys, ws_a, ws_b, lx, ly):
+        def ot(xs, ys, ws_a, ws_b, lx, ly, presolved=None):
             sched = tuple(self._eps_list_for_inputs(xs, ys))
-            return _SinkhornCostFn.apply(xs, ys, ws_a, ws_b, sched, config, lx, ly, self.label_cost_matrix)
+            return _SinkhornCostFn.apply(xs, ys, ws_a, ws_b, sched, config, lx, ly, self.label_cost_matrix,
+                                         presolved)
+
+        multi_gpu = (self.process_group is not None and self.backend != "alternating"
+                     and torch.distributed.get_world_size(self.process_group) > 1)
 
         def divergence(xs, ys, ws_a, ws_b):
-            cross = ot(xs, ys, ws_a, ws_b, label_x, label_y)
             if not self.debias:
-                return cross
-            return cross - 0.5 * ot(xs, xs, ws_a, ws_a, label_x, label_x) - 0.5 * ot(ys, ys, ws_b, ws_b, label_y, label_y)
+                return ot(xs, ys, ws_a, ws_b, label_x, label_y)
+            terms = [(xs, ys, ws_a, ws_b, label_x, label_y), (xs, xs, ws_a, ws_a, label_x, label_x),
+                     (ys, ys, ws_b, ws_b, label_y, label_y)]
+            pre = [None, None, None]
+            if multi_gpu:
+                # The three solves are independent: run them interleaved so that the all-gather of one
+                # overlaps the compute of the next, then hand the potentials to the cost nodes.
+                with torch.no_grad():
+                    sols = sinkhorn_flashstyle_symmetric_many(
+                        [(t[0].detach(), t[1].detach(), t[2].detach(), t[3].detach()) for t in terms],
+                        process_group=self.process_group, blur=self.blur, scaling=self.scaling,
+                        use_epsilon_scaling=self.use_epsilon_scaling, eps=self.eps, n_iters=self.n_iters,
+                        allow_tf32=self.allow_tf32, cost_scale=self.cost_scale, rho_x=self.rho_x,
+                        rho_y=self.rho_y, last_extrapolation=self.last_extrapolation,
+                        threshold=self.threshold, check_every=self.inner_iterations)
+                pre = [(f, g, f, g) if fp is None else (f, g, fp, gp) for (f, g, fp, gp, _) in sols]
+            cross, self_x, self_y = (ot(*t, presolved=p) for t, p in zip(terms, pre))
+            return cross - 0.5 * self_x - 0.5 * self_y
 
         if parsed.batched:
             items = zip(parsed.x, parsed.y, parsed.a, parsed.b)

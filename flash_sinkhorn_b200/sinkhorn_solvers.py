@@ -26,6 +26,16 @@ from flash_sinkhorn_b200.kernels._common import (
 __all__ = ["sinkhorn_flashstyle_alternating", "sinkhorn_flashstyle_symmetric", "tile_mask_to_csr"]
 
 
+def _same_tensor(u: Optional[torch.Tensor], v: Optional[torch.Tensor]) -> bool:
+    """True when u and v are the same view of the same memory (identity, or e.g. two ``detach()`` of one tensor)."""
+    if u is v:
+        return True
+    if u is None or v is None:
+        return False
+    return (u.data_ptr() == v.data_ptr() and u.shape == v.shape and u.stride() == v.stride()
+            and u.dtype == v.dtype and u.device == v.device)
+
+
 def _neg_if_none(v: Optional[float]) -> float:
     return -1.0 if v is None else float(v)
 
@@ -173,6 +183,7 @@ def sinkhorn_flashstyle_symmetric(
     lambda_x: float = 1.0,
     lambda_y: float = 0.0,
     process_group=None,
+    _prepare_only: bool = False,
 ):
     """GeomLoss-style symmetric Sinkhorn (Jacobi steps averaged with weight 1/2).
 
@@ -214,20 +225,23 @@ def sinkhorn_flashstyle_symmetric(
     # A self-transport problem (OT(a,a): the debiasing terms pass the same tensors twice) keeps the same
     # buffers on both sides; the engine recognises it by pointer equality and runs one soft-min per step.
     x32 = _lib.f32c(x)
-    y32 = x32 if y is x else _lib.f32c(y)
+    y32 = x32 if _same_tensor(y, x) else _lib.f32c(y)
     log_a = log_weights(a).contiguous()
-    log_b = log_a if b is a else log_weights(b).contiguous()
+    log_b = log_a if _same_tensor(b, a) else log_weights(b).contiguous()
     fi = None if f_init is None else _lib.f32c(f_init)
-    gi = None if g_init is None else (fi if g_init is f_init else _lib.f32c(g_init))
+    gi = None if g_init is None else (fi if _same_tensor(g_init, f_init) else _lib.f32c(g_init))
     prec = _lib.precision_id(allow_tf32)
 
     if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
         from flash_sinkhorn_b200.distributed import symmetric_solve_sharded
 
-        f, g, f_pre, g_pre, steps = symmetric_solve_sharded(
-            x32, y32, log_a, log_b, list(eps_list), cost_scale=float(cost_scale), rho_x=rho_x, rho_y=rho_y,
-            last_extrapolation=bool(last_extrapolation), threshold=threshold, check_every=int(check_every),
-            f_init=fi, g_init=gi, prec=prec, group=process_group)
+        sharded_args = dict(
+            x=x32, y=y32, log_a=log_a, log_b=log_b, eps_list=list(eps_list), cost_scale=float(cost_scale),
+            rho_x=rho_x, rho_y=rho_y, last_extrapolation=bool(last_extrapolation), threshold=threshold,
+            check_every=int(check_every), f_init=fi, g_init=gi, prec=prec)
+        if _prepare_only:
+            return sharded_args
+        f, g, f_pre, g_pre, steps = symmetric_solve_sharded(group=process_group, **sharded_args)
         out = (f, g)
         if return_prelast and last_extrapolation:
             out = out + (f_pre, g_pre)
@@ -259,3 +273,25 @@ def sinkhorn_flashstyle_symmetric(
     if return_n_iters:
         out = out + (int(iters.item()),)
     return out
+
+
+def sinkhorn_flashstyle_symmetric_many(problems, *, process_group, **kwargs):
+    """Several independent symmetric solves on a multi-GPU ``process_group`` with their steps interleaved.
+
+    Extension without a reference counterpart. ``problems`` is a sequence of ``(x, y, a, b)``; ``kwargs``
+    are keyword arguments of :func:`sinkhorn_flashstyle_symmetric` shared by all of them. Returns one
+    ``(f, g, f_prelast, g_prelast, n_steps)`` tuple per problem (the pre-extrapolation potentials are
+    ``None`` without ``last_extrapolation``). Each result equals the one-at-a-time solve bit for bit;
+    interleaving only lets the all-gather of one problem overlap the compute of the next.
+    """
+    from flash_sinkhorn_b200.distributed import symmetric_solve_sharded_many
+
+    if process_group is None or torch.distributed.get_world_size(process_group) < 2:
+        raise ValueError("sinkhorn_flashstyle_symmetric_many needs a process group with at least two ranks")
+    for drop in ("return_n_iters", "return_prelast", "_prepare_only"):
+        kwargs.pop(drop, None)
+    prepared = [
+        sinkhorn_flashstyle_symmetric(x, y, a, b, process_group=process_group, _prepare_only=True, **kwargs)
+        for (x, y, a, b) in problems
+    ]
+    return symmetric_solve_sharded_many(prepared, group=process_group)

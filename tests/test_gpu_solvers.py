@@ -259,8 +259,14 @@ def test_self_transport_shortcut_is_bit_exact(monkeypatch, mode, threshold):
     x, a = dev(z["x"]), dev(z["a"])
     kw = dict(use_epsilon_scaling=False, eps=0.5, n_iters=25, threshold=threshold, check_every=4,
               return_prelast=True, return_n_iters=True)
-    one = sinkhorn_flashstyle_symmetric(x, x, a, a, **kw)
+    from flash_sinkhorn_b200 import _lib
+    lib = _lib.load()
+    c0 = lib.fs_launch_count()
+    one = sinkhorn_flashstyle_symmetric(x, x.detach(), a, a.detach(), **kw)  # same memory, other objects
+    c1 = lib.fs_launch_count()
     two = sinkhorn_flashstyle_symmetric(x, x.clone(), a, a.clone(), **kw)
+    c2 = lib.fs_launch_count()
+    assert c1 - c0 < c2 - c1  # the shortcut really ran fewer kernels
     assert one[4] == two[4]
     for u, v in zip(one[:4], two[:4]):
         assert torch.equal(u, v)

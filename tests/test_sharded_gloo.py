@@ -19,51 +19,63 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, case, out_dir):
+def _worker(rank, world, port, cases, out_dir):
+    """Runs the given cases with their steps interleaved (one case = the plain one-problem loop)."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from flash_sinkhorn_b200.distributed import run_symmetric_sharded, shard_layout, shard_range
-
-        z = load_golden("solvers_small")
-        x, y = z["x"].astype(np.float64), z["y"].astype(np.float64)
-        a, b = z["a"].astype(np.float64), z[case["b"]].astype(np.float64)
-        if case.get("self"):
-            y, b = x, a
-        n, m = x.shape[0], y.shape[0]
-        cs, rx, ry = case["cs"], case["rho_x"], case["rho_y"]
-        alpha, beta = cs * O.sqnorm(x), cs * O.sqnorm(y)
-        la, lb = O.log_weights(a), O.log_weights(b)
-
-        def step_fn(f_old, g_old, f_new, g_new, eps, w, rng):
-            f_lo, f_hi, g_lo, g_hi = rng
-            fo, go = f_old[:n].numpy(), g_old[:m].numpy()
-            df, dg = O.dampening(eps, rx), O.dampening(eps, ry)
-            cf = O.lse_update_fused(x[f_lo:f_hi], y, go, lb, eps, cs, df)   # only this rank's rows
-            cg = O.lse_update_fused(y[g_lo:g_hi], x, fo, la, eps, cs, dg)
-            nf = (1 - w) * fo[f_lo:f_hi] + w * cf - (w * alpha[f_lo:f_hi] * (1 - df) if df < 1 else 0.0)
-            ng = (1 - w) * go[g_lo:g_hi] + w * cg - (w * beta[g_lo:g_hi] * (1 - dg) if dg < 1 else 0.0)
-            f_new[f_lo:f_hi] = torch.from_numpy(nf)
-            g_new[g_lo:g_hi] = torch.from_numpy(ng)
-
-        def gather_fn(buf, shard):
-            dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard].clone())
-
-        # small alignment so that two ranks really split these ~100-row clouds
+        from flash_sinkhorn_b200.distributed import run_many, sharded_steps, shard_layout, shard_range
         import flash_sinkhorn_b200.distributed as D
+        # small alignment so that two ranks really split these ~100-row clouds
         D.SHARD_ALIGN = 8
         D.shard_layout.__defaults__ = (8,)
         D.shard_range.__defaults__ = (8,)
-        assert shard_layout(n, world) * world >= n and shard_range(n, world, world - 1)[1] == n
-        fh, gh, fp, gp, steps = run_symmetric_sharded(
-            n, m, torch.from_numpy(-alpha), torch.from_numpy(-beta), case["eps_list"],
-            last_extrapolation=True, threshold=case["threshold"], check_every=case["check_every"],
-            world=world, rank=rank, step_fn=step_fn, gather_fn=gather_fn, self_problem=bool(case.get("self")))
-        np.savez(os.path.join(out_dir, f"rank{rank}.npz"), f=fh.numpy() + alpha, g=gh.numpy() + beta,
-                 f_pre=fp.numpy() + alpha, g_pre=gp.numpy() + beta, steps=steps)
+        built = [_build(case, rank, world, sharded_steps, shard_layout, shard_range) for case in cases]
+        results = run_many([g for g, _ in built])
+        for i, ((_, fin), res) in enumerate(zip(built, results)):
+            np.savez(os.path.join(out_dir, f"rank{rank}_{i}.npz"), **fin(res))
     finally:
         dist.destroy_process_group()
+
+
+def _build(case, rank, world, sharded_steps, shard_layout, shard_range):
+    z = load_golden("solvers_small")
+    x, y = z["x"].astype(np.float64), z["y"].astype(np.float64)
+    a, b = z["a"].astype(np.float64), z[case["b"]].astype(np.float64)
+    if case.get("self"):
+        y, b = x, a
+    n, m = x.shape[0], y.shape[0]
+    cs, rx, ry = case["cs"], case["rho_x"], case["rho_y"]
+    alpha, beta = cs * O.sqnorm(x), cs * O.sqnorm(y)
+    la, lb = O.log_weights(a), O.log_weights(b)
+
+    def step_fn(f_old, g_old, f_new, g_new, eps, w, rng):
+        f_lo, f_hi, g_lo, g_hi = rng
+        fo, go = f_old[:n].numpy(), g_old[:m].numpy()
+        df, dg = O.dampening(eps, rx), O.dampening(eps, ry)
+        cf = O.lse_update_fused(x[f_lo:f_hi], y, go, lb, eps, cs, df)   # only this rank's rows
+        cg = O.lse_update_fused(y[g_lo:g_hi], x, fo, la, eps, cs, dg)
+        nf = (1 - w) * fo[f_lo:f_hi] + w * cf - (w * alpha[f_lo:f_hi] * (1 - df) if df < 1 else 0.0)
+        ng = (1 - w) * go[g_lo:g_hi] + w * cg - (w * beta[g_lo:g_hi] * (1 - dg) if dg < 1 else 0.0)
+        f_new[f_lo:f_hi] = torch.from_numpy(nf)
+        g_new[g_lo:g_hi] = torch.from_numpy(ng)
+
+    def gather_fn(buf, shard):
+        dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard].clone())
+
+    assert shard_layout(n, world) * world >= n and shard_range(n, world, world - 1)[1] == n
+    gen = sharded_steps(
+        n, m, torch.from_numpy(-alpha), torch.from_numpy(-beta), case["eps_list"],
+        last_extrapolation=True, threshold=case["threshold"], check_every=case["check_every"],
+        world=world, rank=rank, step_fn=step_fn, gather_fn=gather_fn, self_problem=bool(case.get("self")))
+
+    def finish(res):
+        fh, gh, fp, gp, steps = res
+        return dict(f=fh.numpy() + alpha, g=gh.numpy() + beta, f_pre=fp.numpy() + alpha,
+                    g_pre=gp.numpy() + beta, steps=steps)
+
+    return gen, finish
 
 
 CASES = {
@@ -83,14 +95,35 @@ def test_two_rank_sharded_loop_equals_unsharded_oracle(tmp_path, name):
     if case["eps_list"] is None:
         case["eps_list"] = [float(e) for e in z["sched"]]
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), [case], str(tmp_path)), nprocs=world, join=True)
+    _check(tmp_path, 0, name, case, z, world)
+
+
+def test_interleaved_problems_equal_one_at_a_time(tmp_path):
+    """Three problems with different schedule lengths stepped round-robin (what the multi-GPU divergence
+    does): each must come out exactly as when solved alone."""
+    z = load_golden("solvers_small")
+    names = ["unbalanced_schedule", "self_transport", "early_stop"]
+    cases = []
+    for nm in names:
+        c = dict(CASES[nm])
+        if c["eps_list"] is None:
+            c["eps_list"] = [float(e) for e in z["sched"]]
+        cases.append(c)
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), cases, str(tmp_path)), nprocs=world, join=True)
+    for i, (nm, c) in enumerate(zip(names, cases)):
+        _check(tmp_path, i, nm, c, z, world)
+
+
+def _check(tmp_path, idx, name, case, z, world):
     x, y = z["x"].astype(np.float64), z["y"].astype(np.float64)
     a, b = z["a"].astype(np.float64), z[case["b"]].astype(np.float64)
     if case.get("self"):
         y, b = x, a
     want = O.solve_symmetric(x, y, a, b, case["eps_list"], cost_scale=case["cs"], rho_x=case["rho_x"],
                              rho_y=case["rho_y"], threshold=case["threshold"], check_every=case["check_every"])
-    ranks = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    ranks = [np.load(tmp_path / f"rank{r}_{idx}.npz") for r in range(world)]
     for r in ranks:
         assert int(r["steps"]) == want["n_iters"]
         for k in ("f", "g", "f_pre", "g_pre"):
