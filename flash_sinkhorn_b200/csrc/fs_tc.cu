@@ -238,11 +238,12 @@ struct KernelParams {
   float eps;
   LseEpilogue ep;
   // Column split: blockIdx.y owns tiles [y*tiles_per_chunk, ...). With gridDim.y > 1 every CTA writes
-  // its partial (scale2*max, sum) pair per row and lse_combine_kernel finishes the update.
+  // its partial (scale2*max, sum) pair per row; the last CTA of a row block to finish merges them.
   int tiles_per_chunk;
   float* part_m;
   float* part_s;
   int part_stride;
+  int* tickets;  // one counter per row block, zero between launches
 };
 
 // Soft-max warpgroups per 128-row half: each takes half of every tile's 32-column chunks (more warps per
@@ -262,7 +263,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   const bool split = gridDim.y > 1;
 
   if (p.ep.ctrl && p.ep.ctrl->converged) {  // solve already stopped: identity step
-    if (!split && p.ep.old && p.ep.out)     // (with a column split the combine kernel does the copy)
+    if (blockIdx.y == 0 && p.ep.old && p.ep.out)
       for (int r = tid; r < 128 * NHALF; r += blockDim.x)
         if (row0 + r < p.nr) p.ep.out[row0 + r] = p.ep.old[row0 + r];
     return;
@@ -280,6 +281,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
             A_FULL = S_EMPTY + 2 * NHALF, DRAIN = A_FULL + 1, NBARS = DRAIN + 1;
   uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* last_flag = (volatile int*)(tmem_slot + 2);  // this CTA took the last ticket of its row block
   float* merge_off = (float*)(tmem_slot + 4);        // [NHALF*128] partials of the second column part
   float* merge_sum = merge_off + NHALF * 128;
   auto bar = [&](int i) { return smem_u32(bars + i); };
@@ -512,22 +514,45 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       s_run = s_run * ex2(off_run - on) + s2 * ex2(o2 - on);
       off_run = on;
     }
-    if (ok && part == 0 && r < p.nr) {
-      if (split) {
+    // Column split: every CTA of a row block publishes its (offset, sum) pair per row; the CTA that
+    // finishes last (ticket counter per row block) merges all pairs in chunk order - the result does not
+    // depend on which CTA that is - and applies the epilogue. No separate combine launch.
+    bool finish = !split;
+    if (split) {
+      if (ok && part == 0 && r < p.nr) {
         p.part_m[(size_t)blockIdx.y * p.part_stride + r] = off_run;
         p.part_s[(size_t)blockIdx.y * p.part_stride + r] = s_run;
-      } else {
-        const LseEpilogue& ep = p.ep;
-        float lse2 = off_run + log2f(fmaxf(s_run, 1e-40f));
-        if (ep.lse2) ep.lse2[r] = lse2;
-        if (ep.out) {
-          float cand = -p.eps * ep.damping * (lse2 * kLn2);
-          float o = ep.w * cand;
-          if (ep.old) o += (1.0f - ep.w) * ep.old[r];
-          if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
-          if (ep.addvec) o += ep.addcoef * ep.addvec[r];
-          ep.out[r] = o;
+      }
+      __threadfence();  // the pairs must be visible device-wide before the ticket is taken
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
+      if (warp == 4 && lane == 0) *last_flag = (atomicAdd(p.tickets + blockIdx.x, 1) == (int)gridDim.y - 1) ? 1 : 0;
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
+      finish = *last_flag != 0;
+      if (finish) {
+        __threadfence();
+        if (part == 0 && r < p.nr) {
+          float M = __ldcg(p.part_m + r);
+          for (int c = 1; c < (int)gridDim.y; ++c) M = fmaxf(M, __ldcg(p.part_m + (size_t)c * p.part_stride + r));
+          float S = 0.f;
+          for (int c = 0; c < (int)gridDim.y; ++c)
+            S += __ldcg(p.part_s + (size_t)c * p.part_stride + r) * ex2(__ldcg(p.part_m + (size_t)c * p.part_stride + r) - M);
+          off_run = M;
+          s_run = S;
         }
+        if (warp == 4 && lane == 0) p.tickets[blockIdx.x] = 0;  // ready for the next launch on this stream
+      }
+    }
+    if (finish && ok && part == 0 && r < p.nr && !*abort_flag) {
+      const LseEpilogue& ep = p.ep;
+      float lse2 = off_run + log2f(fmaxf(s_run, 1e-40f));
+      if (ep.lse2) ep.lse2[r] = lse2;
+      if (ep.out) {
+        float cand = -p.eps * ep.damping * (lse2 * kLn2);
+        float o = ep.w * cand;
+        if (ep.old) o += (1.0f - ep.w) * ep.old[r];
+        if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
+        if (ep.addvec) o += ep.addcoef * ep.addvec[r];
+        ep.out[r] = o;
       }
     }
   }
@@ -1050,31 +1075,6 @@ cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUten
   return cudaGetLastError();
 }
 
-// Merges the per-chunk (scaled max, sum) pairs of a column-split LSE pass and applies the epilogue.
-__global__ void lse_combine_kernel(int row_begin, int nr, int nchunk, const float* __restrict__ pm,
-                                   const float* __restrict__ ps, int stride, float eps, LseEpilogue ep) {
-  int r = row_begin + blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= nr) return;
-  if (ep.ctrl && ep.ctrl->converged) {
-    if (ep.old && ep.out) ep.out[r] = ep.old[r];
-    return;
-  }
-  float M = pm[r];
-  for (int c = 1; c < nchunk; ++c) M = fmaxf(M, pm[(size_t)c * stride + r]);
-  float S = 0.f;
-  for (int c = 0; c < nchunk; ++c) S += ps[(size_t)c * stride + r] * ex2(pm[(size_t)c * stride + r] - M);
-  float lse2 = M + log2f(fmaxf(S, 1e-40f));
-  if (ep.lse2) ep.lse2[r] = lse2;
-  if (ep.out) {
-    float cand = -eps * ep.damping * (lse2 * kLn2);
-    float o = ep.w * cand;
-    if (ep.old) o += (1.0f - ep.w) * ep.old[r];
-    if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
-    if (ep.addvec) o += ep.addcoef * ep.addvec[r];
-    ep.out[r] = o;
-  }
-}
-
 constexpr int kMaxChunks = 16;
 constexpr int kNumSMs = 148;
 
@@ -1120,6 +1120,7 @@ size_t staged_bytes(int n, int m, int d, int prec) {
   b += 2 * (((size_t)pad256(n) * per_row + 1023) & ~size_t(1023));
   b += 2 * (((size_t)pad256(m) * per_row + 1023) & ~size_t(1023));
   b += 2 * (size_t)kMaxChunks * pad256(n > m ? n : m) * sizeof(float);  // column-split partials
+  b += (size_t)(pad256(n > m ? n : m) / 128) * sizeof(int);             // row-block tickets
   return b + 1024;
 }
 
@@ -1146,6 +1147,11 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
   s.part_stride = pad256(n > m ? n : m);
   s.part_m = reinterpret_cast<float*>(p);
   s.part_s = s.part_m + (size_t)kMaxChunks * s.part_stride;
+  s.tickets = reinterpret_cast<int*>(s.part_s + (size_t)kMaxChunks * s.part_stride);
+  if (run_kernels) {
+    cudaError_t e = cudaMemsetAsync(s.tickets, 0, (size_t)(s.part_stride / 128) * sizeof(int), st);
+    if (e != cudaSuccess) return e;
+  }
   return cudaGetLastError();
 }
 
@@ -1178,16 +1184,13 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
   if (nblk <= 0) return cudaSuccess;
   const int chunks = pick_chunks(nblk, kp.ntiles);
   kp.tiles_per_chunk = (kp.ntiles + chunks - 1) / chunks;
-  kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride;
+  kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride; kp.tickets = s.tickets;
   dim3 grid(nblk, chunks);
   cudaError_t err;
   if (sh.nhalf == 2) err = launch<2, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   else if (sh.bn == 128) err = launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   else err = launch<1, 64>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  if (err != cudaSuccess || chunks == 1) return err;
-  lse_combine_kernel<<<(a.nr - a.row_begin + 255) / 256, 256, 0, st>>>(a.row_begin, a.nr, chunks, s.part_m, s.part_s,
-                                                                       s.part_stride, a.eps, e);
-  return cudaGetLastError();
+  return err;
 }
 
 // ---- plan-times-matrix host side ----

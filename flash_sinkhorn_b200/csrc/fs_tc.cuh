@@ -24,6 +24,7 @@ struct Staged {
   float* part_m = nullptr;  // [chunks, part_stride] partial scaled maxima of a column-split pass
   float* part_s = nullptr;  // [chunks, part_stride] partial sums
   int part_stride = 0;
+  int* tickets = nullptr;   // [rows_pad / 128] per-row-block arrival counters of a column-split pass (zero at rest)
 };
 
 bool supported(int n, int m, int d, int prec);
