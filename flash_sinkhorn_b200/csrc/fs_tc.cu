@@ -237,9 +237,11 @@ struct KernelParams {
   float scale2;      // 2*cs*log2e/eps: logit = scale2 * S
   float eps;
   LseEpilogue ep;
-  // Column split: blockIdx.y owns tiles [y*tiles_per_chunk, ...). With gridDim.y > 1 every CTA writes
-  // its partial (scale2*max, sum) pair per row; the last CTA of a row block to finish merges them.
-  int tiles_per_chunk;
+  // Work split: the nblk x ntiles (row block, column tile) items are laid out row block after row block
+  // and cut into gridDim.x equal contiguous ranges, one per CTA (one CTA per SM, a single wave). A CTA's
+  // range may end one row block and begin the next; a row block shared by several CTAs gets one partial
+  // (scale2*max, sum) pair per row from each, and the last of them to finish merges the pairs.
+  int nblk;
   float* part_m;
   float* part_s;
   int part_stride;
@@ -257,15 +259,24 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
               const KernelParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = p.row_begin + blockIdx.x * (128 * NHALF);
-  const int t0 = blockIdx.y * p.tiles_per_chunk;
-  const int nt = (p.ntiles - t0 < p.tiles_per_chunk) ? (p.ntiles - t0) : p.tiles_per_chunk;
-  const bool split = gridDim.y > 1;
+  constexpr int BM = 128 * NHALF;
+  // This CTA's items [w_begin, w_end) of the flattened (row block, column tile) list.
+  const long long total_items = (long long)p.nblk * p.ntiles;
+  const int w_begin = (int)((total_items * blockIdx.x) / gridDim.x);
+  const int w_end = (int)((total_items * (blockIdx.x + 1)) / gridDim.x);
+  // First item of CTA c; CTA holding item t (largest c whose first item is <= t).
+  auto cta_first = [&](int c) { return (int)((total_items * c) / gridDim.x); };
+  auto cta_of = [&](int t) {
+    int c = (int)(((long long)t * gridDim.x) / total_items);
+    while (c + 1 < (int)gridDim.x && cta_first(c + 1) <= t) ++c;
+    while (c > 0 && cta_first(c) > t) --c;
+    return c;
+  };
 
   if (p.ep.ctrl && p.ep.ctrl->converged) {  // solve already stopped: identity step
-    if (blockIdx.y == 0 && p.ep.old && p.ep.out)
-      for (int r = tid; r < 128 * NHALF; r += blockDim.x)
-        if (row0 + r < p.nr) p.ep.out[row0 + r] = p.ep.old[row0 + r];
+    if (p.ep.old && p.ep.out)
+      for (int r = p.row_begin + blockIdx.x * blockDim.x + tid; r < p.nr; r += gridDim.x * blockDim.x)
+        p.ep.out[r] = p.ep.old[r];
     return;
   }
 
@@ -278,7 +289,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   uint64_t* bars = (uint64_t*)(b_smem + p.nstage * b_stage_bytes);
   // barrier indices
   const int B_FULL = 0, B_EMPTY = p.nstage, S_FULL = 2 * p.nstage, S_EMPTY = S_FULL + 2 * NHALF,
-            A_FULL = S_EMPTY + 2 * NHALF, DRAIN = A_FULL + 1, NBARS = DRAIN + 1;
+            A_FULL = S_EMPTY + 2 * NHALF, A_EMPTY = A_FULL + 1, DRAIN = A_EMPTY + 1, NBARS = DRAIN + 1;
   uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   volatile int* last_flag = (volatile int*)(tmem_slot + 2);  // this CTA took the last ticket of its row block
@@ -298,6 +309,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       mbar_init(bar(S_EMPTY + i), 4 * kParts);  // one arrive per soft-max warp reading the buffer
     }
     mbar_init(bar(A_FULL), 1);
+    mbar_init(bar(A_EMPTY), 1);
     mbar_init(bar(DRAIN), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -315,34 +327,58 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      mbar_expect_tx(bar(A_FULL), NHALF * a_half_bytes);
-#pragma unroll 1
-      for (int h = 0; h < NHALF; ++h) {
-        uint32_t dst = smem_u32(a_smem + h * a_half_bytes);
-        for (int kb = 0; kb < p.nfull; ++kb)
-          tma_load_2d(dst + kb * (128 * 128), &mapA_full, kb * 32, row0 + h * 128, bar(A_FULL));
-        for (int t = 0; t < p.ntail; ++t)
-          tma_load_2d(dst + p.nfull * (128 * 128) + t * (128 * 32), &mapA_tail, p.nfull * 32 + t * 8,
-                      row0 + h * 128, bar(A_FULL));
-      }
-      int issued = 0;
-#pragma unroll 1
-      for (int j = 0; j < nt; ++j) {
-        const int s = j % p.nstage;
-        const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
+      int issued = 0, seg = 0;  // column tiles issued so far by this CTA (ring position), segment count
+      bool ok = true;
+      // Column tile `issued` (a CTA-wide running index) of the segment that starts at item w0.
+      auto load_b = [&](int j) -> bool {
+        const int s = issued % p.nstage;
+        const uint32_t ph = (issued / p.nstage) & 1;
+        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 2000)) return false;
         mbar_expect_tx(bar(B_FULL + s), b_stage_bytes);
         uint32_t dst = smem_u32(b_smem + s * b_stage_bytes);
-        const int col0 = (t0 + j) * BN;
+        const int col0 = j * BN;
         for (int kb = 0; kb < p.nfull; ++kb)
           tma_load_2d(dst + kb * (BN * 128), &mapB_full, kb * 32, col0, bar(B_FULL + s));
         for (int t = 0; t < p.ntail; ++t)
           tma_load_2d(dst + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, col0,
                       bar(B_FULL + s));
-        issued = j + 1;
+        ++issued;
+        return true;
+      };
+      int pre = 0;  // column tiles of the current segment that were already issued during the previous one
+#pragma unroll 1
+      for (int w = w_begin; ok && w < w_end; ++seg) {
+        const int blk = w / p.ntiles, j0 = w - blk * p.ntiles;
+        const int j1 = (p.ntiles - j0 < w_end - w) ? p.ntiles : j0 + (w_end - w);
+        const int row0 = p.row_begin + blk * BM;
+        // The row operand of the previous segment must have been read by its last MMA.
+        if (!mbar_wait(bar(A_EMPTY), (seg & 1) ^ 1, abort_flag, 2000)) break;
+        mbar_expect_tx(bar(A_FULL), NHALF * a_half_bytes);
+#pragma unroll 1
+        for (int h = 0; h < NHALF; ++h) {
+          uint32_t dst = smem_u32(a_smem + h * a_half_bytes);
+          for (int kb = 0; kb < p.nfull; ++kb)
+            tma_load_2d(dst + kb * (128 * 128), &mapA_full, kb * 32, row0 + h * 128, bar(A_FULL));
+          for (int t = 0; t < p.ntail; ++t)
+            tma_load_2d(dst + p.nfull * (128 * 128) + t * (128 * 32), &mapA_tail, p.nfull * 32 + t * 8,
+                        row0 + h * 128, bar(A_FULL));
+        }
+#pragma unroll 1
+        for (int j = j0 + pre; ok && j < j1; ++j) ok = load_b(j);
+        w += j1 - j0;
+        // Next segment (another row block, columns from 0): its first column tiles do not need the new row
+        // operand, so they go into ring slots as this segment's tiles retire - every slot waited for here
+        // holds a tile of this or an earlier segment, which the MMA lane consumes without the next A.
+        pre = 0;
+        if (ok && w < w_end) {
+          const int nnext = (p.ntiles < w_end - w) ? p.ntiles : (w_end - w);
+          const int npre = nnext < p.nstage ? nnext : p.nstage;
+#pragma unroll 1
+          for (; ok && pre < npre; ++pre) ok = load_b(pre);
+        }
       }
       if (*abort_flag) {  // let every copy we issued land before the CTA goes away
-        mbar_wait_quiet(bar(A_FULL), 0);
+        if (seg > 0) mbar_wait_quiet(bar(A_FULL), (seg - 1) & 1);
         for (int j = (issued > p.nstage ? issued - p.nstage : 0); j < issued; ++j)
           mbar_wait_quiet(bar(B_FULL + j % p.nstage), (j / p.nstage) & 1);
       }
@@ -351,64 +387,71 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // ===================== MMA issuer =====================
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BN);
-      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 2000);
-      tc_fence_after();
       const uint32_t a_lo0 = desc_lo(smem_u32(a_smem));
       const uint32_t a_half_units = a_half_bytes >> 4;
+      bool ok = true;
+      int jt = 0, seg = 0;  // column tiles processed so far by this CTA (ring / buffer position), segment count
 #pragma unroll 1
-      for (int j = 0; ok && j < nt; ++j) {
-        const int s = j % p.nstage;
-        const uint32_t ph = (j / p.nstage) & 1;
-        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) break;
+      for (int w = w_begin; ok && w < w_end; ++seg) {
+        const int blk = w / p.ntiles, j0 = w - blk * p.ntiles;
+        const int nseg = (p.ntiles - j0 < w_end - w) ? (p.ntiles - j0) : (w_end - w);
+        if (!mbar_wait(bar(A_FULL), seg & 1, abort_flag, 2000)) break;
         tc_fence_after();
-        const uint32_t b_addr = smem_u32(b_smem + s * b_stage_bytes);
-        const int buf = j & 1;
-        const uint32_t sph = (j >> 1) & 1;
-        // Both halves' accumulators must be free, then their K chains are interleaved: consecutive MMAs
-        // into the same accumulator are dependent (each waits for the previous one to retire), two
-        // independent chains keep the tensor pipe busy.
 #pragma unroll 1
-        for (int h = 0; h < NHALF; ++h) {
-          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000)) { ok = false; break; }
-        }
-        if (!ok) break;
-        tc_fence_after();
-        // The issuing thread is a single lane: every integer instruction it spends per MMA is exposed
-        // latency (~5 cycles each). Descriptors are therefore advanced incrementally: the low word holds
-        // (address >> 4), the high word (stride, version, swizzle) is a constant per block class.
-        const uint32_t d_tmem0 = tmem_base + (uint32_t)(buf * BN);
-        uint32_t al = a_lo0, bl = desc_lo(b_addr);
-        uint32_t acc = 0;
+        for (int i = 0; i < nseg; ++i, ++jt) {
+          const int s = jt % p.nstage;
+          const uint32_t ph = (jt / p.nstage) & 1;
+          if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t b_addr = smem_u32(b_smem + s * b_stage_bytes);
+          const int buf = jt & 1;
+          const uint32_t sph = (jt >> 1) & 1;
+          // Both halves' accumulators must be free, then their K chains are interleaved: two independent
+          // accumulators in flight keep the tensor pipe busy.
 #pragma unroll 1
-        for (int kb = 0; kb < p.nfull; ++kb) {
+          for (int h = 0; h < NHALF; ++h) {
+            if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000)) { ok = false; break; }
+          }
+          if (!ok) break;
+          tc_fence_after();
+          // The issuing thread is a single lane: every integer instruction it spends per MMA is exposed
+          // latency (~5 cycles each). Descriptors are therefore advanced incrementally: the low word holds
+          // (address >> 4), the high word (stride, version, swizzle) is a constant per block class.
+          const uint32_t d_tmem0 = tmem_base + (uint32_t)(buf * BN);
+          uint32_t al = a_lo0, bl = desc_lo(b_addr);
+          uint32_t acc = 0;
+#pragma unroll 1
+          for (int kb = 0; kb < p.nfull; ++kb) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t bd = pack_desc(bl + 2 * ks, kDescHi128);
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint64_t bd = pack_desc(bl + 2 * ks, kDescHi128);
+#pragma unroll
+              for (int h = 0; h < NHALF; ++h) {
+                umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units + 2 * ks, kDescHi128), bd,
+                          idesc, acc);
+              }
+              acc = 1;
+            }
+            al += (128 * 128) >> 4;
+            bl += (BN * 128) >> 4;
+          }
+#pragma unroll 1
+          for (int t = 0; t < p.ntail; ++t) {
+            const uint64_t bd = pack_desc(bl, kDescHi32);
 #pragma unroll
             for (int h = 0; h < NHALF; ++h) {
-              umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units + 2 * ks, kDescHi128), bd,
-                        idesc, acc);
+              umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units, kDescHi32), bd, idesc, acc);
             }
             acc = 1;
+            al += (128 * 32) >> 4;
+            bl += (BN * 32) >> 4;
           }
-          al += (128 * 128) >> 4;
-          bl += (BN * 128) >> 4;
-        }
-#pragma unroll 1
-        for (int t = 0; t < p.ntail; ++t) {
-          const uint64_t bd = pack_desc(bl, kDescHi32);
 #pragma unroll
-          for (int h = 0; h < NHALF; ++h) {
-            umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units, kDescHi32), bd, idesc, acc);
-          }
-          acc = 1;
-          al += (128 * 32) >> 4;
-          bl += (BN * 32) >> 4;
+          for (int h = 0; h < NHALF; ++h) umma_commit(bar(S_FULL + h * 2 + buf));
+          umma_commit(bar(B_EMPTY + s));
         }
-#pragma unroll
-        for (int h = 0; h < NHALF; ++h) umma_commit(bar(S_FULL + h * 2 + buf));
-        if (!ok) break;
-        umma_commit(bar(B_EMPTY + s));
+        umma_commit(bar(A_EMPTY));  // the row operand may be replaced once every MMA issued so far retired
+        w += nseg;
       }
       if (*abort_flag) {  // wait (bounded) for every MMA issued so far before TMEM is freed
         umma_commit(bar(DRAIN));
@@ -429,7 +472,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     float m_run = kRunInit, off_run = __fmul_rn(scale, kRunInit), s_run = 0.f;
     bool ok = true;
     constexpr int CH = BN / 32 / kParts;  // 32-column chunks of a tile owned by this warpgroup
-    const int total = nt * CH;
+    const int total = (w_end - w_begin) * CH;  // chunks of all segments; g / CH counts the CTA's tiles
     const int c_base = part * CH;
     // One online-softmax update with the 32 scores of a chunk (this thread's row).
     auto consume = [&](const uint32_t (&r)[32]) {
@@ -482,7 +525,86 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         if (lane == 0) mbar_arrive(bar(S_EMPTY + h * 2 + (j & 1)));
       }
     };
-    // Software pipeline, two register buffers: the load of chunk g+1 is in flight while chunk g is consumed.
+    // End of a segment (the part of one row block this CTA covers): merge the two column parts, then either
+    // finish the rows (the block is ours alone) or publish the (offset, sum) pair per row; the CTA that
+    // publishes last (ticket counter per row block) merges all pairs in piece order - the result does not
+    // depend on which CTA that is - and applies the epilogue. Every soft-max warp runs the same barrier
+    // sequence for every segment, also after an abort (live = false), so the named barriers always match.
+    auto finalize = [&](int blk, bool live) {
+      const int r = p.row_begin + blk * BM + h * 128 + q * 32 + lane;
+      if (part == 1) {  // second column part parks its partial in shared memory
+        merge_off[h * 128 + q * 32 + lane] = live ? off_run : kRunInit;
+        merge_sum[h * 128 + q * 32 + lane] = live ? s_run : 0.f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");  // soft-max warps only
+      if (part == 0) {
+        const float o2 = merge_off[h * 128 + q * 32 + lane], s2 = merge_sum[h * 128 + q * 32 + lane];
+        const float on = fmaxf(off_run, o2);
+        s_run = s_run * ex2(off_run - on) + s2 * ex2(o2 - on);
+        off_run = on;
+      }
+      const int c_lo = cta_of(blk * p.ntiles), c_hi = cta_of((blk + 1) * p.ntiles - 1);
+      const int pieces = c_hi - c_lo + 1, piece = (int)blockIdx.x - c_lo;
+      bool finish = pieces == 1;
+      if (pieces > 1) {
+        if (live && part == 0 && r < p.nr) {
+          p.part_m[(size_t)piece * p.part_stride + r] = off_run;
+          p.part_s[(size_t)piece * p.part_stride + r] = s_run;
+        }
+        __threadfence();  // the pairs must be visible device-wide before the ticket is taken
+        asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
+        if (warp == 4 && lane == 0) *last_flag = (atomicAdd(p.tickets + blk, 1) == pieces - 1) ? 1 : 0;
+        asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
+        finish = *last_flag != 0;
+        if (finish) {
+          __threadfence();
+          if (part == 0 && r < p.nr) {
+            float M = __ldcg(p.part_m + r);
+            for (int c = 1; c < pieces; ++c) M = fmaxf(M, __ldcg(p.part_m + (size_t)c * p.part_stride + r));
+            float S = 0.f;
+            for (int c = 0; c < pieces; ++c)
+              S += __ldcg(p.part_s + (size_t)c * p.part_stride + r) * ex2(__ldcg(p.part_m + (size_t)c * p.part_stride + r) - M);
+            off_run = M;
+            s_run = S;
+          }
+          if (warp == 4 && lane == 0) p.tickets[blk] = 0;  // ready for the next launch on this stream
+        }
+      }
+      if (finish && live && part == 0 && r < p.nr && !*abort_flag) {
+        const LseEpilogue& ep = p.ep;
+        float lse2 = off_run + log2f(fmaxf(s_run, 1e-40f));
+        if (ep.lse2) ep.lse2[r] = lse2;
+        if (ep.out) {
+          float cand = -p.eps * ep.damping * (lse2 * kLn2);
+          float o = ep.w * cand;
+          if (ep.old) o += (1.0f - ep.w) * ep.old[r];
+          if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
+          if (ep.addvec) o += ep.addcoef * ep.addvec[r];
+          ep.out[r] = o;
+        }
+      }
+      // merge_off / merge_sum / last_flag are re-used by the next segment
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
+      m_run = kRunInit;
+      off_run = __fmul_rn(scale, kRunInit);
+      s_run = 0.f;
+    };
+    // Segment bookkeeping: seg_w = first item of the current segment, seg_end_g = its last chunk + 1.
+    int seg_w = w_begin;
+    auto seg_len = [&](int w) {
+      const int j0 = w % p.ntiles;
+      return (p.ntiles - j0 < w_end - w) ? (p.ntiles - j0) : (w_end - w);
+    };
+    int seg_end_g = seg_len(seg_w) * CH;
+    auto consumed = [&](int g) {  // chunk g has been folded in: close the segment if it was its last chunk
+      if (g + 1 == seg_end_g) {
+        finalize(seg_w / p.ntiles, true);
+        seg_w += seg_len(seg_w);
+        if (seg_w < w_end) seg_end_g += seg_len(seg_w) * CH;
+      }
+    };
+    // Software pipeline, two register buffers: the load of chunk g+1 is in flight while chunk g is consumed
+    // (also across a segment boundary: the next row block's first scores load during the finalisation).
     uint32_t ra[32], rb[32];
     ok = issue(0, ra);
 #pragma unroll 1
@@ -493,6 +615,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         if (!ok) break;
       }
       consume(ra);
+      if (CH == 1) consumed(g);  // with two chunks per tile a segment can only end on the odd chunk
       if (g + 1 >= total) break;
       landed(g + 1, rb);
       if (g + 2 < total) {
@@ -500,60 +623,13 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         if (!ok) break;
       }
       consume(rb);
+      consumed(g + 1);
     }
-    const int r = row0 + h * 128 + q * 32 + lane;
-    // Second column part parks its partial in shared memory; the first part merges after the barrier.
-    if (part == 1) {
-      merge_off[h * 128 + q * 32 + lane] = ok ? off_run : kRunInit;
-      merge_sum[h * 128 + q * 32 + lane] = ok ? s_run : 0.f;
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");  // soft-max warps only
-    if (part == 0) {
-      const float o2 = merge_off[h * 128 + q * 32 + lane], s2 = merge_sum[h * 128 + q * 32 + lane];
-      const float on = fmaxf(off_run, o2);
-      s_run = s_run * ex2(off_run - on) + s2 * ex2(o2 - on);
-      off_run = on;
-    }
-    // Column split: every CTA of a row block publishes its (offset, sum) pair per row; the CTA that
-    // finishes last (ticket counter per row block) merges all pairs in chunk order - the result does not
-    // depend on which CTA that is - and applies the epilogue. No separate combine launch.
-    bool finish = !split;
-    if (split) {
-      if (ok && part == 0 && r < p.nr) {
-        p.part_m[(size_t)blockIdx.y * p.part_stride + r] = off_run;
-        p.part_s[(size_t)blockIdx.y * p.part_stride + r] = s_run;
-      }
-      __threadfence();  // the pairs must be visible device-wide before the ticket is taken
-      asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
-      if (warp == 4 && lane == 0) *last_flag = (atomicAdd(p.tickets + blockIdx.x, 1) == (int)gridDim.y - 1) ? 1 : 0;
-      asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
-      finish = *last_flag != 0;
-      if (finish) {
-        __threadfence();
-        if (part == 0 && r < p.nr) {
-          float M = __ldcg(p.part_m + r);
-          for (int c = 1; c < (int)gridDim.y; ++c) M = fmaxf(M, __ldcg(p.part_m + (size_t)c * p.part_stride + r));
-          float S = 0.f;
-          for (int c = 0; c < (int)gridDim.y; ++c)
-            S += __ldcg(p.part_s + (size_t)c * p.part_stride + r) * ex2(__ldcg(p.part_m + (size_t)c * p.part_stride + r) - M);
-          off_run = M;
-          s_run = S;
-        }
-        if (warp == 4 && lane == 0) p.tickets[blockIdx.x] = 0;  // ready for the next launch on this stream
-      }
-    }
-    if (finish && ok && part == 0 && r < p.nr && !*abort_flag) {
-      const LseEpilogue& ep = p.ep;
-      float lse2 = off_run + log2f(fmaxf(s_run, 1e-40f));
-      if (ep.lse2) ep.lse2[r] = lse2;
-      if (ep.out) {
-        float cand = -p.eps * ep.damping * (lse2 * kLn2);
-        float o = ep.w * cand;
-        if (ep.old) o += (1.0f - ep.w) * ep.old[r];
-        if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
-        if (ep.addvec) o += ep.addcoef * ep.addvec[r];
-        ep.out[r] = o;
-      }
+    // After an abort: keep the barrier sequence of the remaining segments (no data is written).
+#pragma unroll 1
+    while (seg_w < w_end) {
+      finalize(seg_w / p.ntiles, false);
+      seg_w += seg_len(seg_w);
     }
   }
 
@@ -1078,28 +1154,35 @@ cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUten
 constexpr int kMaxChunks = 16;
 constexpr int kNumSMs = 148;
 
-// Column chunks per row block: fill whole waves of the 148 SMs without making CTAs too short.
-int pick_chunks(int nblk, int ntiles) {
-  if (const char* env = getenv("FLASH_SINKHORN_B200_CHUNKS")) {  // diagnostics: force the column split
+// CTAs of an LSE pass. The nblk*ntiles (row block, column tile) items are cut into equal contiguous ranges,
+// one per CTA: a single wave of at most one CTA per SM, at least ~4 tiles each, and no row block shared by
+// more than kMaxChunks CTAs (that many partial slots exist per row).
+int pick_ctas(int nblk, int ntiles) {
+  const long long total = (long long)nblk * ntiles;
+  long long g = kNumSMs;
+  if (const char* env = getenv("FLASH_SINKHORN_B200_CTAS")) {  // diagnostics: force the CTA count
     int c = atoi(env);
-    if (c >= 1 && c <= kMaxChunks && c <= ntiles) {
-      int tpc = (ntiles + c - 1) / c;
-      return (ntiles + tpc - 1) / tpc;
+    if (c >= 1 && c <= kNumSMs) g = c;
+  }
+  if (g > (total + 3) / 4) g = (total + 3) / 4;
+  if (g > total) g = total;
+  if (g < 1) g = 1;
+  auto first = [&](long long c) { return (total * c) / g; };
+  auto owner = [&](long long t) {
+    long long c = (t * g) / total;
+    while (c + 1 < g && first(c + 1) <= t) ++c;
+    while (c > 0 && first(c) > t) --c;
+    return c;
+  };
+  for (; g > 1; --g) {
+    long long worst = 1;
+    for (int b = 0; b < nblk && worst <= kMaxChunks; ++b) {
+      long long pieces = owner((long long)(b + 1) * ntiles - 1) - owner((long long)b * ntiles) + 1;
+      if (pieces > worst) worst = pieces;
     }
+    if (worst <= kMaxChunks) break;
   }
-  int best = 1;
-  double best_score = -1.0;
-  for (int c = 1; c <= kMaxChunks && c <= ntiles; ++c) {
-    int tpc = (ntiles + c - 1) / c;
-    int ce = (ntiles + tpc - 1) / tpc;  // chunks that actually get tiles
-    if (ce != c) continue;
-    long items = (long)nblk * ce;
-    long waves = (items + kNumSMs - 1) / kNumSMs;
-    double eff = (double)items / (double)(waves * kNumSMs);
-    double score = eff - 0.004 * c - (tpc < 4 ? 0.1 : 0.0);  // per-CTA set-up cost; avoid tiny chunks
-    if (score > best_score) { best_score = score; best = c; }
-  }
-  return best;
+  return (int)g;
 }
 
 }  // namespace
@@ -1182,10 +1265,9 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
   const int bm = 128 * sh.nhalf;
   const int nblk = (a.nr - a.row_begin + bm - 1) / bm;
   if (nblk <= 0) return cudaSuccess;
-  const int chunks = pick_chunks(nblk, kp.ntiles);
-  kp.tiles_per_chunk = (kp.ntiles + chunks - 1) / chunks;
+  kp.nblk = nblk;
   kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride; kp.tickets = s.tickets;
-  dim3 grid(nblk, chunks);
+  dim3 grid(pick_ctas(nblk, kp.ntiles));
   cudaError_t err;
   if (sh.nhalf == 2) err = launch<2, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   else if (sh.bn == 128) err = launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
