@@ -289,7 +289,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   uint64_t* bars = (uint64_t*)(b_smem + p.nstage * b_stage_bytes);
   // barrier indices
   const int B_FULL = 0, B_EMPTY = p.nstage, S_FULL = 2 * p.nstage, S_EMPTY = S_FULL + 2 * NHALF,
-            A_FULL = S_EMPTY + 2 * NHALF, A_EMPTY = A_FULL + 1, DRAIN = A_EMPTY + 1, NBARS = DRAIN + 1;
+            A_FULL = S_EMPTY + 2 * NHALF, A_EMPTY = A_FULL + 1, DRAIN = A_EMPTY + 1, NBARS = DRAIN + 2;
   uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   volatile int* last_flag = (volatile int*)(tmem_slot + 2);  // this CTA took the last ticket of its row block
@@ -302,15 +302,16 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   if (tid == 0) {
     for (int s = 0; s < p.nstage; ++s) {
       mbar_init(bar(B_FULL + s), 1);
-      mbar_init(bar(B_EMPTY + s), 1);
+      mbar_init(bar(B_EMPTY + s), NHALF);  // one commit per MMA-issuing lane (one lane per 128-row half)
     }
     for (int i = 0; i < 2 * NHALF; ++i) {
       mbar_init(bar(S_FULL + i), 1);
       mbar_init(bar(S_EMPTY + i), 4 * kParts);  // one arrive per soft-max warp reading the buffer
     }
     mbar_init(bar(A_FULL), 1);
-    mbar_init(bar(A_EMPTY), 1);
+    mbar_init(bar(A_EMPTY), NHALF);
     mbar_init(bar(DRAIN), 1);
+    mbar_init(bar(DRAIN + 1), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -383,12 +384,15 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           mbar_wait_quiet(bar(B_FULL + j % p.nstage), (j / p.nstage) & 1);
       }
     }
-  } else if (warp == 1) {
-    // ===================== MMA issuer =====================
+  } else if (warp == 1 || (warp == 3 && NHALF == 2)) {
+    // ===================== MMA issuers: one lane per 128-row half =====================
+    // A lane that shares its scheduler with soft-max warps sustains one MMA per ~90 cycles, the tensor pipe
+    // one per 64: with one lane per half (warps 1 and 3) the score tiles of the next column tile are ready
+    // well before the soft-max warps ask for them, instead of just in time.
     if (lane == 0) {
+      const int h = (warp == 1) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc(BN);
-      const uint32_t a_lo0 = desc_lo(smem_u32(a_smem));
-      const uint32_t a_half_units = a_half_bytes >> 4;
+      const uint32_t a_lo0 = desc_lo(smem_u32(a_smem + h * a_half_bytes));
       bool ok = true;
       int jt = 0, seg = 0;  // column tiles processed so far by this CTA (ring / buffer position), segment count
 #pragma unroll 1
@@ -402,34 +406,21 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           const int s = jt % p.nstage;
           const uint32_t ph = (jt / p.nstage) & 1;
           if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t b_addr = smem_u32(b_smem + s * b_stage_bytes);
           const int buf = jt & 1;
           const uint32_t sph = (jt >> 1) & 1;
-          // Both halves' accumulators must be free, then their K chains are interleaved: two independent
-          // accumulators in flight keep the tensor pipe busy.
-#pragma unroll 1
-          for (int h = 0; h < NHALF; ++h) {
-            if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000)) { ok = false; break; }
-          }
-          if (!ok) break;
+          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000)) { ok = false; break; }
           tc_fence_after();
           // The issuing thread is a single lane: every integer instruction it spends per MMA is exposed
           // latency (~5 cycles each). Descriptors are therefore advanced incrementally: the low word holds
           // (address >> 4), the high word (stride, version, swizzle) is a constant per block class.
-          const uint32_t d_tmem0 = tmem_base + (uint32_t)(buf * BN);
-          uint32_t al = a_lo0, bl = desc_lo(b_addr);
+          const uint32_t d_tmem = tmem_base + (uint32_t)((h * 2 + buf) * BN);
+          uint32_t al = a_lo0, bl = desc_lo(smem_u32(b_smem + s * b_stage_bytes));
           uint32_t acc = 0;
 #pragma unroll 1
           for (int kb = 0; kb < p.nfull; ++kb) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              const uint64_t bd = pack_desc(bl + 2 * ks, kDescHi128);
-#pragma unroll
-              for (int h = 0; h < NHALF; ++h) {
-                umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units + 2 * ks, kDescHi128), bd,
-                          idesc, acc);
-              }
+              umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
               acc = 1;
             }
             al += (128 * 128) >> 4;
@@ -437,25 +428,20 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           }
 #pragma unroll 1
           for (int t = 0; t < p.ntail; ++t) {
-            const uint64_t bd = pack_desc(bl, kDescHi32);
-#pragma unroll
-            for (int h = 0; h < NHALF; ++h) {
-              umma_tf32(d_tmem0 + (uint32_t)(h * 2 * BN), pack_desc(al + h * a_half_units, kDescHi32), bd, idesc, acc);
-            }
+            umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc, acc);
             acc = 1;
             al += (128 * 32) >> 4;
             bl += (BN * 32) >> 4;
           }
-#pragma unroll
-          for (int h = 0; h < NHALF; ++h) umma_commit(bar(S_FULL + h * 2 + buf));
+          umma_commit(bar(S_FULL + h * 2 + buf));
           umma_commit(bar(B_EMPTY + s));
         }
         umma_commit(bar(A_EMPTY));  // the row operand may be replaced once every MMA issued so far retired
         w += nseg;
       }
-      if (*abort_flag) {  // wait (bounded) for every MMA issued so far before TMEM is freed
-        umma_commit(bar(DRAIN));
-        mbar_wait_quiet(bar(DRAIN), 0);
+      if (*abort_flag) {  // wait (bounded) for every MMA issued by this lane before TMEM is freed
+        umma_commit(bar(DRAIN + h));
+        mbar_wait_quiet(bar(DRAIN + h), 0);
       }
     }
   } else if (warp >= 4) {
@@ -490,7 +476,10 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       // product would leak into the exponent; with the huge init/mask magnitudes it even overflows).
       const float off_new = __fmul_rn(scale, m_new);
       const float nms = -off_new;
-      float s0 = s_run * ex2(off_run - off_new), s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      // After the first tiles the running max rarely moves; when it moved for no row of the warp the
+      // rescale factor is exactly 2^0 and its ex2 (one slot of the saturated pipe in 33) is skipped.
+      float s0 = s_run, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      if (__any_sync(0xffffffffu, off_new != off_run)) s0 *= ex2(off_run - off_new);
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         s0 += ex2(fmaf(v[i], scale, nms));
