@@ -313,7 +313,11 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "exp" if exp_peak <= tc_peak else "tensor", "achieved": achieved, "peak": peak,
-                         "unit": "entries/s", "frac": achieved / peak, "traffic": None,
+                         "unit": "entries/s", "frac": achieved / peak,
+                         # DRAM bytes per launch of this kernel at this size, from the ncu capture summarised in
+                         # profiles/tc_lse_kernel_config2_50k_d64_tf32.md (algorithmic: 29.2 MB of staged operands)
+                         "traffic": 28925952 if (n == 50000 and m == 50000 and d == 64 and not args.fp32) else None,
+                         "traffic_unit": "bytes per launch (dram read + write)",
                          "kernel": "row soft-min pass (fs_lse), n*m entries per launch", "kernel_ms": kernel_ms,
                          "exp_peak": exp_peak, "exp_peak_nominal": exp_nominal, "tensor_peak": tc_peak,
                          "softmax_loop_rate": softmax_loop_rate,
