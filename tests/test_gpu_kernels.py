@@ -143,3 +143,27 @@ def test_argument_errors():
         SamplesLoss()(x, y, x)
     with pytest.raises(ValueError):
         SamplesLoss()(x.cpu(), y.cpu())
+
+
+@pytest.mark.parametrize("n,m", [(130, 40000), (40000, 130), (300, 9000), (5000, 5000), (2600, 777), (257, 1)])
+@pytest.mark.parametrize("ctas", [None, 1, 7, 148])
+def test_lse_work_split_shapes(monkeypatch, n, m, ctas):
+    """The tensor-core LSE pass cuts (row block, column tile) items into one contiguous range per CTA: row
+    blocks shared by up to 16 CTAs, CTAs spanning several row blocks, and forced CTA counts must all give the
+    torch.logsumexp answer (fp32-exact mode) and run-to-run identical bits."""
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse
+    if ctas is not None:
+        monkeypatch.setenv("FLASH_SINKHORN_B200_CTAS", str(ctas))
+    g = torch.Generator().manual_seed(n + 3 * m)
+    d, eps = 16, 0.25
+    x = (torch.randn(n, d, generator=g) / 4).cuda()
+    y = (torch.randn(m, d, generator=g) / 4).cuda()
+    bias = torch.randn(m, generator=g).cuda()
+    want = -eps * torch.logsumexp((2.0 / eps) * (x.double() @ y.double().T) + bias.double()[None, :], dim=1)
+    got = flashsinkhorn_lse(x, y, bias, eps, allow_tf32=False)
+    torch.testing.assert_close(got.double(), want, rtol=1e-4, atol=1e-4)
+    assert torch.equal(got, flashsinkhorn_lse(x, y, bias, eps, allow_tf32=False))
+    got_tf32 = flashsinkhorn_lse(x, y, bias, eps, allow_tf32=True)
+    torch.testing.assert_close(got_tf32.double(), want, rtol=5e-3, atol=5e-2)
+    assert _lib.load().fs_device_error() == 0
