@@ -13,7 +13,9 @@ from flash_sinkhorn_b200.hvp import (
     geomloss_to_ott_potentials,
     hvp_x_sqeuclid,
     hvp_x_sqeuclid_from_potentials,
+    inverse_hvp_x_sqeuclid_from_potentials,
 )
+from flash_sinkhorn_b200.implicit_grad import ImplicitGradInfo, implicit_grad_x, implicit_grad_x_from_potentials
 
 __all__ = [
     "SamplesLoss",
@@ -23,6 +25,10 @@ __all__ = [
     "geomloss_to_ott_potentials",
     "hvp_x_sqeuclid",
     "hvp_x_sqeuclid_from_potentials",
+    "inverse_hvp_x_sqeuclid_from_potentials",
+    "ImplicitGradInfo",
+    "implicit_grad_x",
+    "implicit_grad_x_from_potentials",
     "__version__",
 ]
 __version__ = "0.1.0"

@@ -21,10 +21,10 @@ struct CloudOps {
 struct Staged {
   CloudOps cloud[2];  // 0 = x, 1 = y
   int d = 0, kc = 0, kp = 0, prec = 0;
-  float* part_m = nullptr;  // [chunks, part_stride] partial scaled maxima of a column-split pass
-  float* part_s = nullptr;  // [chunks, part_stride] partial sums
+  float* part_m = nullptr;  // [pieces, part_stride] partial scaled maxima of row blocks shared by several CTAs
+  float* part_s = nullptr;  // [pieces, part_stride] partial sums
   int part_stride = 0;
-  int* tickets = nullptr;   // [rows_pad / 128] per-row-block arrival counters of a column-split pass (zero at rest)
+  int* tickets = nullptr;   // [rows_pad / 128] per-row-block arrival counters of the CTAs sharing a row block (zero at rest)
 };
 
 bool supported(int n, int m, int d, int prec);

@@ -34,6 +34,7 @@ __all__ = [
     "geomloss_to_ott_potentials",
     "ott_to_geomloss_potentials",
     "hvp_x_sqeuclid",
+    "inverse_hvp_x_sqeuclid_from_potentials",
     "hvp_x_sqeuclid_from_potentials",
     "sinkhorn_prelast_potentials_sqeuclid",
 ]
@@ -260,3 +261,65 @@ def hvp_x_sqeuclid(
         cg_stabilise_every=cg_stabilise_every, preconditioner=preconditioner, precond_terms=precond_terms,
         use_preconditioner=use_preconditioner, allow_tf32=allow_tf32,
     )
+
+
+def inverse_hvp_x_sqeuclid_from_potentials(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    f_hat: torch.Tensor,
+    g_hat: torch.Tensor,
+    gr: torch.Tensor,
+    *,
+    eps: float,
+    rho_x: Optional[float] = None,
+    rho_y: Optional[float] = None,
+    cost_scale: float = 1.0,
+    tau2: float = 1e-5,
+    max_outer_iter: int = 100,
+    outer_rtol: float = 1e-6,
+    outer_atol: float = 1e-6,
+    max_inner_iter: int = 100,
+    inner_rtol: float = 1e-8,
+    inner_atol: float = 1e-8,
+    cg_stabilise_every: int = 0,
+    preconditioner: str = "none",
+    precond_terms: int = 3,
+    use_preconditioner: bool = True,
+    allow_tf32: bool = False,
+    use_exp2: bool = True,
+    block_m: Optional[int] = None,
+    block_n: Optional[int] = None,
+    block_k: Optional[int] = None,
+    num_warps: int = 4,
+    num_stages: int = 2,
+):
+    """Solve ``H z = gr`` for the Hessian ``H`` of the OT cost in x (reference hvp.py:696-835).
+
+    Outer conjugate gradients on the flattened ``[n*d]`` vector with :func:`hvp_x_sqeuclid_from_potentials`
+    as the operator (whose own Schur-complement solve runs on the device with the ``inner_*`` tolerances).
+    Like the reference this assumes ``H`` is positive definite at the given potentials; when it is not, the
+    outer loop stops at ``max_outer_iter`` and ``info.cg_converged`` is False. ``cost_scale`` is an extension
+    (the reference's inverse solve is fixed to the full squared distance).
+    """
+    if x.ndim != 2 or y.ndim != 2 or gr.ndim != 2:
+        raise ValueError("x, y, gr must be 2D tensors.")
+    if not x.is_cuda or not y.is_cuda or not f_hat.is_cuda or not g_hat.is_cuda:
+        raise ValueError("inverse_hvp_x_sqeuclid_from_potentials requires CUDA tensors.")
+    n, d = x.shape
+    m, d2 = y.shape
+    if d != d2 or gr.shape != (n, d):
+        raise ValueError("Shapes must satisfy x:(n,d), y:(m,d), gr:(n,d).")
+
+    def hessian_times(flat: torch.Tensor) -> torch.Tensor:
+        out, _ = hvp_x_sqeuclid_from_potentials(
+            x, y, f_hat, g_hat, flat.reshape(n, d), eps=eps, rho_x=rho_x, rho_y=rho_y, cost_scale=cost_scale,
+            tau2=tau2, max_cg_iter=max_inner_iter, cg_rtol=inner_rtol, cg_atol=inner_atol,
+            cg_stabilise_every=cg_stabilise_every, preconditioner=preconditioner, precond_terms=precond_terms,
+            use_preconditioner=use_preconditioner, allow_tf32=allow_tf32,
+        )
+        return out.reshape(-1)
+
+    z, cg = conjugate_gradient(hessian_times, gr.float().reshape(-1), max_iter=max_outer_iter, rtol=outer_rtol,
+                               atol=outer_atol, stabilise_every=cg_stabilise_every)
+    info = HvpInfo(bool(cg.cg_converged), int(cg.cg_iters), float(cg.cg_residual), float(cg.cg_initial_residual))
+    return z.reshape(n, d), info

@@ -333,3 +333,53 @@ def hvp_x(x, y, f_ott, g_ott, A, eps, *, rho_x=None, rho_y=None, cost_scale=1.0,
     t5 = mat5(x, y, f_ott, g_ott, A, e, cost_scale)
     return dict(hvp=RTz / e + t1 + t2 + t3 + t4 + t5, cg_converged=conv, cg_iters=iters, cg_residual=res,
                 cg_initial_residual=r0)
+
+
+def inverse_hvp_x(x, y, f_ott, g_ott, gr, eps, *, cost_scale=1.0, tau2=1e-5, max_outer_iter=100,
+                  outer_rtol=1e-6, outer_atol=1e-6, direct_solve=False) -> Dict:
+    """hvp.py:696-835: outer CG on H z = gr with the HVP as operator (inner Schur systems solved densely).
+    direct_solve=True assembles H column by column and solves the n*d x n*d system instead."""
+    n, d = x.shape
+
+    def hessian_times(flat):
+        return hvp_x(x, y, f_ott, g_ott, flat.reshape(n, d), eps, cost_scale=cost_scale, tau2=tau2,
+                     direct_solve=True)["hvp"].reshape(-1)
+
+    b = gr.reshape(-1).astype(np.float64)
+    if direct_solve:
+        H = np.stack([hessian_times(col) for col in np.eye(n * d)], axis=1)
+        z = np.linalg.solve(H, b)
+        conv, iters, res, r0 = True, 0, float(np.linalg.norm(H @ z - b)), float(np.linalg.norm(b))
+    else:
+        z, conv, iters, res, r0 = conjugate_gradient(hessian_times, b, max_outer_iter, outer_rtol, outer_atol)
+    return dict(z=z.reshape(n, d), cg_converged=conv, cg_iters=iters, cg_residual=res, cg_initial_residual=r0)
+
+
+# --------------------------------------------------------------------------- implicit differentiation
+def implicit_grad_x(x, y, f_hat, g_hat, grad_f, grad_g, log_a, log_b, eps, *, cost_scale=1.0, tau2=1e-5,
+                    max_cg_iter=100, cg_rtol=1e-6, cg_atol=1e-6, direct_solve=False) -> Dict:
+    """implicit_grad.py:36-242 with the plan materialised: marginals r, c; Schur system
+    [diag(c + eps*tau2)/eps - P^T diag(1/r) P / eps] lam_g = grad_g - P^T (grad_f / r) (:176-194);
+    lam_f = eps grad_f / r - P lam_g / r (:202);
+    grad_x = (2/eps) [lam_f (x r - P y) + (P lam_g) x - P (lam_g y)] (:221-236)."""
+    e = float(eps)
+    P = plan_shifted(x, y, f_hat, g_hat, log_a, log_b, e, cost_scale)
+    r, c = P.sum(axis=1), P.sum(axis=0)
+    rhs = grad_g - P.T @ (grad_f / r)
+    diag = (c + e * tau2) / e
+
+    def schur(z):
+        return diag * z - P.T @ ((P @ z) / r) / e
+
+    if direct_solve:
+        S = np.diag(diag) - P.T @ (P / r[:, None]) / e
+        lam_g = np.linalg.solve(S, rhs)
+        conv, iters, res = True, 0, float(np.linalg.norm(schur(lam_g) - rhs))
+    else:
+        lam_g, conv, iters, res, _ = conjugate_gradient(schur, rhs, max_cg_iter, cg_rtol, cg_atol)
+    P_lam = P @ lam_g
+    lam_f = e * grad_f / r - P_lam / r
+    Py = P @ y
+    Py_lam = P @ (y * lam_g[:, None])
+    grad_x = (2.0 / e) * (lam_f[:, None] * (x * r[:, None] - Py) + P_lam[:, None] * x - Py_lam)
+    return dict(grad_x=grad_x, cg_converged=conv, cg_iters=iters, cg_residual=res)

@@ -229,6 +229,53 @@ def gen_hvp():
     save("hvp_small", **out)
 
 
+def gen_implicit():
+    """Implicit gradient (implicit_grad.py) and inverse HVP (hvp.py:696-835) of the reference, interpreter run.
+    The autotuned kernels cannot run without a GPU driver and these two wrappers do not forward
+    ``autotune``; the module-level names they call are therefore wrapped with ``autotune=False`` for the
+    run (functools.partial on the imported functions; no reference source is modified)."""
+    import functools
+
+    import flash_sinkhorn.hvp as ref_hvp
+    import flash_sinkhorn.implicit_grad as ref_ig
+
+    ref_ig.apply_plan_mat_flashstyle = functools.partial(ref_ig.apply_plan_mat_flashstyle, **MANUAL)
+    ref_hvp.hvp_x_sqeuclid_from_potentials = functools.partial(ref_hvp.hvp_x_sqeuclid_from_potentials,
+                                                               autotune=False)
+    n, m, d = 40, 32, 6
+    x, y, a, b = clouds(61, n, m, d, shift=0.2, weights="softmax")
+    gen = torch.Generator().manual_seed(62)
+    grad_f, grad_g = torch.randn(n, generator=gen), torch.randn(m, generator=gen)
+    out = dict(x=np32(x), y=np32(y), a=np32(a), b=np32(b), grad_f=np32(grad_f), grad_g=np32(grad_g))
+    for name, (eps, cs) in {"full": (0.45, 1.0), "half": (0.3, 0.5)}.items():
+        f, g = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=eps, n_iters=300,
+                                             allow_tf32=False, autotune=False, cost_scale=cs)
+        f_hat, g_hat = f - cs * (x**2).sum(1), g - cs * (y**2).sum(1)
+        gx, info = ref_ig.implicit_grad_x_from_potentials(x, y, f_hat, g_hat, grad_f, grad_g, eps=eps,
+                                                          log_a=a.log(), log_b=b.log(), cost_scale=cs,
+                                                          max_cg_iter=300)
+        out[name + "_eps"], out[name + "_cs"] = np.float64(eps), np.float64(cs)
+        out[name + "_f_hat"], out[name + "_g_hat"] = np32(f_hat), np32(g_hat)
+        out[name + "_grad_x"] = np32(gx)
+        out[name + "_cg"] = np.array([float(info.cg_converged), info.cg_iters, info.cg_residual], np.float64)
+    # inverse HVP where the Hessian is positive definite (large eps); small problem: every outer CG
+    # iteration is a full HVP with its own inner solve under the interpreter
+    n, m, d = 24, 20, 3
+    x, y, a, b = clouds(63, n, m, d, shift=0.2, weights="softmax")
+    gr = torch.randn(n, d, generator=torch.Generator().manual_seed(64))
+    eps = 5.0
+    f, g, fp, gp = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=eps, n_iters=200,
+                                                 allow_tf32=False, autotune=False, return_prelast=True)
+    f_ott, g_ott = geomloss_to_ott_potentials(fp, gp, a, b, eps=eps)
+    z, info = ref_hvp.inverse_hvp_x_sqeuclid_from_potentials(x, y, f_ott, g_ott, gr, eps=eps, max_outer_iter=80,
+                                                             max_inner_iter=300, block_m=32, block_n=32, block_k=16)
+    out.update(inv_x=np32(x), inv_y=np32(y), inv_a=np32(a), inv_b=np32(b), inv_gr=np32(gr),
+               inv_eps=np.float64(eps), inv_f_ott=np32(f_ott), inv_g_ott=np32(g_ott), inv_z=np32(z),
+               inv_cg=np.array([float(info.cg_converged), info.cg_iters, info.cg_residual,
+                                info.cg_initial_residual], np.float64))
+    save("implicit_small", **out)
+
+
 def gen_dense_reference():
     """The reference's dense oracles alone (no Triton): symmetric potentials, OTT alternating, gradients."""
     n, m, d = 128, 96, 32
@@ -286,9 +333,10 @@ def gen_config1():
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--skip-c1", action="store_true", help="skip the 4096x4096 dense solves (several minutes)")
-    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,dense,c1")
+    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,dense,c1")
     args = ap.parse_args()
-    which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "dense", "c1"}
+    which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "implicit", "dense",
+                                                         "c1"}
     print("reference version", flash_sinkhorn.__version__, "from", os.path.dirname(flash_sinkhorn.__file__))
     if "dense" in which:
         gen_dense_reference()
@@ -300,6 +348,8 @@ if __name__ == "__main__":
         gen_samples_loss()
     if "hvp" in which:
         gen_hvp()
+    if "implicit" in which:
+        gen_implicit()
     if "c1" in which and not args.skip_c1:
         gen_config1()
     sys.exit(0)

@@ -274,3 +274,41 @@ def test_self_transport_shortcut_is_bit_exact(monkeypatch, mode, threshold):
     want = O.solve_symmetric(z["x"].astype(np.float64), z["x"].astype(np.float64), z["a"].astype(np.float64),
                              z["a"].astype(np.float64), [0.5] * 25, threshold=threshold, check_every=4)
     assert rel(host(one[0]), want["f"]) < TOL[mode]
+
+
+@pytest.mark.parametrize("name", ["full", "half"])
+def test_implicit_gradient_vs_reference(monkeypatch, name):
+    """implicit_grad_x_from_potentials on the CUDA engine (device-resident Schur CG) against the reference's
+    result and the fp64 oracle; exact-fp32 products, as the reference defaults to."""
+    from flash_sinkhorn_b200 import implicit_grad_x, implicit_grad_x_from_potentials
+    set_mode(monkeypatch, "fp32")
+    z = load_golden("implicit_small")
+    x, y, a, b, gf, gg = (dev(z[k]) for k in ("x", "y", "a", "b", "grad_f", "grad_g"))
+    fh, gh = dev(z[name + "_f_hat"]), dev(z[name + "_g_hat"])
+    eps, cs = float(z[name + "_eps"]), float(z[name + "_cs"])
+    gx, info = implicit_grad_x_from_potentials(x, y, fh, gh, gf, gg, eps=eps, log_a=a.log(), log_b=b.log(),
+                                               cost_scale=cs, max_cg_iter=300)
+    assert info.cg_converged and info.cg_iters <= int(z[name + "_cg"][1]) + 10
+    assert rel(host(gx), z[name + "_grad_x"]) < 2e-3  # fp32 solves of a nearly singular system on both sides
+    f64 = lambda k: z[k].astype(np.float64)
+    want = O.implicit_grad_x(f64("x"), f64("y"), f64(name + "_f_hat"), f64(name + "_g_hat"), f64("grad_f"),
+                             f64("grad_g"), np.log(f64("a")), np.log(f64("b")), eps, cost_scale=cs,
+                             direct_solve=True)["grad_x"]
+    assert rel(host(gx), want) < 2e-3
+    # end-to-end wrapper: solves first, then differentiates (same potentials up to the solve's tolerance)
+    gx2, info2 = implicit_grad_x(x, y, a, b, gf, gg, eps=eps, cost_scale=cs, n_iters=300, max_cg_iter=300)
+    assert info2.cg_converged and rel(host(gx2), want) < 5e-3
+
+
+def test_inverse_hvp_vs_reference(monkeypatch):
+    from flash_sinkhorn_b200 import hvp_x_sqeuclid_from_potentials, inverse_hvp_x_sqeuclid_from_potentials
+    set_mode(monkeypatch, "fp32")
+    z = load_golden("implicit_small")
+    x, y, gr, fo, go = (dev(z[k]) for k in ("inv_x", "inv_y", "inv_gr", "inv_f_ott", "inv_g_ott"))
+    eps = float(z["inv_eps"])
+    sol, info = inverse_hvp_x_sqeuclid_from_potentials(x, y, fo, go, gr, eps=eps, max_outer_iter=80,
+                                                       max_inner_iter=300)
+    assert info.cg_converged and info.cg_iters <= int(z["inv_cg"][1]) + 10
+    assert rel(host(sol), z["inv_z"]) < 2e-3
+    back, _ = hvp_x_sqeuclid_from_potentials(x, y, fo, go, sol, eps=eps, max_cg_iter=300, cg_rtol=1e-8, cg_atol=1e-8)
+    assert rel(host(back), z["inv_gr"]) < 1e-4

@@ -157,3 +157,42 @@ def test_config1_golden_is_recorded():
     # Values measured independently during the survey of the reference (fp32 dense path).
     assert float(z["loss"]) == pytest.approx(36.8802109, rel=2e-6)
     assert float(z["grad_x_norm"]) == pytest.approx(0.128287598, rel=2e-4)
+
+
+@pytest.mark.parametrize("name", ["full", "half"])
+def test_implicit_gradient(name):
+    """Oracle vs the reference's implicit_grad_x_from_potentials (CG and direct solve of the Schur system)."""
+    z = load_golden("implicit_small")
+    x, y, a, b, gf, gg = d64(z, "x", "y", "a", "b", "grad_f", "grad_g")
+    fh, gh = d64(z, name + "_f_hat", name + "_g_hat")
+    eps, cs = float(z[name + "_eps"]), float(z[name + "_cs"])
+    want = z[name + "_grad_x"].astype(F64)
+    conv, iters, _ = z[name + "_cg"]
+    assert conv == 1.0
+    got = O.implicit_grad_x(x, y, fh, gh, gf, gg, np.log(a), np.log(b), eps, cost_scale=cs, max_cg_iter=300)
+    # the reference iterates in fp32, the oracle in fp64: it may need fewer steps, never noticeably more
+    assert got["cg_converged"] and got["cg_iters"] <= int(iters) + 3
+    # the Schur system is nearly singular along constants (only tau2 = 1e-5 regularises it), so the
+    # reference's fp32 solve carries ~5e-4 of error relative to this fp64 restatement
+    assert rel_err(got["grad_x"], want) < 2e-3
+    direct = O.implicit_grad_x(x, y, fh, gh, gf, gg, np.log(a), np.log(b), eps, cost_scale=cs, direct_solve=True)
+    assert rel_err(direct["grad_x"], want) < 2e-3
+    assert rel_err(direct["grad_x"], got["grad_x"]) < 1e-4
+
+
+def test_inverse_hvp():
+    """Oracle vs the reference's inverse_hvp_x_sqeuclid_from_potentials (positive definite case, eps = 5)."""
+    z = load_golden("implicit_small")
+    x, y, gr, fo, go = d64(z, "inv_x", "inv_y", "inv_gr", "inv_f_ott", "inv_g_ott")
+    eps = float(z["inv_eps"])
+    conv, iters, res, res0 = z["inv_cg"]
+    assert conv == 1.0 and res <= 1e-6 * res0 + 1e-6
+    want = z["inv_z"].astype(F64)
+    got = O.inverse_hvp_x(x, y, fo, go, gr, eps, max_outer_iter=80)
+    assert got["cg_converged"] and got["cg_iters"] <= int(iters) + 3
+    assert rel_err(got["z"], want) < 5e-4
+    direct = O.inverse_hvp_x(x, y, fo, go, gr, eps, direct_solve=True)
+    assert rel_err(direct["z"], want) < 5e-4
+    # H z reproduces the right-hand side
+    back = O.hvp_x(x, y, fo, go, direct["z"], eps, direct_solve=True)["hvp"]
+    assert rel_err(back, gr) < 1e-8
