@@ -15,6 +15,7 @@ from flash_sinkhorn_b200.hvp import (
     hvp_x_sqeuclid_from_potentials,
     inverse_hvp_x_sqeuclid_from_potentials,
 )
+from flash_sinkhorn_b200.c_transform import c_transform_cost, c_transform_fwd
 from flash_sinkhorn_b200.implicit_grad import ImplicitGradInfo, implicit_grad_x, implicit_grad_x_from_potentials
 
 __all__ = [
@@ -29,6 +30,8 @@ __all__ = [
     "ImplicitGradInfo",
     "implicit_grad_x",
     "implicit_grad_x_from_potentials",
+    "c_transform_fwd",
+    "c_transform_cost",
     "__version__",
 ]
 __version__ = "0.1.0"

@@ -188,6 +188,13 @@ struct Problem {
     if (use_tc) return tc::lse(staged, side, s, ep, st);
     return simt_lse(s, ep, st);
   }
+  // Hard c-transform: min_j(-2cs x_i.y_j + bias_j) and its smallest arg-min, rows of `side`.
+  cudaError_t argmin(int side, const float* bias, float* out_val, int* out_idx) const {
+    StreamArgs s = stream_args(side, bias, nullptr, 1.0f);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (use_tc) return tc::argmax(staged, side, s, out_val, out_idx, st);
+    return simt_argmin(s, out_val, out_idx, st);
+  }
   // Weighted pass. With a row normaliser R (log2 LSE of the same scores, from lse()) and the tensor-core
   // engine available it runs as a one-column matrix pass on tcgen05; otherwise on the CUDA-core engine.
   cudaError_t vec(int side, const float* pot, const float* logw, float eps, const VecArgs& v,
@@ -369,6 +376,19 @@ int fs_lse(const float* x, const float* y, int n, int m, int d, const float* pot
   ep.w = 1.f;
   ep.out = out;
   FS_CUDA(p.lse(0, pot, logw, eps, ep));
+  return FS_OK;
+}
+
+int fs_c_transform(const float* x, const float* y, int n, int m, int d, const float* bias, float cost_scale,
+                   float* out_val, int* out_idx, int prec, void* wsp, size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, 1.0f, cost_scale, prec));
+  if (!bias || !out_val || !out_idx) return fail(FS_ERR_BAD_ARG, "bias, out_val and out_idx must be non-null");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Problem p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  FS_CUDA(p.argmin(0, bias, out_val, out_idx));
   return FS_OK;
 }
 

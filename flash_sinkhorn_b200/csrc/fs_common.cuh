@@ -92,5 +92,7 @@ struct PvArgs {
 cudaError_t simt_lse(const StreamArgs& s, const LseEpilogue& e, cudaStream_t st);
 cudaError_t simt_vec(const StreamArgs& s, const VecArgs& v, cudaStream_t st);
 cudaError_t simt_pv(const StreamArgs& s, const PvArgs& p, cudaStream_t st);
+// min_j(-2cs rows_i.cols_j + s.pot[j]) and the smallest j attaining it (s.logw, s.eps unused).
+cudaError_t simt_argmin(const StreamArgs& s, float* out_val, int* out_idx, cudaStream_t st);
 
 }  // namespace fs

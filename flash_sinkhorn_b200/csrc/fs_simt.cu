@@ -318,7 +318,77 @@ __global__ void __launch_bounds__(NT) simt_pv_kernel(StreamArgs s, PvArgs p) {
   }
 }
 
+// Hard c-transform: out_val_i = min_j (-2cs x_i.y_j + bias_j), out_idx_i = the smallest j attaining it
+// (reference kernels/c_transform_sqeuclid.py:117-206). s.pot holds the bias. A thread visits its columns in
+// increasing order and replaces its candidate only on a strictly smaller value; the 16 candidates of a row
+// are merged with "smaller value, then smaller column".
+__global__ void __launch_bounds__(NT) simt_argmin_kernel(StreamArgs s, float* __restrict__ out_val,
+                                                         int* __restrict__ out_idx) {
+  __shared__ __align__(16) float As[TK][LDS_T];
+  __shared__ __align__(16) float Bs[TK][LDS_T];
+  __shared__ float bias_s[TN];
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  const int row0 = s.row_begin + blockIdx.x * TM;
+  const float coord = 2.0f * s.cost_scale;
+  float best[4];
+  int arg[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { best[i] = INFINITY; arg[i] = 0x7fffffff; }
+  const int ntiles = (s.nc + TN - 1) / TN;
+  for (int ct = 0; ct < ntiles; ++ct) {
+    const int col0 = ct * TN;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    if (tid < TN) bias_s[tid] = (col0 + tid < s.nc) ? __ldg(s.pot + col0 + tid) : INFINITY;
+    for (int k0 = 0; k0 < s.d; k0 += TK) {
+      __syncthreads();
+      stage_tile(As, s.rows, row0, s.nr, k0, s.d, tid);
+      stage_tile(Bs, s.cols, col0, s.nc, k0, s.d, tid);
+      __syncthreads();
+      fma_tile(acc, As, Bs, ty, tx);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float bj = bias_s[tx * 4 + j];  // +inf masks padded columns
+      const int c = col0 + tx * 4 + j;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float v = fmaf(-coord, acc[i][j], bj);
+        if (v < best[i]) { best[i] = v; arg[i] = c; }
+      }
+    }
+    __syncthreads();  // bias_s is rewritten by the next tile
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) {
+      const float vo = __shfl_xor_sync(0xffffffffu, best[i], off);
+      const int ao = __shfl_xor_sync(0xffffffffu, arg[i], off);
+      if (vo < best[i] || (vo == best[i] && ao < arg[i])) { best[i] = vo; arg[i] = ao; }
+    }
+  }
+  if (tx == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = row0 + ty * 4 + i;
+      if (r < s.nr) { out_val[r] = best[i]; out_idx[r] = arg[i]; }
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t simt_argmin(const StreamArgs& s, float* out_val, int* out_idx, cudaStream_t st) {
+  if (s.nr - s.row_begin <= 0) return cudaSuccess;
+  dim3 grid((s.nr - s.row_begin + TM - 1) / TM);
+  simt_argmin_kernel<<<grid, NT, 0, st>>>(s, out_val, out_idx);
+  return cudaGetLastError();
+}
 
 cudaError_t simt_lse(const StreamArgs& s, const LseEpilogue& e, cudaStream_t st) {
   if (s.nr - s.row_begin <= 0) return cudaSuccess;

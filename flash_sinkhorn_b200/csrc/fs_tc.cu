@@ -246,13 +246,16 @@ struct KernelParams {
   float* part_s;
   int part_stride;
   int* tickets;  // one counter per row block, zero between launches
+  int* out_idx;  // AM kernels: arg-max column per row (values go to ep.out, multiplied by scale2)
 };
 
 // Soft-max warpgroups per 128-row half: each takes half of every tile's 32-column chunks (more warps per
 // scheduler to hide the fixed latencies around the chunk max / rescale); their partials merge at the end.
 constexpr int kParts = 2;
 
-template <int NHALF, int BN>
+// AM = false: online log-sum-exp of the scaled scores (potential update). AM = true: running maximum of the
+// raw scores and the smallest column attaining it (hard c-transform); no exponentials at all.
+template <int NHALF, int BN, bool AM>
 __global__ void __launch_bounds__(128 + 128 * NHALF * kParts, 1)
 tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constant__ CUtensorMap mapA_tail,
               const __grid_constant__ CUtensorMap mapB_full, const __grid_constant__ CUtensorMap mapB_tail,
@@ -456,12 +459,14 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // It is carried as the ROUNDED value scale*max (not recomputed from the max), so that rescaling by
     // 2^(off_old - off_new) and the final off_run + log2(s_run) are exact identities in fp32.
     float m_run = kRunInit, off_run = __fmul_rn(scale, kRunInit), s_run = 0.f;
+    int idx_run = 0;   // AM: column of the running maximum m_run
+    int col_tile = w_begin % p.ntiles;  // AM: column tile of the chunk being consumed
     bool ok = true;
     constexpr int CH = BN / 32 / kParts;  // 32-column chunks of a tile owned by this warpgroup
     const int total = (w_end - w_begin) * CH;  // chunks of all segments; g / CH counts the CTA's tiles
     const int c_base = part * CH;
     // One online-softmax update with the 32 scores of a chunk (this thread's row).
-    auto consume = [&](const uint32_t (&r)[32]) {
+    auto consume = [&](const uint32_t (&r)[32], int chunk_in_tile) {
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -471,6 +476,18 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       t[10] = fmaxf(v[30], v[31]);
       float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
       float cm = fmaxf(max3(u0, u1, u2), fmaxf(t[9], t[10]));
+      if (AM) {
+        // Columns are visited in increasing order by this thread, so a later column only replaces the
+        // running maximum when strictly larger; inside the chunk the smallest index attaining cm wins.
+        if (cm > m_run) {
+          int bi = 31;
+#pragma unroll
+          for (int i = 30; i >= 0; --i) bi = (v[i] == cm) ? i : bi;
+          m_run = cm;
+          idx_run = col_tile * BN + (c_base + chunk_in_tile) * 32 + bi;
+        }
+        return;
+      }
       const float m_new = fmaxf(m_run, cm);
       // __fmul_rn: must not be contracted into an FMA with the subtraction below (the residual of the
       // product would leak into the exponent; with the huge init/mask magnitudes it even overflows).
@@ -521,24 +538,30 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // sequence for every segment, also after an abort (live = false), so the named barriers always match.
     auto finalize = [&](int blk, bool live) {
       const int r = p.row_begin + blk * BM + h * 128 + q * 32 + lane;
+      // AM: a partial is (maximum, column); the larger maximum wins, equal maxima keep the smaller column.
+      auto better = [](float va, int ia, float vb, int ib) { return vb > va || (vb == va && ib < ia); };
       if (part == 1) {  // second column part parks its partial in shared memory
-        merge_off[h * 128 + q * 32 + lane] = live ? off_run : kRunInit;
-        merge_sum[h * 128 + q * 32 + lane] = live ? s_run : 0.f;
+        merge_off[h * 128 + q * 32 + lane] = live ? (AM ? m_run : off_run) : kRunInit;
+        merge_sum[h * 128 + q * 32 + lane] = AM ? __int_as_float(idx_run) : (live ? s_run : 0.f);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");  // soft-max warps only
       if (part == 0) {
         const float o2 = merge_off[h * 128 + q * 32 + lane], s2 = merge_sum[h * 128 + q * 32 + lane];
-        const float on = fmaxf(off_run, o2);
-        s_run = s_run * ex2(off_run - on) + s2 * ex2(o2 - on);
-        off_run = on;
+        if (AM) {
+          if (better(m_run, idx_run, o2, __float_as_int(s2))) { m_run = o2; idx_run = __float_as_int(s2); }
+        } else {
+          const float on = fmaxf(off_run, o2);
+          s_run = s_run * ex2(off_run - on) + s2 * ex2(o2 - on);
+          off_run = on;
+        }
       }
       const int c_lo = cta_of(blk * p.ntiles), c_hi = cta_of((blk + 1) * p.ntiles - 1);
       const int pieces = c_hi - c_lo + 1, piece = (int)blockIdx.x - c_lo;
       bool finish = pieces == 1;
       if (pieces > 1) {
         if (live && part == 0 && r < p.nr) {
-          p.part_m[(size_t)piece * p.part_stride + r] = off_run;
-          p.part_s[(size_t)piece * p.part_stride + r] = s_run;
+          p.part_m[(size_t)piece * p.part_stride + r] = AM ? m_run : off_run;
+          p.part_s[(size_t)piece * p.part_stride + r] = AM ? __int_as_float(idx_run) : s_run;
         }
         __threadfence();  // the pairs must be visible device-wide before the ticket is taken
         asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
@@ -549,17 +572,34 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           __threadfence();
           if (part == 0 && r < p.nr) {
             float M = __ldcg(p.part_m + r);
-            for (int c = 1; c < pieces; ++c) M = fmaxf(M, __ldcg(p.part_m + (size_t)c * p.part_stride + r));
-            float S = 0.f;
-            for (int c = 0; c < pieces; ++c)
-              S += __ldcg(p.part_s + (size_t)c * p.part_stride + r) * ex2(__ldcg(p.part_m + (size_t)c * p.part_stride + r) - M);
-            off_run = M;
-            s_run = S;
+            if (AM) {
+              int I = __float_as_int(__ldcg(p.part_s + r));
+              for (int c = 1; c < pieces; ++c) {
+                const float vc = __ldcg(p.part_m + (size_t)c * p.part_stride + r);
+                const int ic = __float_as_int(__ldcg(p.part_s + (size_t)c * p.part_stride + r));
+                if (better(M, I, vc, ic)) { M = vc; I = ic; }
+              }
+              m_run = M;
+              idx_run = I;
+            } else {
+              for (int c = 1; c < pieces; ++c) M = fmaxf(M, __ldcg(p.part_m + (size_t)c * p.part_stride + r));
+              float S = 0.f;
+              for (int c = 0; c < pieces; ++c)
+                S += __ldcg(p.part_s + (size_t)c * p.part_stride + r) *
+                     ex2(__ldcg(p.part_m + (size_t)c * p.part_stride + r) - M);
+              off_run = M;
+              s_run = S;
+            }
           }
           if (warp == 4 && lane == 0) p.tickets[blk] = 0;  // ready for the next launch on this stream
         }
       }
-      if (finish && live && part == 0 && r < p.nr && !*abort_flag) {
+      if (AM) {
+        if (finish && live && part == 0 && r < p.nr && !*abort_flag) {
+          p.ep.out[r] = p.scale2 * m_run;  // scale2 = -2*cost_scale turns the maximal score into the minimal cost
+          p.out_idx[r] = idx_run;
+        }
+      } else if (finish && live && part == 0 && r < p.nr && !*abort_flag) {
         const LseEpilogue& ep = p.ep;
         float lse2 = off_run + log2f(fmaxf(s_run, 1e-40f));
         if (ep.lse2) ep.lse2[r] = lse2;
@@ -577,6 +617,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       m_run = kRunInit;
       off_run = __fmul_rn(scale, kRunInit);
       s_run = 0.f;
+      idx_run = 0;
     };
     // Segment bookkeeping: seg_w = first item of the current segment, seg_end_g = its last chunk + 1.
     int seg_w = w_begin;
@@ -586,10 +627,12 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     };
     int seg_end_g = seg_len(seg_w) * CH;
     auto consumed = [&](int g) {  // chunk g has been folded in: close the segment if it was its last chunk
+      if (AM && g % CH == CH - 1) ++col_tile;
       if (g + 1 == seg_end_g) {
         finalize(seg_w / p.ntiles, true);
         seg_w += seg_len(seg_w);
         if (seg_w < w_end) seg_end_g += seg_len(seg_w) * CH;
+        if (AM) col_tile = 0;  // every later segment starts a new row block at column 0
       }
     };
     // Software pipeline, two register buffers: the load of chunk g+1 is in flight while chunk g is consumed
@@ -603,7 +646,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         ok = issue(g + 1, rb);
         if (!ok) break;
       }
-      consume(ra);
+      consume(ra, g % CH);
       if (CH == 1) consumed(g);  // with two chunks per tile a segment can only end on the odd chunk
       if (g + 1 >= total) break;
       landed(g + 1, rb);
@@ -611,7 +654,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         ok = issue(g + 2, ra);
         if (!ok) break;
       }
-      consume(rb);
+      consume(rb, (g + 1) % CH);
       consumed(g + 1);
     }
     // After an abort: keep the barrier sequence of the remaining segments (no data is written).
@@ -1129,10 +1172,10 @@ Shape plan_shape(int d, int prec) {
   return s;
 }
 
-template <int NHALF, int BN>
+template <int NHALF, int BN, bool AM>
 cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUtensorMap& mb_f,
                    const CUtensorMap& mb_t, const KernelParams& kp, dim3 grid, size_t smem, cudaStream_t st) {
-  auto kern = tc_lse_kernel<NHALF, BN>;
+  auto kern = tc_lse_kernel<NHALF, BN, AM>;
   // Per device (context) attribute; cheap enough to set on every launch.
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
   if (e != cudaSuccess) return e;
@@ -1227,14 +1270,24 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
   return cudaGetLastError();
 }
 
-cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st) {
+namespace {
+// One streaming pass over the staged operands: LSE (out_idx == nullptr) or running arg-max of the raw scores.
+cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, int* out_idx,
+                        cudaStream_t st) {
   Shape sh = plan_shape(s.d, s.prec);
   if (!sh.ok) return cudaErrorNotSupported;
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
-  const float scale2 = (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;
-  bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, sh.kc, sh.kp, a.pot, a.logw,
-                                                       1.0f / a.eps, 1.0f / scale2, e.ctrl);
+  const bool am = out_idx != nullptr;
+  // LSE: logit = scale2 * (x.y + bias/scale2). Arg-max: cost = -2cs * (x.y - bias/(2cs)), so the column
+  // "bias" staged next to y is -bias/(2cs) (a.pot holds the raw bias, no log-weights) and scale2 = -2cs.
+  const float scale2 = am ? -2.0f * a.cost_scale : (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;
+  if (am)
+    bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, sh.kc, sh.kp, a.pot, nullptr, 1.0f,
+                                                         1.0f / (scale2 * kLog2e), nullptr);
+  else
+    bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, sh.kc, sh.kp, a.pot, a.logw,
+                                                         1.0f / a.eps, 1.0f / scale2, e.ctrl);
   CUtensorMap ma_f, ma_t, mb_f, mb_t;
   // A tensor map boxes are 128 rows; B boxes BN rows. When a K-block class is absent its map
   // still has to be a valid object: encode it over the first columns (never used by the kernel).
@@ -1256,12 +1309,28 @@ cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogu
   if (nblk <= 0) return cudaSuccess;
   kp.nblk = nblk;
   kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride; kp.tickets = s.tickets;
+  kp.out_idx = out_idx;
   dim3 grid(pick_ctas(nblk, kp.ntiles));
-  cudaError_t err;
-  if (sh.nhalf == 2) err = launch<2, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  else if (sh.bn == 128) err = launch<1, 128>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  else err = launch<1, 64>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  return err;
+  if (am) {
+    if (sh.nhalf == 2) return launch<2, 128, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+    if (sh.bn == 128) return launch<1, 128, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+    return launch<1, 64, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  }
+  if (sh.nhalf == 2) return launch<2, 128, false>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  if (sh.bn == 128) return launch<1, 128, false>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  return launch<1, 64, false>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+}
+}  // namespace
+
+cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st) {
+  return stream_pass(s, side, a, e, nullptr, st);
+}
+
+cudaError_t argmax(const Staged& s, int side, const StreamArgs& a, float* out_val, int* out_idx, cudaStream_t st) {
+  if (!out_val || !out_idx) return cudaErrorInvalidValue;
+  LseEpilogue e;
+  e.out = out_val;
+  return stream_pass(s, side, a, e, out_idx, st);
 }
 
 // ---- plan-times-matrix host side ----

@@ -36,6 +36,10 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
 // One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st);
 
+// Hard c-transform pass over the same staged operands: out_val_i = min_j(-2cs x_i.y_j + bias_j) and the
+// smallest column attaining it (a.pot = bias, a.logw ignored, a.eps unused).
+cudaError_t argmax(const Staged& s, int side, const StreamArgs& a, float* out_val, int* out_idx, cudaStream_t st);
+
 // Plan-times-matrix pass on the tensor cores (same staged operands, hence bit-identical scores
 // to the LSE passes). `scratch` holds the transposed, TF32-split copy of V (pv_scratch_bytes).
 bool pv_supported(int d, int prec, int dv);

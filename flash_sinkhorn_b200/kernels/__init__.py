@@ -7,6 +7,7 @@ from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import (
 )
 from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_mat_flashstyle, apply_plan_vec_flashstyle
 from flash_sinkhorn_b200.kernels.grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid
+from flash_sinkhorn_b200.kernels.c_transform_sqeuclid import c_transform_kernel
 
 __all__ = [
     "epsilon_schedule",
@@ -16,6 +17,7 @@ __all__ = [
     "apply_plan_vec_flashstyle",
     "apply_plan_mat_flashstyle",
     "sinkhorn_geomloss_online_grad_sqeuclid",
+    "c_transform_kernel",
 ]
 
 _LAZY = {

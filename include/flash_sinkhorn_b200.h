@@ -105,6 +105,15 @@ int fs_lse(const float* x, const float* y, int n, int m, int d,
            float eps, float cost_scale, float damping,
            int prec, void* ws, size_t ws_bytes, void* stream);
 
+/* Hard (non-entropic) c-transform, inner minimum:
+ *   out_val_i = min_j ( -2*cost_scale * x_i.y_j + bias_j ),   out_idx_i = the smallest j attaining it
+ * (the caller adds cost_scale*|x_i|^2 and passes bias_j = cost_scale*|y_j|^2 - psi_j). Same staged
+ * operands and tile engine as fs_lse (workspace: fs_workspace_bytes(FS_OP_LSE, ...)); prec selects TF32,
+ * 3xTF32 or true-fp32 products. Replaces kernels/c_transform_sqeuclid.py:219-354 (c_transform_kernel). */
+int fs_c_transform(const float* x, const float* y, int n, int m, int d,
+                   const float* bias, float cost_scale, float* out_val, int* out_idx,
+                   int prec, void* ws, size_t ws_bytes, void* stream);
+
 /* One Jacobi (symmetric) step: both sides read the OLD potentials.
  *   f_out = (1-w) f_hat + w * (-eps*damp_f*LSE_j[(2cs/eps)x_i.y_j + g_hat_j/eps + log_b_j])
  *   g_out likewise with roles swapped.

@@ -355,6 +355,24 @@ def inverse_hvp_x(x, y, f_ott, g_ott, gr, eps, *, cost_scale=1.0, tau2=1e-5, max
     return dict(z=z.reshape(n, d), cg_converged=conv, cg_iters=iters, cg_residual=res, cg_initial_residual=r0)
 
 
+# --------------------------------------------------------------------------- hard c-transform
+def c_transform(x, y, psi, cost_scale=1.0):
+    """c_transform.py:32-112 / kernels/c_transform_sqeuclid.py:117-206: c_i = min_j [cs|x_i-y_j|^2 - psi_j]
+    evaluated in the factored form alpha_i + min_j(-2cs x_i.y_j + cs|y_j|^2 - psi_j); first minimiser."""
+    inner = -2.0 * cost_scale * (x @ y.T) + (cost_scale * sqnorm(y) - psi)[None, :]
+    idx = np.argmin(inner, axis=1)
+    return cost_scale * sqnorm(x) + inner[np.arange(x.shape[0]), idx], idx.astype(np.int64)
+
+
+def c_transform_cost(x, y, psi, a, b, cost_scale=1.0) -> Dict:
+    """c_transform.py:115-174: L = <a, c^psi(x)> + <b, psi>; Danskin gradients at the arg-min."""
+    c, idx = c_transform(x, y, psi, cost_scale)
+    grad_x = (a * 2.0 * cost_scale)[:, None] * (x - y[idx])
+    mass = np.zeros(y.shape[0])
+    np.add.at(mass, idx, a)
+    return dict(loss=float(a @ c + b @ psi), grad_x=grad_x, grad_psi=b - mass, c=c, idx=idx)
+
+
 # --------------------------------------------------------------------------- implicit differentiation
 def implicit_grad_x(x, y, f_hat, g_hat, grad_f, grad_g, log_a, log_b, eps, *, cost_scale=1.0, tau2=1e-5,
                     max_cg_iter=100, cg_rtol=1e-6, cg_atol=1e-6, direct_solve=False) -> Dict:

@@ -276,6 +276,45 @@ def gen_implicit():
     save("implicit_small", **out)
 
 
+def gen_c_transform():
+    """Hard c-transform (c_transform.py, kernels/c_transform_sqeuclid.py), interpreter run with manual blocks:
+    values, arg-min indices, the semi-dual objective and its Danskin gradients; plus the tie-break case of
+    the reference's test_c_transform.py:179-212 (two equidistant targets in different tiles)."""
+    from flash_sinkhorn.c_transform import c_transform_cost, c_transform_fwd
+
+    man = dict(autotune=False, block_m=32, block_n=32, block_k=16)
+    out = {}
+    for name, (n, m, d, cs) in {"a": (90, 130, 5, 1.0), "b": (150, 70, 24, 0.5)}.items():
+        gen = torch.Generator().manual_seed(71 + n)
+        x, y, psi = torch.randn(n, d, generator=gen), torch.randn(m, d, generator=gen), torch.randn(m, generator=gen)
+        wa = torch.softmax(torch.randn(n, generator=gen), 0)
+        wb = torch.softmax(torch.randn(m, generator=gen), 0)
+        c, idx = c_transform_fwd(x, y, psi, cost_scale=cs, allow_tf32=False, **man)
+        xr, pr = x.clone().requires_grad_(True), psi.clone().requires_grad_(True)
+        # c_transform_cost does not forward block sizes: wrap the kernel it calls for the run
+        import functools
+
+        import flash_sinkhorn.c_transform as ref_ct
+        orig = ref_ct.c_transform_kernel
+        ref_ct.c_transform_kernel = functools.partial(orig, block_m=32, block_n=32, block_k=16)
+        try:
+            loss = c_transform_cost(xr, y, pr, cost_scale=cs, allow_tf32=False, autotune=False, a=wa, b=wb)
+        finally:
+            ref_ct.c_transform_kernel = orig
+        gx, gpsi = torch.autograd.grad(loss, [xr, pr])
+        out.update({name + "_x": np32(x), name + "_y": np32(y), name + "_psi": np32(psi), name + "_wa": np32(wa),
+                    name + "_wb": np32(wb), name + "_cs": np.float64(cs), name + "_c": np32(c),
+                    name + "_idx": idx.numpy().astype(np.int64), name + "_loss": np.float64(loss.item()),
+                    name + "_grad_x": np32(gx), name + "_grad_psi": np32(gpsi)})
+    x = torch.zeros(1, 4)
+    y = torch.zeros(96, 4)
+    y[:, 0] = 100.0
+    y[0, 0], y[64, 0] = 1.0, -1.0
+    _, idx = c_transform_fwd(x, y, torch.zeros(96), autotune=False, block_n=32)
+    out["tie_y"], out["tie_idx"] = np32(y), idx.numpy().astype(np.int64)
+    save("c_transform_small", **out)
+
+
 def gen_dense_reference():
     """The reference's dense oracles alone (no Triton): symmetric potentials, OTT alternating, gradients."""
     n, m, d = 128, 96, 32
@@ -333,10 +372,10 @@ def gen_config1():
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--skip-c1", action="store_true", help="skip the 4096x4096 dense solves (several minutes)")
-    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,dense,c1")
+    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,dense,c1")
     args = ap.parse_args()
-    which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "implicit", "dense",
-                                                         "c1"}
+    which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "implicit",
+                                                         "ctransform", "dense", "c1"}
     print("reference version", flash_sinkhorn.__version__, "from", os.path.dirname(flash_sinkhorn.__file__))
     if "dense" in which:
         gen_dense_reference()
@@ -350,6 +389,8 @@ if __name__ == "__main__":
         gen_hvp()
     if "implicit" in which:
         gen_implicit()
+    if "ctransform" in which:
+        gen_c_transform()
     if "c1" in which and not args.skip_c1:
         gen_config1()
     sys.exit(0)

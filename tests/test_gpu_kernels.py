@@ -167,3 +167,72 @@ def test_lse_work_split_shapes(monkeypatch, n, m, ctas):
     got_tf32 = flashsinkhorn_lse(x, y, bias, eps, allow_tf32=True)
     torch.testing.assert_close(got_tf32.double(), want, rtol=5e-3, atol=5e-2)
     assert _lib.load().fs_device_error() == 0
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_c_transform_vs_reference(monkeypatch, mode, name):
+    """Hard c-transform (values, arg-min, semi-dual objective and Danskin gradients) against the reference's
+    results; the exact-product modes must reproduce every index."""
+    from flash_sinkhorn_b200 import c_transform_cost, c_transform_fwd
+    set_mode(monkeypatch, mode)
+    z = load_golden("c_transform_small")
+    x, y, psi, wa, wb = (dev(z[name + k]) for k in ("_x", "_y", "_psi", "_wa", "_wb"))
+    cs = float(z[name + "_cs"])
+    c, idx = c_transform_fwd(x, y, psi, cost_scale=cs, allow_tf32=(mode == "tf32"))
+    assert idx.dtype == torch.int64 and not c.requires_grad
+    want_c, want_idx = z[name + "_c"], z[name + "_idx"]
+    if mode == "tf32":
+        # TF32 scores may pick a different near-minimal target; its true cost must be within TF32 noise
+        full = O.c_transform(z[name + "_x"].astype(np.float64), z[name + "_y"].astype(np.float64),
+                             z[name + "_psi"].astype(np.float64), cs)[0]
+        X, Y, P = (z[name + k].astype(np.float64) for k in ("_x", "_y", "_psi"))
+        picked = cs * ((X - Y[idx.cpu().numpy()]) ** 2).sum(1) - P[idx.cpu().numpy()]
+        assert np.abs(picked - full).max() < 5e-2 and np.abs(host(c) - want_c).max() < 5e-2
+        assert (idx.cpu().numpy() == want_idx).mean() > 0.9
+        return
+    assert np.array_equal(idx.cpu().numpy(), want_idx)
+    assert np.abs(host(c) - want_c).max() < 1e-4
+    xr, pr = x.clone().requires_grad_(True), psi.clone().requires_grad_(True)
+    loss = c_transform_cost(xr, y, pr, cost_scale=cs, allow_tf32=False, a=wa, b=wb)
+    gx, gp = torch.autograd.grad(loss, [xr, pr])
+    assert abs(loss.item() - float(z[name + "_loss"])) < 1e-5 * max(1.0, abs(float(z[name + "_loss"])))
+    assert rel(host(gx), z[name + "_grad_x"]) < 1e-5 and np.abs(host(gp) - z[name + "_grad_psi"]).max() < 1e-6
+    with pytest.raises(NotImplementedError):
+        c_transform_fwd(x, y.clone().requires_grad_(True), psi)
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("n,m,d", [(1, 96, 4), (500, 300, 64), (3000, 40000, 16), (40000, 130, 8)])
+def test_c_transform_shapes_and_ties(monkeypatch, mode, n, m, d):
+    """Tie-break (smallest index among equal minima, also across tiles, column parts and CTAs) and large /
+    ragged shapes against torch on the GPU."""
+    from flash_sinkhorn_b200 import c_transform_fwd
+    set_mode(monkeypatch, mode)
+    if (n, m) == (1, 96):
+        z = load_golden("c_transform_small")
+        _, idx = c_transform_fwd(torch.zeros(1, 4).cuda(), dev(z["tie_y"]), torch.zeros(96).cuda(),
+                                 allow_tf32=(mode == "tf32"))
+        assert idx.item() == 0
+        return
+    g = torch.Generator().manual_seed(n + m)
+    x = torch.randn(n, d, generator=g).cuda()
+    y = torch.randn(m, d, generator=g).cuda()
+    y[m // 2:] = y[: m - m // 2]          # every target exists twice: ties everywhere, the first copy must win
+    psi = torch.randn(m, generator=g).cuda()
+    psi[m // 2:] = psi[: m - m // 2]
+    c, idx = c_transform_fwd(x, y, psi, allow_tf32=(mode == "tf32"))
+    assert int(idx.max()) < m - m // 2 or m % 2 == 1
+    assert int((idx >= (m + 1) // 2).sum()) == 0
+    rows = slice(0, min(n, 2000))
+    cost = ((x[rows, None, :].double() - y[None, : (m + 1) // 2, :].double()) ** 2).sum(-1) - psi[None, : (m + 1) // 2].double() \
+        if m <= 400 else None
+    if cost is not None:
+        want, widx = cost.min(dim=1)
+        tol = 5e-2 if mode == "tf32" else 1e-4
+        assert (c[rows].double() - want).abs().max() < tol
+        if mode != "tf32":
+            assert torch.equal(idx[rows], widx)
+    else:
+        picked = ((x.double() - y[idx].double()) ** 2).sum(1) - psi[idx].double()
+        assert (picked - c.double()).abs().max() < (5e-2 if mode == "tf32" else 2e-4)

@@ -196,3 +196,25 @@ def test_inverse_hvp():
     # H z reproduces the right-hand side
     back = O.hvp_x(x, y, fo, go, direct["z"], eps, direct_solve=True)["hvp"]
     assert rel_err(back, gr) < 1e-8
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_c_transform(name):
+    """Oracle vs the reference's c_transform_fwd / c_transform_cost (values, indices, Danskin gradients)."""
+    z = load_golden("c_transform_small")
+    x, y, psi, wa, wb = d64(z, name + "_x", name + "_y", name + "_psi", name + "_wa", name + "_wb")
+    cs = float(z[name + "_cs"])
+    c, idx = O.c_transform(x, y, psi, cs)
+    assert np.array_equal(idx, z[name + "_idx"])
+    assert np.abs(c - z[name + "_c"]).max() < 1e-4
+    r = O.c_transform_cost(x, y, psi, wa, wb, cs)
+    assert abs(r["loss"] - float(z[name + "_loss"])) < 1e-5 * max(1.0, abs(float(z[name + "_loss"])))
+    assert rel_err(r["grad_x"], z[name + "_grad_x"]) < 1e-5
+    assert np.abs(r["grad_psi"] - z[name + "_grad_psi"]).max() < 1e-6
+
+
+def test_c_transform_tie_break():
+    z = load_golden("c_transform_small")
+    y = z["tie_y"].astype(F64)
+    _, idx = O.c_transform(np.zeros((1, 4)), y, np.zeros(96))
+    assert int(z["tie_idx"][0]) == 0 and int(idx[0]) == 0  # equidistant targets 0 and 64: the smaller index
