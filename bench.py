@@ -162,6 +162,7 @@ def main():
     if args.kernel_only:
         from flash_sinkhorn_b200.kernels.grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid
         from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse_fused
+        from flash_sinkhorn_b200 import c_transform_fwd
         x_dev, y_dev = x_host.to(dev), y_host.to(dev)
         gh = -(y_dev**2).sum(1)
         a_w = torch.full((n,), 1.0 / n, device=dev)
@@ -171,7 +172,8 @@ def main():
         for name, fn in (("lse_pass", lambda: flashsinkhorn_lse_fused(x_dev, y_dev, gh, lb, eps, allow_tf32=not args.fp32)),
                          ("grad_x_pass", lambda: sinkhorn_geomloss_online_grad_sqeuclid(
                              x_dev, y_dev, a_w, b_w, torch.zeros(n, device=dev), gh + (y_dev**2).sum(1), eps=eps,
-                             allow_tf32=not args.fp32, compute_grad_y=False))):
+                             allow_tf32=not args.fp32, compute_grad_y=False)),
+                         ("c_transform_pass", lambda: c_transform_fwd(x_dev, y_dev, gh, allow_tf32=not args.fp32))):
             for _ in range(3):
                 fn()
             torch.cuda.synchronize()
