@@ -66,16 +66,20 @@ class _SinkhornGradFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, y, a, b, f_grad, g_grad, grad_scale, eps: float, config: _SinkhornConfig,
-                want_x: bool, want_y: bool):
+                want_x: bool, want_y: bool, label_x=None, label_y=None, label_cost_matrix=None):
         gx, gy = sinkhorn_geomloss_online_grad_sqeuclid(
             x, y, a, b, f_grad, g_grad,
             eps=float(eps), allow_tf32=config.allow_tf32, grad_scale=grad_scale,
             compute_grad_x=bool(want_x), compute_grad_y=bool(want_y), cost_scale=config.cost_scale,
+            label_x=label_x, label_y=label_y, label_cost_matrix=label_cost_matrix,
+            lambda_x=config.lambda_x, lambda_y=config.lambda_y,
             process_group=config.process_group,
         )
         ctx.save_for_backward(x, y, a, b, f_grad, g_grad, grad_scale)
         ctx.eps = float(eps)
         ctx.config = config
+        ctx.use_label_cost = (label_x is not None and label_y is not None and label_cost_matrix is not None
+                              and config.lambda_y != 0.0)
         return gx, gy
 
     @staticmethod
@@ -84,6 +88,9 @@ class _SinkhornGradFn(torch.autograd.Function):
         cfg = ctx.config
         if v_y is not None:
             raise NotImplementedError("Double backward w.r.t y is not implemented yet.")
+        if ctx.use_label_cost:
+            raise NotImplementedError("Double backward (HVP) is not supported with OTDD label-augmented cost. "
+                                      "Use gradient flow without HVP.")
         out_x = None
         if v_x is not None:
             if v_x.shape != x.shape:
@@ -103,7 +110,7 @@ class _SinkhornGradFn(torch.autograd.Function):
                     allow_tf32=False,  # second-order products need fp32-exact scores
                 )
                 out_x = hv * grad_scale
-        return (out_x,) + (None,) * 10
+        return (out_x,) + (None,) * 13
 
 
 class _SinkhornCostFn(torch.autograd.Function):
@@ -114,8 +121,8 @@ class _SinkhornCostFn(torch.autograd.Function):
                 label_x, label_y, label_cost_matrix, presolved=None):
         # `presolved` (extension): (f_cost, g_cost, f_grad, g_grad) from a solve done elsewhere - the multi-GPU
         # divergence solves its three problems interleaved before building the three cost nodes.
-        if label_cost_matrix is not None and label_x is not None and label_y is not None and config.lambda_y != 0.0:
-            raise NotImplementedError("The OTDD label-augmented cost is not implemented in flash_sinkhorn_b200.")
+        label_kw = dict(label_x=label_x, label_y=label_y, label_cost_matrix=label_cost_matrix,
+                        lambda_x=config.lambda_x, lambda_y=config.lambda_y)
         if presolved is not None:
             eps = float(eps_list[-1])
             f_cost, g_cost, f_grad, g_grad = presolved
@@ -139,15 +146,17 @@ class _SinkhornCostFn(torch.autograd.Function):
             )
             if config.last_extrapolation:
                 f_cost, g_cost, f_grad, g_grad = sinkhorn_flashstyle_symmetric(
-                    x, y, a, b, last_extrapolation=True, return_prelast=True, **common)
+                    x, y, a, b, last_extrapolation=True, return_prelast=True, **common, **label_kw)
             else:
-                f_cost, g_cost = sinkhorn_flashstyle_symmetric(x, y, a, b, last_extrapolation=False, **common)
+                f_cost, g_cost = sinkhorn_flashstyle_symmetric(x, y, a, b, last_extrapolation=False, **common,
+                                                               **label_kw)
                 f_grad, g_grad = f_cost, g_cost
             plain_dual = config.rho_x is None or config.rho_y is None  # balanced or semi-unbalanced
 
         ctx.save_for_backward(x, y, a, b, f_cost, g_cost, f_grad, g_grad)
         ctx.eps = eps
         ctx.config = config
+        ctx.labels = (label_x, label_y, label_cost_matrix)
 
         if plain_dual:
             return (a * f_cost).sum() + (b * g_cost).sum()
@@ -163,7 +172,8 @@ class _SinkhornCostFn(torch.autograd.Function):
         gx = gy = ga = gb = None
         if x.requires_grad or y.requires_grad:
             gx, gy = _SinkhornGradFn.apply(
-                x, y, a, b, f_grad, g_grad, grad_out, ctx.eps, ctx.config, x.requires_grad, y.requires_grad)
+                x, y, a, b, f_grad, g_grad, grad_out, ctx.eps, ctx.config, x.requires_grad, y.requires_grad,
+                *ctx.labels)
             if not x.requires_grad:
                 gx = None
             if not y.requires_grad:

@@ -55,7 +55,7 @@ SIGNATURES = {
     "fs_symmetric_step": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
-         c_float, c_float, c_float, c_float, c_float, c_int, _P, c_size_t, _P],
+         c_float, c_float, c_float, c_float, c_float, c_int, _P, c_size_t, _P, _P],
     ),
     "fs_symmetric_step_range": (
         c_int,
@@ -70,7 +70,7 @@ SIGNATURES = {
     "fs_solve_symmetric": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_float, c_double, c_double,
-         c_double, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_size_t, _P],
+         c_double, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_size_t, _P, _P],
     ),
     "fs_solve_alternating": (
         c_int,
@@ -93,7 +93,7 @@ SIGNATURES = {
     "fs_grad": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float,
-         c_int, _P, c_size_t, _P],
+         c_int, _P, c_size_t, _P, _P],
     ),
     "fs_mat5": (
         c_int,
@@ -184,6 +184,54 @@ def require_cuda(**tensors: Optional[torch.Tensor]) -> torch.device:
 def workspace(op: int, n: int, m: int, d: int, prec: int, device: torch.device) -> torch.Tensor:
     nbytes = int(load().fs_workspace_bytes(op, n, m, d, prec))
     return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+
+
+class LabelCostStruct(ctypes.Structure):
+    """``fs_label_cost`` of the C header."""
+
+    _fields_ = [("label_x", c_void_p), ("label_y", c_void_p), ("W", c_void_p), ("V", c_int),
+                ("lambda_x", c_float), ("lambda_y", c_float)]
+
+
+class LabelCost:
+    """Validated label-cost arguments (reference kernels/sinkhorn_flashstyle_sqeuclid.py:1183-1213): int32
+    labels on the device of x, a square fp32 table, and the ctypes descriptor that points at them.
+    ``LabelCost.make`` returns None when the label cost is inactive (any of the four inputs missing, or
+    ``lambda_y == 0``), exactly the reference's ``use_label_cost`` condition."""
+
+    def __init__(self, label_x, label_y, table, lambda_x, lambda_y):
+        self.label_x, self.label_y, self.table = label_x, label_y, table
+        self.V = int(table.shape[0])
+        self.struct = LabelCostStruct(label_x.data_ptr(), label_y.data_ptr(), table.data_ptr(), self.V,
+                                      float(lambda_x), float(lambda_y))
+
+    @property
+    def ref(self):
+        return ctypes.cast(ctypes.pointer(self.struct), c_void_p)
+
+    @staticmethod
+    def make(label_x, label_y, label_cost_matrix, lambda_x, lambda_y, n, m, device):
+        if label_x is None or label_y is None or label_cost_matrix is None or float(lambda_y) == 0.0:
+            return None
+        if label_x.shape[0] != n:
+            raise ValueError(f"label_x must have length n={n}, got {label_x.shape[0]}")
+        if label_y.shape[0] != m:
+            raise ValueError(f"label_y must have length m={m}, got {label_y.shape[0]}")
+        if label_cost_matrix.ndim != 2:
+            raise ValueError("label_cost_matrix must be 2D (V, V)")
+        if label_cost_matrix.shape[0] != label_cost_matrix.shape[1]:
+            raise ValueError("label_cost_matrix must be square (V, V)")
+        V = label_cost_matrix.shape[0]
+        for name, lab in (("label_x", label_x), ("label_y", label_y)):
+            lo, hi = int(lab.min()), int(lab.max())
+            if hi >= V or lo < 0:
+                raise ValueError(f"{name} values must be in [0, {V}), got range [{lo}, {hi}]")
+        if not float(lambda_x) > 0.0:
+            raise ValueError("lambda_x must be > 0 when a label cost is used")
+        return LabelCost(label_x.to(dtype=torch.int32, device=device).contiguous(),
+                         label_y.to(dtype=torch.int32, device=device).contiguous(),
+                         label_cost_matrix.to(dtype=torch.float32, device=device).contiguous(),
+                         lambda_x, lambda_y)
 
 
 def stream_ptr(device: torch.device) -> int:

@@ -160,6 +160,8 @@ struct Problem {
   const int* csr_ci[2] = {nullptr, nullptr};
   tc::Staged staged;  // tcgen05 operands (valid when use_tc)
   bool use_tc = false;
+  LabelCost lab;      // V == 0: plain squared-Euclidean cost
+  int d_tc = 0;       // feature count the tensor-core engine plans with (d + 3V: the label table rides in the contraction)
 
   StreamArgs stream_args(int side, const float* pot, const float* logw, float eps) const {
     StreamArgs s;
@@ -174,6 +176,12 @@ struct Problem {
     s.cost_scale = cs;
     s.tile_row_ptr = csr_rp[side];
     s.tile_col_idx = csr_ci[side];
+    if (lab.V > 0) {
+      s.lab_rows = lab.lab[side == 0 ? 0 : 1];
+      s.lab_cols = lab.lab[side == 0 ? 1 : 0];
+      s.W = lab.W; s.V = lab.V; s.lam_w = lab.lam_w;
+      s.w_row_major = side == 0 ? 1 : 0;
+    }
     s.row_begin = row_lo[side];
     if (row_hi[side] >= 0 && row_hi[side] < s.nr) s.nr = row_hi[side];
     return s;
@@ -210,14 +218,14 @@ struct Problem {
     return simt_vec(s, v, st);
   }
   bool vec_on_tc() const {
-    return use_tc && pv_scratch && !csr_rp[0] && tc::pv_supported(d, prec, 1) &&
-           tc::pv_scratch_bytes(n > m ? n : m, d, prec, 1) <= pv_scratch_bytes;
+    return use_tc && pv_scratch && !csr_rp[0] && tc::pv_supported(d_tc, prec, 1) &&
+           tc::pv_scratch_bytes(n > m ? n : m, d_tc, prec, 1) <= pv_scratch_bytes;
   }
   cudaError_t pv(int side, const float* pot, const float* logw, float eps, const PvArgs& p) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (use_tc && !p.rows2 && !s.tile_row_ptr && pv_scratch && tc::pv_supported(d, prec, p.dv) &&
-        tc::pv_scratch_bytes(s.nc, d, prec, p.dv) <= pv_scratch_bytes)
+    if (use_tc && !p.rows2 && !s.tile_row_ptr && pv_scratch && tc::pv_supported(d_tc, prec, p.dv) &&
+        tc::pv_scratch_bytes(s.nc, d_tc, prec, p.dv) <= pv_scratch_bytes)
       return tc::pv(staged, side, s, p, pv_scratch, st);
     return simt_pv(s, p, st);
   }
@@ -245,19 +253,24 @@ int check_device() {
 // Sets up `p` (engine choice + staged tcgen05 operands carved from ws).
 // `lse_only` is true for ops that only run LSE passes.
 int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int m, int d, float cs, int prec,
-                 cudaStream_t st, bool measure_only, int pv_dv = 0, bool run_staging = true) {
+                 cudaStream_t st, bool measure_only, int pv_dv = 0, bool run_staging = true,
+                 const LabelCost* lab = nullptr) {
   p.x = x; p.y = y; p.n = n; p.m = m; p.d = d; p.cs = cs; p.prec = prec; p.st = st;
-  p.use_tc = (prec != FS_PREC_SIMT) && tc::supported(n, m, d, prec);
+  if (lab && lab->V > 0) p.lab = *lab;
+  p.d_tc = d + 3 * p.lab.V;
+  p.use_tc = (prec != FS_PREC_SIMT) && tc::supported(n, m, p.d_tc, prec);
   if (p.use_tc) {
-    size_t bytes = tc::staged_bytes(n, m, d, prec);
+    size_t bytes = tc::staged_bytes(n, m, p.d_tc, prec);
     char* buf = ws.take<char>(bytes);
     if (!measure_only) {
       if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
-      cudaError_t e = tc::stage(p.staged, buf, x, y, n, m, d, prec, st, run_staging);
+      // staged label entries: logit = scale2 * S with scale2 = 2cs/eps*log2e, so S gets -lam_w*W/(2cs)
+      cudaError_t e = tc::stage(p.staged, buf, x, y, n, m, d, prec, st, run_staging, p.lab.V ? &p.lab : nullptr,
+                                -p.lab.lam_w / (2.0f * cs));
       if (e != cudaSuccess) return fail(FS_ERR_CUDA, "staging tcgen05 operands failed: %s", cudaGetErrorString(e));
     }
-    if (pv_dv > 0 && tc::pv_supported(d, prec, pv_dv)) {
-      p.pv_scratch_bytes = tc::pv_scratch_bytes(n > m ? n : m, d, prec, pv_dv);
+    if (pv_dv > 0 && tc::pv_supported(p.d_tc, prec, pv_dv)) {
+      p.pv_scratch_bytes = tc::pv_scratch_bytes(n > m ? n : m, p.d_tc, prec, pv_dv);
       p.pv_scratch = ws.take<char>(p.pv_scratch_bytes);
       if (!measure_only && ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
     }
@@ -279,6 +292,19 @@ void carve_solve(Ws& ws, SolveBufs& b, int n, int m) {
   b.pg = ws.take<float>(m);
   b.zeros_n = ws.take<float>(n);
   b.zeros_m = ws.take<float>(m);
+}
+
+// C-ABI label-cost descriptor -> engine form. Returns false on an inconsistent descriptor.
+// Kernels then run with cost scale cs*lambda_x on the dot term and subtract lambda_y*cs*W/eps from the logit
+// (reference kernels/sinkhorn_flashstyle_sqeuclid.py:545-560).
+inline bool label_cost_from_abi(const fs_label_cost* in, float cost_scale, LabelCost& out, float& cs_kernel) {
+  cs_kernel = cost_scale;
+  if (!in || in->V <= 0 || in->lambda_y == 0.f) return true;
+  if (!in->label_x || !in->label_y || !in->W || !(in->lambda_x > 0.f)) return false;
+  out.lab[0] = in->label_x; out.lab[1] = in->label_y; out.W = in->W; out.V = in->V;
+  out.lam_w = in->lambda_y * cost_scale;
+  cs_kernel = cost_scale * in->lambda_x;
+  return true;
 }
 
 inline double dampening(double eps, double rho) {
@@ -395,7 +421,7 @@ int fs_c_transform(const float* x, const float* y, int n, int m, int d, const fl
 int fs_symmetric_step(const float* x, const float* y, int n, int m, int d, const float* f_hat, const float* g_hat,
                       const float* log_a, const float* log_b, float* f_out, float* g_out, const float* alpha_x,
                       const float* beta_y, float eps, float w, float damp_f, float damp_g, float cost_scale,
-                      int prec, void* wsp, size_t ws_bytes, void* stream) {
+                      int prec, void* wsp, size_t ws_bytes, void* stream, const fs_label_cost* labels) {
   FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
   if (!f_hat || !g_hat || !log_a || !log_b || !f_out || !g_out)
     return fail(FS_ERR_BAD_ARG, "potentials, log-weights and outputs must be non-null");
@@ -404,7 +430,10 @@ int fs_symmetric_step(const float* x, const float* y, int n, int m, int d, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  LabelCost lc;
+  float cs_kernel;
+  if (!label_cost_from_abi(labels, cost_scale, lc, cs_kernel)) return fail(FS_ERR_BAD_ARG, "invalid label cost descriptor");
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cs_kernel, prec, st, false, 0, true, &lc));
   LseEpilogue ef;
   ef.damping = damp_f; ef.old = f_hat; ef.w = w; ef.out = f_out;
   if (alpha_x && damp_f < 1.f) { ef.shift = alpha_x; ef.shiftcoef = w * (1.f - damp_f); }
@@ -420,7 +449,7 @@ int fs_solve_symmetric(const float* x, const float* y, int n, int m, int d, cons
                        const double* eps_list, int n_eps, int last_extrapolation, float cost_scale, double rho_x,
                        double rho_y, double threshold, int check_every, const float* f_init, const float* g_init,
                        float* f, float* g, float* f_pre, float* g_pre, int* iters_used, int prec, void* wsp,
-                       size_t ws_bytes, void* stream) {
+                       size_t ws_bytes, void* stream, const fs_label_cost* labels) {
   if (!eps_list || n_eps <= 0) return fail(FS_ERR_BAD_ARG, "eps_list must be non-empty");
   FS_TRY(check_common(x, y, n, m, d, (float)eps_list[0], cost_scale, prec));
   for (int i = 0; i < n_eps; ++i)
@@ -432,7 +461,11 @@ int fs_solve_symmetric(const float* x, const float* y, int n, int m, int d, cons
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  LabelCost lc;
+  float cs_kernel;
+  if (!label_cost_from_abi(labels, cost_scale, lc, cs_kernel)) return fail(FS_ERR_BAD_ARG, "invalid label cost descriptor");
+  // lambda_x scales the dot term only; the shifts alpha, beta below keep the plain cost scale (as the reference does)
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cs_kernel, prec, st, false, 0, true, &lc));
   SolveBufs b;
   carve_solve(ws, b, n, m);
   if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
@@ -448,7 +481,8 @@ int fs_solve_symmetric(const float* x, const float* y, int n, int m, int d, cons
   // Self-transport problem (the debiasing terms OT(a,a), OT(b,b)): same cloud, weights, penalties and
   // initial potentials on both sides. Both Jacobi updates then read identical inputs through the same
   // kernel, so g equals f bit for bit after every step: run one soft-min per step and copy its result.
-  const bool self_problem = x == y && n == m && log_a == log_b && f_init == g_init && rho_x == rho_y;
+  const bool self_problem = x == y && n == m && log_a == log_b && f_init == g_init && rho_x == rho_y &&
+                            lc.V == 0;  // a label table need not be symmetric: keep both sides then
 
   int cur = 0;
   auto step = [&](double eps, float w, bool in_loop) -> int {
@@ -642,14 +676,21 @@ int fs_apply_mat(const float* x, const float* y, int n, int m, int d, const floa
 int fs_grad(const float* x, const float* y, int n, int m, int d, const float* a, const float* b,
             const float* log_a, const float* log_b, const float* f, const float* g, const float* grad_scale,
             float* grad_x, float* grad_y, float eps, float cost_scale, int prec, void* wsp, size_t ws_bytes,
-            void* stream) {
+            void* stream, const fs_label_cost* labels) {
   FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
   if (!a || !b || !log_a || !log_b || !f || !g) return fail(FS_ERR_BAD_ARG, "null argument");
   FS_TRY(check_device());
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, d));
+  LabelCost lc;
+  {
+    // The gradient kernels of the reference scale the WHOLE squared distance by lambda_x
+    // (kernels/sinkhorn_triton_grad_sqeuclid.py:236, :275): from here on cost_scale means cs*lambda_x.
+    const float cs_plain = cost_scale;
+    if (!label_cost_from_abi(labels, cs_plain, lc, cost_scale)) return fail(FS_ERR_BAD_ARG, "invalid label cost descriptor");
+  }
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, d, true, &lc));
   // The normaliser R and the weights must come from the same engine (bit-identical scores).
   if (p.use_tc && !p.pv_scratch) p.use_tc = false;
   float* fh = ws.take<float>(n);

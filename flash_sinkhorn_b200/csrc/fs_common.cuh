@@ -36,6 +36,25 @@ struct StreamArgs {
   // Block-sparse tile list over 128x128 (row-tile, col-tile) pairs, CSR by row tile; nullptr = dense.
   const int* tile_row_ptr = nullptr;
   const int* tile_col_idx = nullptr;
+  // Label cost (V > 0): t_ij -= lam_w/eps*log2e * W[a, b] with (a, b) = (label of the x point, label of the
+  // y point); w_row_major says whether the ROWS of this pass are the x cloud (index = lab_rows*V + lab_cols)
+  // or the y cloud (index = lab_cols*V + lab_rows). The tensor-core engine folds the same term into the
+  // contraction when the operands are staged and ignores these fields.
+  const int* lab_rows = nullptr;
+  const int* lab_cols = nullptr;
+  const float* W = nullptr;
+  int V = 0;
+  int w_row_major = 1;
+  float lam_w = 0.f;
+};
+
+// Label-augmented ground cost C_ij = cs*lambda_x*|x_i-y_j|^2-like dot term + lam_w * W[label_x_i, label_y_j]
+// (reference kernels/sinkhorn_flashstyle_sqeuclid.py:545-560): device labels of both clouds and the V x V table.
+struct LabelCost {
+  const int* lab[2] = {nullptr, nullptr};  // labels of cloud 0 (x) and cloud 1 (y)
+  const float* W = nullptr;                // [V, V] row-major, W[label_x, label_y]
+  int V = 0;                               // 0 = no label cost
+  float lam_w = 0.f;                       // lambda_y * cost_scale
 };
 
 // LSE pass epilogue:

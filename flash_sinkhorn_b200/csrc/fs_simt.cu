@@ -61,6 +61,11 @@ __device__ __forceinline__ float col_bias2(const StreamArgs& s, int col, float i
   return __ldg(s.pot + col) * kLog2e;
 }
 
+// Label-cost term of entry (row label lr, column label lc), in log2 units (0 without label cost).
+__device__ __forceinline__ float label_term2(const StreamArgs& s, int lr, int lc, float lw2) {
+  return lw2 * __ldg(s.W + (s.w_row_major ? lr * s.V + lc : lc * s.V + lr));
+}
+
 // Column-tile iteration (dense, or CSR over 128-wide tiles => two 64-wide tiles each).
 struct TileIter {
   int pos, end, sub, ntiles;
@@ -99,6 +104,7 @@ __global__ void __launch_bounds__(NT) simt_stream_kernel(StreamArgs s, LseEpilog
   __shared__ __align__(16) float Bs[TK][LDS_T];
   __shared__ float bias_s[TN];
   __shared__ float vec_s[TN];
+  __shared__ int lab_s[TN];
 
   const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
   const int row0 = s.row_begin + blockIdx.x * TM;
@@ -117,6 +123,15 @@ __global__ void __launch_bounds__(NT) simt_stream_kernel(StreamArgs s, LseEpilog
   float m[4], acc1[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) { m[i] = -INFINITY; acc1[i] = 0.f; }
+  const float lw2 = s.lam_w * inv_eps_log2;
+  int lr[4] = {0, 0, 0, 0};
+  if (s.V) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = row0 + ty * 4 + i;
+      lr[i] = (r < s.nr) ? __ldg(s.lab_rows + r) : 0;
+    }
+  }
 
   TileIter it(s, row0);
   for (int ct = it.next(); ct >= 0; ct = it.next()) {
@@ -131,6 +146,7 @@ __global__ void __launch_bounds__(NT) simt_stream_kernel(StreamArgs s, LseEpilog
       int c = col0 + tid;
       bias_s[tid] = (c < s.nc) ? col_bias2(s, c, inv_eps_log2) : -INFINITY;
       if (MODE == MODE_VEC) vec_s[tid] = (c < s.nc) ? __ldg(va.v + c) : 0.f;
+      if (s.V) lab_s[tid] = (c < s.nc) ? __ldg(s.lab_cols + c) : 0;
     }
     for (int k0 = 0; k0 < s.d; k0 += TK) {
       __syncthreads();
@@ -154,6 +170,7 @@ __global__ void __launch_bounds__(NT) simt_stream_kernel(StreamArgs s, LseEpilog
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         t[j] = fmaf(acc[i][j], scale2, bj[j]);  // -inf bias masks padded columns
+        if (s.V) t[j] -= label_term2(s, lr[i], lab_s[tx * 4 + j], lw2);
         tmax = fmaxf(tmax, t[j]);
       }
       float mn = fmaxf(m[i], tmax);
@@ -216,6 +233,7 @@ __global__ void __launch_bounds__(NT) simt_pv_kernel(StreamArgs s, PvArgs p) {
   __shared__ __align__(16) float Vs[TN][64];
   __shared__ float bias_s[TN];
   __shared__ float cs_s[TN];
+  __shared__ int lab_s[TN];
 
   const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
   const int row0 = s.row_begin + blockIdx.x * TM;
@@ -226,10 +244,13 @@ __global__ void __launch_bounds__(NT) simt_pv_kernel(StreamArgs s, PvArgs p) {
   const float scale2 = (2.0f * s.cost_scale) * inv_eps * kLog2e;
 
   float Rr[4];
+  int lr[4] = {0, 0, 0, 0};
+  const float lw2 = s.lam_w * inv_eps_log2;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     int r = row0 + ty * 4 + i;
     Rr[i] = (r < s.nr) ? __ldg(p.R + r) : 0.f;
+    if (s.V) lr[i] = (r < s.nr) ? __ldg(s.lab_rows + r) : 0;
   }
   float O[4][4];
 #pragma unroll
@@ -250,6 +271,7 @@ __global__ void __launch_bounds__(NT) simt_pv_kernel(StreamArgs s, PvArgs p) {
       int c = col0 + tid;
       bias_s[tid] = (c < s.nc) ? col_bias2(s, c, inv_eps_log2) : -INFINITY;
       cs_s[tid] = (c < s.nc && p.colscale) ? __ldg(p.colscale + c) : 1.f;
+      if (s.V) lab_s[tid] = (c < s.nc) ? __ldg(s.lab_cols + c) : 0;
     }
     for (int k0 = 0; k0 < s.d; k0 += TK) {
       __syncthreads();
@@ -274,7 +296,9 @@ __global__ void __launch_bounds__(NT) simt_pv_kernel(StreamArgs s, PvArgs p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         int cj = tx * 4 + j;
-        float w = ex2(fmaf(acc[i][j], scale2, bias_s[cj]) - Rr[i]);  // padded columns: 2^-inf = 0
+        float tij = fmaf(acc[i][j], scale2, bias_s[cj]);
+        if (s.V) tij -= label_term2(s, lr[i], lab_s[cj], lw2);
+        float w = ex2(tij - Rr[i]);  // padded columns: 2^-inf = 0
         if (DOT2) w *= acc2[i][j];
         w *= cs_s[cj];
         Ws[ty * 4 + i][cj] = w;

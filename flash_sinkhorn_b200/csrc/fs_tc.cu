@@ -1072,8 +1072,14 @@ __global__ void stage_vt_kernel(const float* __restrict__ V, int nc, int dv, con
 //   TF32 mode : [ x (d) | aug (3) | 0 ... ]                       A-role aug = 1,1,1 ; B-role aug = bias split
 //   FP32 mode : A-role [ xh (d) | xh (d) | xl (d) | aug | 0 ...]   B-role [ yh | yl | yh | aug | 0 ... ]
 // so that sum_k A_k B_k = xh.yh + xh.yl + xl.yh + bias  (the dropped xl.yl term is ~2^-22 relative).
+// Label cost: the d_real coordinates are followed by 3V "virtual features" per point, so that the table
+// lookup becomes part of the same contraction: in the row role a point of label l carries (1,1,1) in the
+// three features of class l and zeros elsewhere; in the column role it carries, for every class v, the
+// three-piece TF32 split of w_coef * W[.,.] between v and its own label (exact in fp32). d = d_real + 3V.
 __global__ void stage_kernel(const float* __restrict__ src, int rows, int rows_pad, int d, int kc, int kp, int prec,
-                             float* __restrict__ opA, float* __restrict__ opB) {
+                             float* __restrict__ opA, float* __restrict__ opB, int d_real,
+                             const int* __restrict__ labels, const float* __restrict__ W, int V, int cloud,
+                             float w_coef) {
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t total = (size_t)rows_pad * kp;
   if (idx >= total) return;
@@ -1082,11 +1088,22 @@ __global__ void stage_kernel(const float* __restrict__ src, int rows, int rows_p
   if (k < kc) {
     if (r < rows) {
       int part = k / d, c = k % d;
-      float x = src[(size_t)r * d + c];
-      float hi = to_tf32(x);
-      float lo = to_tf32(x - hi);
-      if (prec == 0) { va = hi; vb = hi; }
-      else { va = (part == 2) ? lo : hi; vb = (part == 1) ? lo : hi; }
+      float xa, xb;  // value of this feature in the row role / in the column role
+      if (c < d_real) {
+        xa = xb = src[(size_t)r * d_real + c];
+      } else {
+        const int v = (c - d_real) / 3, piece = (c - d_real) % 3;
+        const int l = labels[r];
+        xa = (l == v) ? 1.f : 0.f;
+        // cloud 0 (x) as column: rows are y points of label v -> W[l, v]; cloud 1 (y) as column: W[v, l]
+        const float w = w_coef * W[cloud == 0 ? l * V + v : v * V + l];
+        const float h = to_tf32(w), mid = to_tf32(w - h), low = to_tf32(w - h - mid);
+        xb = piece == 0 ? h : (piece == 1 ? mid : low);
+      }
+      float ha = to_tf32(xa), la = to_tf32(xa - ha);
+      float hb = to_tf32(xb), lb = to_tf32(xb - hb);
+      if (prec == 0) { va = ha; vb = hb; }
+      else { va = (part == 2) ? la : ha; vb = (part == 1) ? lb : hb; }
     }
   } else if (k < kc + 3) {
     va = 1.f;
@@ -1240,7 +1257,10 @@ size_t staged_bytes(int n, int m, int d, int prec) {
 }
 
 cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
-                  cudaStream_t st, bool run_kernels) {
+                  cudaStream_t st, bool run_kernels, const LabelCost* lab, float w_coef) {
+  const int V = (lab && lab->V > 0) ? lab->V : 0;
+  const int d_real = d;
+  d = d_real + 3 * V;  // the engine sees the label table as 3V extra features (see stage_kernel)
   Shape sh = plan_shape(d, prec);
   if (!sh.ok) return cudaErrorNotSupported;
   s.d = d; s.kc = sh.kc; s.kp = sh.kp; s.prec = prec;
@@ -1257,7 +1277,8 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
     size_t total = (size_t)o.rows_pad * sh.kp;
     if (run_kernels)
       stage_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src[c], o.rows, o.rows_pad, d, sh.kc, sh.kp, prec,
-                                                                    o.opA, o.opB);
+                                                                    o.opA, o.opB, d_real, V ? lab->lab[c] : nullptr,
+                                                                    V ? lab->W : nullptr, V, c, w_coef);
   }
   s.part_stride = pad256(n > m ? n : m);
   s.part_m = reinterpret_cast<float*>(p);

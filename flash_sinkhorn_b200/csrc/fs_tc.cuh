@@ -31,8 +31,10 @@ bool supported(int n, int m, int d, int prec);
 size_t staged_bytes(int n, int m, int d, int prec);
 // run_kernels = false only lays out the pointers inside `buf` (operands staged there by an earlier call
 // with the same sizes are re-used: row-sharded solvers stage once and step many times).
+// With a label cost (lab->V > 0) the operands get 3V extra columns that carry w_coef * W[label, label']
+// through the contraction; every size query for such a problem must then use d + 3V as the feature count.
 cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
-                  cudaStream_t st, bool run_kernels = true);
+                  cudaStream_t st, bool run_kernels = true, const LabelCost* lab = nullptr, float w_coef = 0.f);
 // One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st);
 

@@ -65,11 +65,12 @@ def sinkhorn_geomloss_online_grad_sqeuclid(
         raise ValueError("b and g shapes must match y.")
     if x.dtype not in (torch.float16, torch.bfloat16, torch.float32):
         raise ValueError(f"Unsupported dtype for x/y: {x.dtype}")
-    if label_x is not None and label_y is not None and label_cost_matrix is not None and lambda_y != 0.0:
-        raise NotImplementedError("The OTDD label-augmented cost is not implemented in flash_sinkhorn_b200.")
     if not compute_grad_x and not compute_grad_y:
         return None, None
     dev = _lib.require_cuda(x=x, y=y, a=a, b=b, f=f, g=g)
+    # Label-augmented cost lambda_x*cs|x-y|^2 + lambda_y*cs*W[label, label'] inside the weights
+    # (reference :225-236); the barycentric formula itself only gains the factor lambda_x (:275).
+    labels = _lib.LabelCost.make(label_x, label_y, label_cost_matrix, lambda_x, lambda_y, n, m, dev)
     x32, y32, a32, b32, f32, g32 = map(_lib.f32c, (x, y, a, b, f, g))
     la, lb = log_weights(a32).contiguous(), log_weights(b32).contiguous()
     gs = None
@@ -80,18 +81,21 @@ def sinkhorn_geomloss_online_grad_sqeuclid(
             raise ValueError("grad_scale must be on the same device as x.")
         gs = _lib.f32c(grad_scale.detach().reshape(1))
     prec = _lib.precision_id(allow_tf32)
+    if labels is not None and process_group is not None:
+        raise NotImplementedError("The label cost is not available in the multi-GPU sharded gradient.")
     if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
         from flash_sinkhorn_b200.distributed import grad_sharded  # rows sharded over the ranks, then all-gathered
         return grad_sharded(x32, y32, a32, b32, la, lb, f32, g32, gs, float(eps), float(cost_scale), prec,
                             bool(compute_grad_x), bool(compute_grad_y), process_group)
     gx = torch.empty((n, d), device=dev, dtype=torch.float32) if compute_grad_x else None
     gy = torch.empty((m, d), device=dev, dtype=torch.float32) if compute_grad_y else None
-    ws = _lib.workspace(_lib.OP_GRAD, n, m, d, prec, dev)
+    ws = _lib.workspace(_lib.OP_GRAD, n, m, d + (3 * labels.V if labels else 0), prec, dev)
     _lib.call(
         "fs_grad", dev,
         _lib.ptr(x32), _lib.ptr(y32), n, m, d,
         _lib.ptr(a32), _lib.ptr(b32), _lib.ptr(la), _lib.ptr(lb), _lib.ptr(f32), _lib.ptr(g32),
         _lib.ptr(gs), _lib.ptr(gx), _lib.ptr(gy),
         float(eps), float(cost_scale), prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+        labels.ref if labels else None,
     )
     return gx, gy

@@ -159,24 +159,23 @@ def flashsinkhorn_symmetric_step(
     Both candidates are computed from the old potentials. The unbalanced shift
     correction is NOT applied here (as in the reference, the solver does it).
     """
-    if label_x is not None and label_y is not None and label_cost_matrix is not None and lambda_y != 0.0:
-        raise NotImplementedError("The OTDD label-augmented cost is not implemented in flash_sinkhorn_b200.")
     n, d = x.shape
     m = y.shape[0]
     dev = _lib.require_cuda(x=x, y=y, f_hat=f_hat, g_hat=g_hat, log_a=log_a, log_b=log_b)
+    labels = _lib.LabelCost.make(label_x, label_y, label_cost_matrix, lambda_x, lambda_y, n, m, dev)
     x32, y32 = _lib.f32c(x), _lib.f32c(y)
     f32, g32, la32, lb32 = _lib.f32c(f_hat), _lib.f32c(g_hat), _lib.f32c(log_a), _lib.f32c(log_b)
     prec = _lib.precision_id(allow_tf32)
     f_out = torch.empty((n,), device=dev, dtype=torch.float32)
     g_out = torch.empty((m,), device=dev, dtype=torch.float32)
-    ws = _lib.workspace(_lib.OP_STEP, n, m, d, prec, dev)
+    ws = _lib.workspace(_lib.OP_STEP, n, m, d + (3 * labels.V if labels else 0), prec, dev)
     _lib.call(
         "fs_symmetric_step", dev,
         _lib.ptr(x32), _lib.ptr(y32), n, m, d,
         _lib.ptr(f32), _lib.ptr(g32), _lib.ptr(la32), _lib.ptr(lb32),
         _lib.ptr(f_out), _lib.ptr(g_out), None, None,
         float(eps), float(alpha), float(damping_f), float(damping_g), float(cost_scale),
-        prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+        prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev), labels.ref if labels else None,
     )
     return f_out, g_out
 

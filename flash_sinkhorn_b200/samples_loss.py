@@ -4,8 +4,10 @@ Drop-in for the reference's ``samples_loss.py`` (argument parsing :73-191, const
 :260-414, eps schedule :451-470, forward :472-597): same constructor keywords and
 defaults, the two call forms ``loss(x, y)`` / ``loss(a, x, b, y)``, ``(N, D)`` or batched
 ``(B, N, D)`` clouds, the same ValueError / TypeError / DeprecationWarning behaviour.
-Triton tuning keywords are stored and ignored. The OTDD label cost raises
-``NotImplementedError``.
+Triton tuning keywords are stored and ignored. The OTDD label-augmented cost
+(``label_cost_matrix``, ``lambda_x``, ``lambda_y``; labels given to ``forward``) is supported on the
+symmetric backend for forward and gradient; its double backward raises ``NotImplementedError`` as in
+the reference.
 """
 from __future__ import annotations
 
@@ -306,6 +308,8 @@ class SamplesLoss(torch.nn.Module):
             terms = [(xs, ys, ws_a, ws_b, label_x, label_y), (xs, xs, ws_a, ws_a, label_x, label_x),
                      (ys, ys, ws_b, ws_b, label_y, label_y)]
             pre = [None, None, None]
+            if multi_gpu and self.label_cost_matrix is not None and label_x is not None and self.lambda_y != 0.0:
+                raise NotImplementedError("The label cost is not available in the multi-GPU sharded solver.")
             if multi_gpu:
                 # The three solves are independent: run them interleaved so that the all-gather of one
                 # overlaps the compute of the next, then hand the potentials to the cost nodes.

@@ -199,10 +199,15 @@ def sinkhorn_flashstyle_symmetric(
     last step, and with ``return_n_iters`` the number of steps taken. ``fused`` is accepted
     and ignored (one implementation serves both of the reference's paths).
     """
-    if label_x is not None and label_y is not None and label_cost_matrix is not None and lambda_y != 0.0:
-        raise NotImplementedError("The OTDD label-augmented cost is not implemented in flash_sinkhorn_b200.")
     n, d = x.shape
     m = y.shape[0]
+    # OTDD label-augmented cost (reference sinkhorn_solvers.py:323-328, :557-560): the table lookup rides in
+    # the tensor-core contraction as 3V extra operand columns, so no kernel differs from the plain solve.
+    labels = _lib.LabelCost.make(label_x, label_y, label_cost_matrix, lambda_x, lambda_y, n, m, x.device)
+    if labels is not None and fused is False:
+        raise ValueError("OTDD label cost requires fused=True (default). Set fused=True or omit label_cost_matrix.")
+    if labels is not None and process_group is not None:
+        raise NotImplementedError("The label cost is not available in the multi-GPU sharded solver.")
     rho_x, rho_y = resolve_marginal_penalties(rho, reach, rho_x, rho_y, reach_x, reach_y)
 
     if eps_list is None:
@@ -255,7 +260,7 @@ def sinkhorn_flashstyle_symmetric(
     f_pre = torch.empty((n,), device=dev, dtype=torch.float32) if want_pre else None
     g_pre = torch.empty((m,), device=dev, dtype=torch.float32) if want_pre else None
     iters = torch.zeros((1,), device=dev, dtype=torch.int32) if return_n_iters else None
-    ws = _lib.workspace(_lib.OP_SOLVE_SYMMETRIC, n, m, d, prec, dev)
+    ws = _lib.workspace(_lib.OP_SOLVE_SYMMETRIC, n, m, d + (3 * labels.V if labels else 0), prec, dev)
     eps_arr = _eps_array(eps_list)
     _lib.call(
         "fs_solve_symmetric", dev,
@@ -265,7 +270,7 @@ def sinkhorn_flashstyle_symmetric(
         _neg_if_none(threshold), int(check_every),
         _lib.ptr(fi), _lib.ptr(gi), _lib.ptr(f), _lib.ptr(g), _lib.ptr(f_pre), _lib.ptr(g_pre),
         _lib.ptr(iters),
-        prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+        prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev), labels.ref if labels else None,
     )
     out = (f, g)
     if want_pre:

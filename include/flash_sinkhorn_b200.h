@@ -90,6 +90,21 @@ double fs_micro_exp_rate(int mode, int warps_per_sm);
  * tile). Allocates a few KB and synchronises; < 0 on error. */
 double fs_micro_mma_cycles(int n_cols, int a_in_tmem);
 
+/* Optional label-augmented ground cost (OTDD), reference kernels/sinkhorn_flashstyle_sqeuclid.py:545-560
+ * and kernels/sinkhorn_triton_grad_sqeuclid.py:225-236: the logit of entry (i, j) becomes
+ *   (lambda_x * 2cs * x_i.y_j - lambda_y * cs * W[label_x_i, label_y_j]) / eps + bias_j.
+ * A NULL pointer, V <= 0 or lambda_y == 0 means the plain squared-Euclidean cost. Entry points that take
+ * this descriptor size their workspace with d + 3*V in place of d (the tensor-core engine carries the
+ * table through the contraction as 3V extra operand columns). All pointers are device pointers. */
+typedef struct fs_label_cost {
+  const int* label_x;    /* [n] class of every x point, in [0, V) */
+  const int* label_y;    /* [m] class of every y point, in [0, V) */
+  const float* W;        /* [V, V] row-major label-to-label cost, indexed W[label_x, label_y] */
+  int V;
+  float lambda_x;        /* weight of the Euclidean term (> 0) */
+  float lambda_y;        /* weight of the label term */
+} fs_label_cost;
+
 /* Scratch bytes needed by `op` (one of FS_OP_*) at these sizes. */
 size_t fs_workspace_bytes(int op, int n, int m, int d, int prec);
 
@@ -128,7 +143,8 @@ int fs_symmetric_step(const float* x, const float* y, int n, int m, int d,
                       float* f_out, float* g_out,
                       const float* alpha_x, const float* beta_y,
                       float eps, float w, float damp_f, float damp_g, float cost_scale,
-                      int prec, void* ws, size_t ws_bytes, void* stream);
+                      int prec, void* ws, size_t ws_bytes, void* stream,
+                      const fs_label_cost* labels);
 
 /* Row-sharded form of fs_symmetric_step for multi-GPU solves (no reference counterpart: the
  * reference is single-GPU). Only rows [f_begin, f_end) of f_out and [g_begin, g_end) of g_out are
@@ -173,7 +189,8 @@ int fs_solve_symmetric(const float* x, const float* y, int n, int m, int d,
                        const float* f_init, const float* g_init,
                        float* f, float* g, float* f_pre, float* g_pre,
                        int* iters_used,
-                       int prec, void* ws, size_t ws_bytes, void* stream);
+                       int prec, void* ws, size_t ws_bytes, void* stream,
+                       const fs_label_cost* labels);
 
 /* Whole alternating (Gauss-Seidel) solve. For each eps of eps_list, iters_per_eps
  * iterations of { f_hat <- LSE(g_hat) ; g_hat <- LSE(new f_hat) } (no averaging,
@@ -243,7 +260,8 @@ int fs_grad(const float* x, const float* y, int n, int m, int d,
             const float* f, const float* g, const float* grad_scale,
             float* grad_x, float* grad_y,
             float eps, float cost_scale,
-            int prec, void* ws, size_t ws_bytes, void* stream);
+            int prec, void* ws, size_t ws_bytes, void* stream,
+            const fs_label_cost* labels);
 
 /* out_i = (-4cs/eps) sum_j P_ij (A_i.y_j) y_j with P_ij = exp((f_i+g_j-C_ij)/eps)
  * (OTT-convention potentials, log-weights already inside f, g). Replaces

@@ -355,6 +355,71 @@ def inverse_hvp_x(x, y, f_ott, g_ott, gr, eps, *, cost_scale=1.0, tau2=1e-5, max
     return dict(z=z.reshape(n, d), cg_converged=conv, cg_iters=iters, cg_residual=res, cg_initial_residual=r0)
 
 
+# --------------------------------------------------------------------------- OTDD label-augmented cost
+def label_solve_symmetric(x, y, a, b, eps_list: Sequence[float], label_x, label_y, W, *, lambda_x=1.0,
+                          lambda_y=1.0, cost_scale=1.0, last_extrapolation=True) -> Dict:
+    """Balanced symmetric solve with the label term of kernels/sinkhorn_flashstyle_sqeuclid.py:545-560:
+    logit_ij = (lambda_x*2cs*x_i.y_j - lambda_y*cs*W[lx_i, ly_j] + g_hat_j)/eps + log b_j, the shifts
+    alpha = cs|x|^2, beta = cs|y|^2 NOT scaled by lambda_x (sinkhorn_solvers.py:463-470); same step
+    sequence as solve_symmetric."""
+    dt = x.dtype
+    alpha, beta = cost_scale * sqnorm(x), cost_scale * sqnorm(y)
+    log_a, log_b = log_weights(a).astype(dt), log_weights(b).astype(dt)
+    core = lambda_x * 2.0 * cost_scale * (x @ y.T) - lambda_y * cost_scale * W[np.ix_(label_x, label_y)]
+    f_hat, g_hat = -alpha.copy(), -beta.copy()
+
+    def step(fh, gh, eps, w):
+        cf = -eps * _lse((core + gh[None, :]) / eps + log_b[None, :], axis=1)
+        cg = -eps * _lse((core + fh[:, None]) / eps + log_a[:, None], axis=0)
+        return ((1 - w) * fh + w * cf).astype(dt), ((1 - w) * gh + w * cg).astype(dt)
+
+    f_hat, g_hat = step(f_hat, g_hat, eps_list[0], 1.0)
+    for eps in eps_list:
+        f_hat, g_hat = step(f_hat, g_hat, eps, 0.5)
+    out = dict(f_pre=f_hat + alpha, g_pre=g_hat + beta)
+    if last_extrapolation:
+        f_hat, g_hat = step(f_hat, g_hat, eps_list[-1], 1.0)
+    out.update(f=f_hat + alpha, g=g_hat + beta)
+    return out
+
+
+def label_grad_xy(x, y, a, b, f, g, eps, label_x, label_y, W, *, lambda_x=1.0, lambda_y=1.0, cost_scale=1.0,
+                  grad_scale=1.0):
+    """kernels/sinkhorn_triton_grad_sqeuclid.py:225-236, :275: weights from the cost
+    lambda_x*cs|x-y|^2 + lambda_y*cs*W[lx, ly]; grad_x_i = 2*lambda_x*cs*gs*a_i*(x_i - ybar_i)."""
+    C = (lambda_x * cost_scale * (sqnorm(x)[:, None] + sqnorm(y)[None, :] - 2.0 * (x @ y.T))
+         + lambda_y * cost_scale * W[np.ix_(label_x, label_y)])
+    lw = (g[None, :] - C) / eps + log_weights(b)[None, :]
+    w = np.exp(lw - lw.max(axis=1, keepdims=True))
+    gx = (2.0 * lambda_x * cost_scale * grad_scale) * a[:, None] * (x - (w @ y) / w.sum(axis=1, keepdims=True))
+    lw = (f[:, None] - C) / eps + log_weights(a)[:, None]
+    w = np.exp(lw - lw.max(axis=0, keepdims=True))
+    gy = (2.0 * lambda_x * cost_scale * grad_scale) * b[:, None] * (y - (w.T @ x) / w.sum(axis=0)[:, None])
+    return gx, gy
+
+
+def label_samples_loss(x, y, a, b, eps_list, label_x, label_y, W, *, lambda_x=1.0, lambda_y=1.0, cost_scale=1.0,
+                       debias=False) -> Dict:
+    """samples_loss.py:494-512 with labels: OT(x,y) uses (label_x, label_y), OT(x,x) (label_x, label_x),
+    OT(y,y) (label_y, label_y); cost <a,f>+<b,g>; gradient from the pre-extrapolation potentials."""
+    eps = float(eps_list[-1])
+    kw = dict(lambda_x=lambda_x, lambda_y=lambda_y, cost_scale=cost_scale)
+
+    def one(p, q, wp, wq, lp, lq):
+        s = label_solve_symmetric(p, q, wp, wq, eps_list, lp, lq, W, **kw)
+        return float(np.sum(wp * s["f"]) + np.sum(wq * s["g"])), s
+
+    c_xy, s_xy = one(x, y, a, b, label_x, label_y)
+    gx, _ = label_grad_xy(x, y, a, b, s_xy["f_pre"], s_xy["g_pre"], eps, label_x, label_y, W, **kw)
+    out = dict(loss=c_xy, grad_x=gx)
+    if debias:
+        c_xx, s_xx = one(x, x, a, a, label_x, label_x)
+        c_yy, _ = one(y, y, b, b, label_y, label_y)
+        g1, g2 = label_grad_xy(x, x, a, a, s_xx["f_pre"], s_xx["g_pre"], eps, label_x, label_x, W, **kw)
+        out.update(loss=c_xy - 0.5 * c_xx - 0.5 * c_yy, grad_x=gx - 0.5 * (g1 + g2))
+    return out
+
+
 # --------------------------------------------------------------------------- hard c-transform
 def c_transform(x, y, psi, cost_scale=1.0):
     """c_transform.py:32-112 / kernels/c_transform_sqeuclid.py:117-206: c_i = min_j [cs|x_i-y_j|^2 - psi_j]

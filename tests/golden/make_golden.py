@@ -276,6 +276,40 @@ def gen_implicit():
     save("implicit_small", **out)
 
 
+def gen_label_cost():
+    """OTDD label-augmented cost: the reference's symmetric solver, gradient kernel and SamplesLoss
+    (forward + grad_x, debiased and not) with a non-symmetric label table, interpreter run."""
+    n, m, d, V = 60, 44, 7, 5
+    x, y, a, b = clouds(81, n, m, d, shift=0.25, weights="softmax")
+    gen = torch.Generator().manual_seed(82)
+    lx = torch.randint(0, V, (n,), generator=gen)
+    ly = torch.randint(0, V, (m,), generator=gen)
+    W = torch.rand(V, V, generator=gen) * 2.0
+    W.fill_diagonal_(0.0)
+    out = dict(x=np32(x), y=np32(y), a=np32(a), b=np32(b), label_x=lx.numpy().astype(np.int64),
+               label_y=ly.numpy().astype(np.int64), W=np32(W))
+    for name, (lam_x, lam_y, cs, eps) in {"unit": (1.0, 1.0, 1.0, 0.5), "mixed": (0.7, 1.8, 0.5, 0.4)}.items():
+        kw = dict(label_x=lx, label_y=ly, label_cost_matrix=W, lambda_x=lam_x, lambda_y=lam_y)
+        f, g, fp, gp = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=eps, n_iters=40,
+                                                     allow_tf32=False, autotune=False, cost_scale=cs,
+                                                     return_prelast=True, **kw)
+        gx, gy = sinkhorn_geomloss_online_grad_sqeuclid(x, y, a, b, fp, gp, eps=eps, allow_tf32=False, cost_scale=cs,
+                                                        num_warps=4, **MANUAL, **kw)
+        out.update({name + "_lam": np.array([lam_x, lam_y, cs, eps], np.float64), name + "_f": np32(f),
+                    name + "_g": np32(g), name + "_fpre": np32(fp), name + "_gpre": np32(gp),
+                    name + "_grad_x": np32(gx), name + "_grad_y": np32(gy)})
+        for debias in (False, True):
+            loss = SamplesLoss("sinkhorn", use_epsilon_scaling=False, eps=eps, n_iters=40, debias=debias,
+                               half_cost=(cs == 0.5), allow_tf32=False, autotune=False, normalize=False,
+                               label_cost_matrix=W, lambda_x=lam_x, lambda_y=lam_y)
+            xr = x.clone().requires_grad_(True)
+            val = loss(a, xr, b, y, label_x=lx, label_y=ly)
+            (gxl,) = torch.autograd.grad(val, xr)
+            tag = f"{name}_loss_{'deb' if debias else 'raw'}"
+            out[tag], out[tag + "_grad_x"] = np.float64(val.item()), np32(gxl)
+    save("label_cost_small", **out)
+
+
 def gen_c_transform():
     """Hard c-transform (c_transform.py, kernels/c_transform_sqeuclid.py), interpreter run with manual blocks:
     values, arg-min indices, the semi-dual objective and its Danskin gradients; plus the tie-break case of
@@ -372,10 +406,10 @@ def gen_config1():
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--skip-c1", action="store_true", help="skip the 4096x4096 dense solves (several minutes)")
-    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,dense,c1")
+    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,labels,dense,c1")
     args = ap.parse_args()
     which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "implicit",
-                                                         "ctransform", "dense", "c1"}
+                                                         "ctransform", "labels", "dense", "c1"}
     print("reference version", flash_sinkhorn.__version__, "from", os.path.dirname(flash_sinkhorn.__file__))
     if "dense" in which:
         gen_dense_reference()
@@ -391,6 +425,8 @@ if __name__ == "__main__":
         gen_implicit()
     if "ctransform" in which:
         gen_c_transform()
+    if "labels" in which:
+        gen_label_cost()
     if "c1" in which and not args.skip_c1:
         gen_config1()
     sys.exit(0)

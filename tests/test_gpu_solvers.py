@@ -312,3 +312,43 @@ def test_inverse_hvp_vs_reference(monkeypatch):
     assert rel(host(sol), z["inv_z"]) < 2e-3
     back, _ = hvp_x_sqeuclid_from_potentials(x, y, fo, go, sol, eps=eps, max_cg_iter=300, cg_rtol=1e-8, cg_atol=1e-8)
     assert rel(host(back), z["inv_gr"]) < 1e-4
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", ["unit", "mixed"])
+def test_label_cost_vs_reference(monkeypatch, mode, name):
+    """OTDD label-augmented cost (non-symmetric table, lambda_x != 1 in the 'mixed' case): solver, gradient
+    kernel and SamplesLoss forward + grad_x, debiased and not, against the reference's results."""
+    from flash_sinkhorn_b200 import SamplesLoss
+    from flash_sinkhorn_b200.kernels.grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_symmetric
+    set_mode(monkeypatch, mode)
+    z = load_golden("label_cost_small")
+    x, y, a, b, W = (dev(z[k]) for k in ("x", "y", "a", "b", "W"))
+    lx, ly = torch.as_tensor(z["label_x"]).cuda(), torch.as_tensor(z["label_y"]).cuda()
+    lam_x, lam_y, cs, eps = (float(v) for v in z[name + "_lam"])
+    kw = dict(label_x=lx, label_y=ly, label_cost_matrix=W, lambda_x=lam_x, lambda_y=lam_y)
+    tol = TOL[mode]
+    f, g, fp, gp = sinkhorn_flashstyle_symmetric(x, y, a, b, use_epsilon_scaling=False, eps=eps, n_iters=40,
+                                                 cost_scale=cs, return_prelast=True, allow_tf32=(mode == "tf32"), **kw)
+    for got, tag in ((f, "_f"), (g, "_g"), (fp, "_fpre"), (gp, "_gpre")):
+        assert rel(host(got), z[name + tag]) < tol, tag
+    gx, gy = sinkhorn_geomloss_online_grad_sqeuclid(x, y, a, b, dev(z[name + "_fpre"]), dev(z[name + "_gpre"]),
+                                                    eps=eps, cost_scale=cs, allow_tf32=(mode == "tf32"), **kw)
+    gtol = 3e-2 if mode == "tf32" else 3e-4
+    assert rel(host(gx), z[name + "_grad_x"]) < gtol and rel(host(gy), z[name + "_grad_y"]) < gtol
+    for debias, tag in ((False, "raw"), (True, "deb")):
+        loss = SamplesLoss("sinkhorn", use_epsilon_scaling=False, eps=eps, n_iters=40, debias=debias,
+                           half_cost=(cs == 0.5), allow_tf32=(mode == "tf32"), normalize=False,
+                           label_cost_matrix=W, lambda_x=lam_x, lambda_y=lam_y)
+        xr = x.clone().requires_grad_(True)
+        val = loss(a, xr, b, y, label_x=lx, label_y=ly)
+        (gxl,) = torch.autograd.grad(val, xr, create_graph=True)
+        want = float(z[f"{name}_loss_{tag}"])
+        assert abs(val.item() - want) < (2e-3 if mode == "tf32" else 5e-5) * max(1.0, abs(want))
+        assert rel(host(gxl), z[f"{name}_loss_{tag}_grad_x"]) < gtol
+        with pytest.raises(NotImplementedError):
+            torch.autograd.grad(gxl.sum(), xr)  # HVP with a label cost, as in the reference
+    with pytest.raises(ValueError):
+        sinkhorn_flashstyle_symmetric(x, y, a, b, eps=eps, n_iters=3, use_epsilon_scaling=False,
+                                      label_x=lx + 100, label_y=ly, label_cost_matrix=W, lambda_y=1.0)

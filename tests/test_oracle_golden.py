@@ -218,3 +218,25 @@ def test_c_transform_tie_break():
     y = z["tie_y"].astype(F64)
     _, idx = O.c_transform(np.zeros((1, 4)), y, np.zeros(96))
     assert int(z["tie_idx"][0]) == 0 and int(idx[0]) == 0  # equidistant targets 0 and 64: the smaller index
+
+
+@pytest.mark.parametrize("name", ["unit", "mixed"])
+def test_label_cost(name):
+    """Oracle vs the reference's label-augmented symmetric solve, gradient kernel and SamplesLoss."""
+    z = load_golden("label_cost_small")
+    x, y, a, b, W = d64(z, "x", "y", "a", "b", "W")
+    lx, ly = z["label_x"], z["label_y"]
+    lam_x, lam_y, cs, eps = (float(v) for v in z[name + "_lam"])
+    kw = dict(lambda_x=lam_x, lambda_y=lam_y, cost_scale=cs)
+    s = O.label_solve_symmetric(x, y, a, b, [eps] * 40, lx, ly, W, **kw)
+    for key, tag in (("f", "_f"), ("g", "_g"), ("f_pre", "_fpre"), ("g_pre", "_gpre")):
+        assert np.isfinite(z[name + tag]).all()
+        assert rel_err(s[key], z[name + tag]) < 3e-5, key
+    gx, gy = O.label_grad_xy(x, y, a, b, z[name + "_fpre"].astype(F64), z[name + "_gpre"].astype(F64), eps, lx, ly,
+                             W, **kw)
+    assert rel_err(gx, z[name + "_grad_x"]) < 1e-4 and rel_err(gy, z[name + "_grad_y"]) < 1e-4
+    for debias, tag in ((False, "raw"), (True, "deb")):
+        r = O.label_samples_loss(x, y, a, b, [eps] * 40, lx, ly, W, debias=debias, **kw)
+        want = float(z[f"{name}_loss_{tag}"])
+        assert abs(r["loss"] - want) < 2e-5 * max(1.0, abs(want)), (debias, r["loss"], want)
+        assert rel_err(r["grad_x"], z[f"{name}_loss_{tag}_grad_x"]) < 2e-4
