@@ -49,6 +49,7 @@ SIGNATURES = {
     "fs_device_error": (c_int, []),
     "fs_micro_exp_rate": (c_double, [c_int, c_int]),
     "fs_micro_mma_cycles": (c_double, [c_int, c_int]),
+    "fs_set_reserved_sms": (c_int, [c_int]),
     "fs_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "fs_lse": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_float, c_float, c_float, c_int, _P, c_size_t, _P]),
     "fs_c_transform": (c_int, [_P, _P, c_int, c_int, c_int, _P, c_float, _P, _P, c_int, _P, c_size_t, _P]),

@@ -96,3 +96,6 @@ extern "C" double fs_micro_exp_rate(int mode, int warps_per_sm) {
 extern "C" double fs_micro_mma_cycles(int n_cols, int a_in_tmem) {
   return fs::tc::micro_mma_cycles(n_cols, a_in_tmem != 0);
 }
+
+// See the header: SMs the streaming passes leave to concurrently running collectives.
+extern "C" int fs_set_reserved_sms(int k) { return fs::tc::set_reserved_sms(k); }

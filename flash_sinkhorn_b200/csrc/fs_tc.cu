@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 namespace fs {
@@ -1206,9 +1207,14 @@ constexpr int kNumSMs = 148;
 // CTAs of an LSE pass. The nblk*ntiles (row block, column tile) items are cut into equal contiguous ranges,
 // one per CTA: a single wave of at most one CTA per SM, at least ~4 tiles each, and no row block shared by
 // more than kMaxChunks CTAs (that many partial slots exist per row).
+std::atomic<int> g_reserved_sms{0};
+
 int pick_ctas(int nblk, int ntiles) {
   const long long total = (long long)nblk * ntiles;
-  long long g = kNumSMs;
+  // SMs left free on request (a collective running next to the pass needs a few: a CTA of this kernel
+  // fills its SM, and one that has to wait for the collective to leave delays the whole single wave).
+  long long g = kNumSMs - g_reserved_sms.load(std::memory_order_relaxed);
+  if (g < 1) g = 1;
   if (const char* env = getenv("FLASH_SINKHORN_B200_CTAS")) {  // diagnostics: force the CTA count
     int c = atoi(env);
     if (c >= 1 && c <= kNumSMs) g = c;
@@ -1235,6 +1241,12 @@ int pick_ctas(int nblk, int ntiles) {
 }
 
 }  // namespace
+
+int set_reserved_sms(int k) {
+  if (k < 0) k = 0;
+  if (k > kNumSMs - 1) k = kNumSMs - 1;
+  return g_reserved_sms.exchange(k, std::memory_order_relaxed);
+}
 
 bool supported(int n, int m, int d, int prec) {
   if (prec != 0 && prec != 1) return false;

@@ -27,6 +27,9 @@ struct Staged {
   int* tickets = nullptr;   // [rows_pad / 128] per-row-block arrival counters of the CTAs sharing a row block (zero at rest)
 };
 
+// Streaming passes leave `k` SMs unused from now on (process-wide; returns the previous value).
+int set_reserved_sms(int k);
+
 bool supported(int n, int m, int d, int prec);
 size_t staged_bytes(int n, int m, int d, int prec);
 // run_kernels = false only lays out the pointers inside `buf` (operands staged there by an earlier call

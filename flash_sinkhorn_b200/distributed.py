@@ -236,9 +236,20 @@ def symmetric_solve_sharded_many(problems, *, group):
     set of :func:`symmetric_solve_sharded` without ``group``). While one problem's all-gather is in flight
     the next problem computes, which hides the exchange even for self-transport problems, whose single
     half-step per iteration leaves nothing of their own to overlap with."""
+    import os
+
+    from flash_sinkhorn_b200 import _lib
+
     gather, world, rank = _gather_inplace(group, overlap=True)
     built = [_cuda_problem(gather=gather, world=world, rank=rank, **pr) for pr in problems]
-    results = run_many([g for g, _ in built])
+    # The all-gather of one half-step runs next to the streaming pass of the next one; that pass is a single
+    # wave of one CTA per SM, so it leaves a few SMs to the collective instead of waiting for them.
+    lib = _lib.load()
+    previous = lib.fs_set_reserved_sms(int(os.environ.get("FLASH_SINKHORN_B200_RESERVED_SMS", "2")))
+    try:
+        results = run_many([g for g, _ in built])
+    finally:
+        lib.fs_set_reserved_sms(previous)
     return [fin(res) for (_, fin), res in zip(built, results)]
 
 

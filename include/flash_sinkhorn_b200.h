@@ -90,6 +90,13 @@ double fs_micro_exp_rate(int mode, int warps_per_sm);
  * tile). Allocates a few KB and synchronises; < 0 on error. */
 double fs_micro_mma_cycles(int n_cols, int a_in_tmem);
 
+/* Multi-GPU helper (no reference counterpart): from now on the streaming passes of this process use k SMs
+ * fewer than the device has, leaving them to a collective (NCCL all-gather of the previous half-step) that
+ * runs next to the pass. A pass is a single wave of one CTA per SM with a static work split, so a CTA that
+ * must wait for the collective's CTAs to leave its SM delays the whole pass; k = 2 costs ~1 % when nothing
+ * else runs. Returns the previous value; 0 restores the default. */
+int fs_set_reserved_sms(int k);
+
 /* Optional label-augmented ground cost (OTDD), reference kernels/sinkhorn_flashstyle_sqeuclid.py:545-560
  * and kernels/sinkhorn_triton_grad_sqeuclid.py:225-236: the logit of entry (i, j) becomes
  *   (lambda_x * 2cs * x_i.y_j - lambda_y * cs * W[label_x_i, label_y_j]) / eps + bias_j.
