@@ -50,3 +50,29 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError):
         _lib.load()
+
+
+def test_label_cost_descriptor_validation_and_workspace():
+    """Host logic of the label-cost arguments (no GPU): the reference's activation rule and errors
+    (kernels/sinkhorn_flashstyle_sqeuclid.py:1183-1208), the ctypes mirror of fs_label_cost, and the
+    workspace rule d -> d + 3V."""
+    import torch
+    from flash_sinkhorn_b200 import _lib
+    cpu = torch.device("cpu")
+    lx, ly, W = torch.tensor([0, 2, 1]), torch.tensor([1, 1]), torch.rand(3, 3)
+    mk = lambda **kw: _lib.LabelCost.make(kw.get("lx", lx), kw.get("ly", ly), kw.get("W", W), kw.get("lam_x", 1.0),
+                                          kw.get("lam_y", 1.0), 3, 2, cpu)
+    assert mk(lam_y=0.0) is None and mk(W=None) is None and mk(lx=None) is None
+    lc = mk()
+    assert lc.V == 3 and lc.label_x.dtype == torch.int32 and lc.table.dtype == torch.float32
+    assert lc.struct.V == 3 and lc.struct.label_x == lc.label_x.data_ptr() and lc.struct.lambda_y == 1.0
+    assert ctypes.sizeof(_lib.LabelCostStruct) == 3 * ctypes.sizeof(ctypes.c_void_p) + 12 + 4  # padded to 8
+    for bad in (dict(lx=torch.tensor([0, 1])), dict(ly=torch.tensor([0, 3])), dict(W=torch.rand(3, 2)),
+                dict(W=torch.rand(3)), dict(lx=torch.tensor([0, -1, 1])), dict(lam_x=0.0)):
+        with pytest.raises(ValueError):
+            mk(**bad)
+    lib = _lib.load()
+    plain = lib.fs_workspace_bytes(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_TF32)
+    labelled = lib.fs_workspace_bytes(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64 + 3 * 10, _lib.PREC_TF32)
+    assert labelled > plain
+    assert lib.fs_set_reserved_sms(3) == 0 and lib.fs_set_reserved_sms(0) == 3
