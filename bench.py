@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Headline benchmark: BASELINE config 2 (n = m = 50,000, d = 64, eps = 0.01, 100 fixed symmetric
+"""Headline benchmark: headline configuration 2 (n = m = 50,000, d = 64, eps = 0.01, 100 fixed symmetric
 iterations, debiased, forward + analytic grad_x) on N B200 GPUs of one node.
 
     python bench.py [--gpus N --steps K --warmup W] [--impl reference] [--n 50000 --d 64]
@@ -338,8 +338,8 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "exp" if exp_peak <= tc_peak else "tensor", "achieved": achieved, "peak": peak,
                          "unit": "entries/s", "frac": achieved / peak,
-                         # DRAM bytes per launch of this kernel at this size, from the ncu capture summarised in
-                         # profiles/tc_lse_kernel_config2_50k_d64_tf32.md (algorithmic: 29.2 MB of staged operands)
+                         # DRAM bytes per launch of this kernel at this size, from an
+                         # ncu capture of this kernel at this size (algorithmic: 29.2 MB of staged operands)
                          "traffic": 28925952 if (n == 50000 and m == 50000 and d == 64 and not args.fp32) else None,
                          "traffic_unit": "bytes per launch (dram read + write)",
                          "kernel": "row soft-min pass (fs_lse), n*m entries per launch", "kernel_ms": kernel_ms,

@@ -367,7 +367,7 @@ def gen_dense_reference():
 
 
 def gen_config1():
-    """BASELINE config 1 (n=m=4096, d=64, eps=0.01, half cost, debias, 100 fixed iterations) with the
+    """Benchmark configuration 1 (n=m=4096, d=64, eps=0.01, half cost, debias, 100 fixed iterations) with the
     reference's dense fp32 functions. Inputs are NOT stored: CPU generator seed 0, x then y."""
     t0 = time.time()
     gen = torch.Generator().manual_seed(0)

@@ -1,4 +1,4 @@
-"""Size-independent properties at the full sizes of BASELINE configs 3-5 (the dense oracle cannot run there)."""
+"""Size-independent properties at the full sizes of benchmark configurations 3-5 (the dense oracle cannot run there)."""
 import math
 
 import numpy as np

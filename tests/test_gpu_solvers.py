@@ -204,7 +204,7 @@ def test_double_backward_equals_direct_hvp():
 
 @pytest.mark.parametrize("allow_tf32", [False, True])
 def test_config1_matches_reference_golden(allow_tf32):
-    """BASELINE config 1: n=m=4096, d=64, eps=0.01, half cost, debias, 100 fixed iterations.
+    """Benchmark configuration 1: n=m=4096, d=64, eps=0.01, half cost, debias, 100 fixed iterations.
     Tolerances are the north-star ones: loss rel 1e-4, grad_x rel 1e-3 (of the gradient's max-norm)."""
     from flash_sinkhorn_b200 import SamplesLoss
     z = load_golden("config1")
@@ -225,7 +225,7 @@ def test_config1_matches_reference_golden(allow_tf32):
 
 
 def test_marginals_at_scale_property():
-    """Size-independent property at BASELINE config-2 size (n=m=50,000, d=64): after a g-update of the
+    """Size-independent property at configuration-2 size (n=m=50,000, d=64): after a g-update of the
     alternating solver the column marginals of the plan equal b (reference test_flashstyle_parity.py:291-320)."""
     from flash_sinkhorn_b200.kernels._common import log_weights
     from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_vec_flashstyle
