@@ -79,6 +79,8 @@ def cpu_reference_sample(n, m, d, eps, seconds_budget=20.0):
     """Dense PyTorch CPU baseline on a bounded sample of the same workload (entries/s is scale-free)."""
     import torch
     from oracle import dense_torch
+    # all host threads, also under torchrun (which exports OMP_NUM_THREADS=1 to every rank when N > 1)
+    torch.set_num_threads(max(torch.get_num_threads(), len(os.sched_getaffinity(0))))
     gen = torch.Generator().manual_seed(1)
     x = torch.randn(n, d, generator=gen)
     y = 0.5 + torch.randn(m, d, generator=gen)
