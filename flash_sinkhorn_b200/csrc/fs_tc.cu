@@ -1,19 +1,23 @@
-// tcgen05 / TMEM / TMA streaming log-sum-exp engine for sm_100a.
+// tcgen05 / TMEM / TMA streaming engine for sm_100a: LSE pass (potential updates), arg-max pass (hard
+// c-transform) and plan-times-matrix pass (gradient, plan applications).
 //
-// One CTA owns BM = 128*NHALF rows of the "row" cloud. Its row operand (K-padded, with
-// constant ones in the bias columns) is loaded once by TMA and stays resident in shared
-// memory; column tiles of BN rows of the "column" cloud stream through an NSTAGE ring of
-// TMA-filled buffers. Warp roles (FlashAttention-style specialisation):
-//   warp 0      : TMA producer (one elected lane)
-//   warp 1      : tcgen05.mma issuer (one elected lane); owns the TMEM allocation
-//   warps 2,3   : idle
-//   warps 4..   : one soft-max warpgroup per 128-row half; thread t of a warpgroup owns
-//                 score row t (TMEM lane t), so row max / row sum need no shuffles.
-// Per column tile and half the MMA warp accumulates S = A_half x B_tile^T (M=128, N=BN,
-// K=8 per instruction, kind::tf32) into one of two TMEM buffers of that half, commits to
-// an mbarrier, and the warpgroup drains the other buffer with tcgen05.ld meanwhile.
-// Because the bias sits in the contraction, the drained value is (logit / scale): the
-// warpgroup does max -> one FFMA + one ex2.approx + one FADD per entry.
+// LSE / arg-max pass. Work item = (row block of BM = 128*NHALF rows of the "row" cloud, column tile of BN
+// rows of the "column" cloud). The items, row block after row block, are cut into equal contiguous ranges,
+// one per CTA, one CTA per SM (a single wave). For each row block it touches ("segment") a CTA keeps the
+// K-padded row operand (constant ones in the bias columns) resident in shared memory while column tiles
+// stream through an NSTAGE ring of TMA-filled buffers. Warp roles (FlashAttention-style specialisation):
+//   warp 0      : TMA producer (one lane)
+//   warps 1, 3  : tcgen05.mma issuers, one lane per 128-row half; warp 1 owns the TMEM allocation
+//   warp 2      : idle
+//   warps 4..   : soft-max warpgroups, one per 128-row half and half of each tile's columns; thread t of a
+//                 warpgroup owns score row t (TMEM lane t), so row max / row sum need no shuffles.
+// Per column tile and half an MMA lane accumulates S = A_half x B_tile^T (M=128, N=BN, K=8 per instruction,
+// kind::tf32) into one of two TMEM buffers of that half, commits to an mbarrier, and the warpgroups drain the
+// other buffer with tcgen05.ld meanwhile. Because the bias sits in the contraction, the drained value is
+// (logit / scale): max -> one FFMA + one ex2.approx + one FADD per entry. A row block shared by several CTAs
+// gets one partial per row from each; the CTA that takes the block's last ticket merges them in a fixed order.
+//
+// Plan-times-matrix pass: see tc_pv_kernel below (second GEMM with the weights read from TMEM).
 //
 // Every wait on an mbarrier is bounded (clock64 budget); a wait that runs out raises a
 // CTA-wide abort flag, the CTA drains its outstanding copies and MMAs (bounded again),
