@@ -51,6 +51,7 @@ SIGNATURES = {
     "fs_micro_mma_cycles": (c_double, [c_int, c_int]),
     "fs_set_reserved_sms": (c_int, [c_int]),
     "fs_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "fs_workspace_bytes_labels": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "fs_lse": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_float, c_float, c_float, c_int, _P, c_size_t, _P]),
     "fs_c_transform": (c_int, [_P, _P, c_int, c_int, c_int, _P, c_float, _P, _P, c_int, _P, c_size_t, _P]),
     "fs_symmetric_step": (
@@ -182,8 +183,9 @@ def require_cuda(**tensors: Optional[torch.Tensor]) -> torch.device:
     return dev
 
 
-def workspace(op: int, n: int, m: int, d: int, prec: int, device: torch.device) -> torch.Tensor:
-    nbytes = int(load().fs_workspace_bytes(op, n, m, d, prec))
+def workspace(op: int, n: int, m: int, d: int, prec: int, device: torch.device, n_classes: int = 0) -> torch.Tensor:
+    """Scratch tensor for one call of ``op``; ``n_classes`` = V of the label cost the call will pass (0 = none)."""
+    nbytes = int(load().fs_workspace_bytes_labels(op, n, m, d, prec, int(n_classes)))
     return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
 
 

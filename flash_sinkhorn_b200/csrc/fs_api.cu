@@ -161,7 +161,7 @@ struct Problem {
   tc::Staged staged;  // tcgen05 operands (valid when use_tc)
   bool use_tc = false;
   LabelCost lab;      // V == 0: plain squared-Euclidean cost
-  int d_tc = 0;       // feature count the tensor-core engine plans with (d + 3V: the label table rides in the contraction)
+  int nlab = 0;       // label-table columns of the tensor-core operands (3V: the table rides in the contraction)
 
   StreamArgs stream_args(int side, const float* pot, const float* logw, float eps) const {
     StreamArgs s;
@@ -218,14 +218,14 @@ struct Problem {
     return simt_vec(s, v, st);
   }
   bool vec_on_tc() const {
-    return use_tc && pv_scratch && !csr_rp[0] && tc::pv_supported(d_tc, prec, 1) &&
-           tc::pv_scratch_bytes(n > m ? n : m, d_tc, prec, 1) <= pv_scratch_bytes;
+    return use_tc && pv_scratch && !csr_rp[0] && tc::pv_supported(d, prec, 1, nlab) &&
+           tc::pv_scratch_bytes(n > m ? n : m, d, prec, 1, nlab) <= pv_scratch_bytes;
   }
   cudaError_t pv(int side, const float* pot, const float* logw, float eps, const PvArgs& p) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (use_tc && !p.rows2 && !s.tile_row_ptr && pv_scratch && tc::pv_supported(d_tc, prec, p.dv) &&
-        tc::pv_scratch_bytes(s.nc, d_tc, prec, p.dv) <= pv_scratch_bytes)
+    if (use_tc && !p.rows2 && !s.tile_row_ptr && pv_scratch && tc::pv_supported(d, prec, p.dv, nlab) &&
+        tc::pv_scratch_bytes(s.nc, d, prec, p.dv, nlab) <= pv_scratch_bytes)
       return tc::pv(staged, side, s, p, pv_scratch, st);
     return simt_pv(s, p, st);
   }
@@ -257,10 +257,10 @@ int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int 
                  const LabelCost* lab = nullptr) {
   p.x = x; p.y = y; p.n = n; p.m = m; p.d = d; p.cs = cs; p.prec = prec; p.st = st;
   if (lab && lab->V > 0) p.lab = *lab;
-  p.d_tc = d + 3 * p.lab.V;
-  p.use_tc = (prec != FS_PREC_SIMT) && tc::supported(n, m, p.d_tc, prec);
+  p.nlab = 3 * p.lab.V;
+  p.use_tc = (prec != FS_PREC_SIMT) && tc::supported(n, m, d, prec, p.nlab);
   if (p.use_tc) {
-    size_t bytes = tc::staged_bytes(n, m, p.d_tc, prec);
+    size_t bytes = tc::staged_bytes(n, m, d, prec, p.nlab);
     char* buf = ws.take<char>(bytes);
     if (!measure_only) {
       if (ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
@@ -269,8 +269,8 @@ int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int 
                                 -p.lab.lam_w / (2.0f * cs));
       if (e != cudaSuccess) return fail(FS_ERR_CUDA, "staging tcgen05 operands failed: %s", cudaGetErrorString(e));
     }
-    if (pv_dv > 0 && tc::pv_supported(p.d_tc, prec, pv_dv)) {
-      p.pv_scratch_bytes = tc::pv_scratch_bytes(n > m ? n : m, p.d_tc, prec, pv_dv);
+    if (pv_dv > 0 && tc::pv_supported(d, prec, pv_dv, p.nlab)) {
+      p.pv_scratch_bytes = tc::pv_scratch_bytes(n > m ? n : m, d, prec, pv_dv, p.nlab);
       p.pv_scratch = ws.take<char>(p.pv_scratch_bytes);
       if (!measure_only && ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
     }
@@ -342,12 +342,19 @@ int fs_device_arch(void) {
 }
 
 size_t fs_workspace_bytes(int op, int n, int m, int d, int prec) {
+  return fs_workspace_bytes_labels(op, n, m, d, prec, 0);
+}
+
+size_t fs_workspace_bytes_labels(int op, int n, int m, int d, int prec, int n_classes) {
   if (n <= 0 || m <= 0 || d <= 0) return 0;
   Ws ws(nullptr, 0);
   Problem p;
   const bool matrix_op = (op == FS_OP_APPLY_MAT || op == FS_OP_GRAD);
   const bool vector_op = (op == FS_OP_APPLY_VEC || op == FS_OP_SCHUR);
-  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true, matrix_op ? d : (vector_op ? 1 : 0));
+  LabelCost lc;
+  lc.V = n_classes > 0 ? n_classes : 0;  // only the class count matters for sizes
+  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true, matrix_op ? d : (vector_op ? 1 : 0),
+               true, &lc);
   size_t nm = (size_t)(n > m ? n : m);
   switch (op) {
     case FS_OP_LSE:

@@ -1077,38 +1077,39 @@ __global__ void stage_vt_kernel(const float* __restrict__ V, int nc, int dv, con
 //   TF32 mode : [ x (d) | aug (3) | 0 ... ]                       A-role aug = 1,1,1 ; B-role aug = bias split
 //   FP32 mode : A-role [ xh (d) | xh (d) | xl (d) | aug | 0 ...]   B-role [ yh | yl | yh | aug | 0 ... ]
 // so that sum_k A_k B_k = xh.yh + xh.yl + xl.yh + bias  (the dropped xl.yl term is ~2^-22 relative).
-// Label cost: the d_real coordinates are followed by 3V "virtual features" per point, so that the table
-// lookup becomes part of the same contraction: in the row role a point of label l carries (1,1,1) in the
-// three features of class l and zeros elsewhere; in the column role it carries, for every class v, the
-// three-piece TF32 split of w_coef * W[.,.] between v and its own label (exact in fp32). d = d_real + 3V.
+// Label cost: the coordinate columns are followed by 3V label columns per point, so that the table lookup
+// becomes part of the same contraction: in the row role a point of label l carries (1,1,1) in the three
+// columns of class l and zeros elsewhere; in the column role it carries, for every class v, the three-piece
+// TF32 split of w_coef * W[.,.] between v and its own label (exact in fp32, so the block is staged once in
+// either precision mode).
 __global__ void stage_kernel(const float* __restrict__ src, int rows, int rows_pad, int d, int kc, int kp, int prec,
-                             float* __restrict__ opA, float* __restrict__ opB, int d_real,
+                             float* __restrict__ opA, float* __restrict__ opB,
                              const int* __restrict__ labels, const float* __restrict__ W, int V, int cloud,
                              float w_coef) {
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t total = (size_t)rows_pad * kp;
   if (idx >= total) return;
   int r = (int)(idx / kp), k = (int)(idx % kp);
+  const int kcoord = (prec == 0) ? d : 3 * d;  // coordinate columns; [kcoord, kc) is the label block
   float va = 0.f, vb = 0.f;
-  if (k < kc) {
+  if (k < kcoord) {
     if (r < rows) {
       int part = k / d, c = k % d;
-      float xa, xb;  // value of this feature in the row role / in the column role
-      if (c < d_real) {
-        xa = xb = src[(size_t)r * d_real + c];
-      } else {
-        const int v = (c - d_real) / 3, piece = (c - d_real) % 3;
-        const int l = labels[r];
-        xa = (l == v) ? 1.f : 0.f;
-        // cloud 0 (x) as column: rows are y points of label v -> W[l, v]; cloud 1 (y) as column: W[v, l]
-        const float w = w_coef * W[cloud == 0 ? l * V + v : v * V + l];
-        const float h = to_tf32(w), mid = to_tf32(w - h), low = to_tf32(w - h - mid);
-        xb = piece == 0 ? h : (piece == 1 ? mid : low);
-      }
-      float ha = to_tf32(xa), la = to_tf32(xa - ha);
-      float hb = to_tf32(xb), lb = to_tf32(xb - hb);
-      if (prec == 0) { va = ha; vb = hb; }
-      else { va = (part == 2) ? la : ha; vb = (part == 1) ? lb : hb; }
+      float x = src[(size_t)r * d + c];
+      float hi = to_tf32(x);
+      float lo = to_tf32(x - hi);
+      if (prec == 0) { va = hi; vb = hi; }
+      else { va = (part == 2) ? lo : hi; vb = (part == 1) ? lo : hi; }
+    }
+  } else if (k < kc) {
+    if (r < rows) {
+      const int v = (k - kcoord) / 3, piece = (k - kcoord) % 3;
+      const int l = labels[r];
+      va = (l == v) ? 1.f : 0.f;
+      // cloud 0 (x) as column: rows are y points of label v -> W[l, v]; cloud 1 (y) as column: W[v, l]
+      const float w = w_coef * W[cloud == 0 ? l * V + v : v * V + l];
+      const float h = to_tf32(w), mid = to_tf32(w - h), low = to_tf32(w - h - mid);
+      vb = piece == 0 ? h : (piece == 1 ? mid : low);
     }
   } else if (k < kc + 3) {
     va = 1.f;
@@ -1170,9 +1171,10 @@ struct Shape {
   bool ok;
 };
 
-Shape plan_shape(int d, int prec) {
+// nlab = label-table columns (3 per class), staged once in either precision mode: their values are exact in TF32.
+Shape plan_shape(int d, int prec, int nlab = 0) {
   Shape s{};
-  s.kc = (prec == 0) ? d : 3 * d;
+  s.kc = ((prec == 0) ? d : 3 * d) + nlab;
   s.kp = (s.kc + 3 + 7) & ~7;  // + 3 bias columns, padded to whole K steps of 8
   s.nfull = s.kp / 32;
   s.ntail = (s.kp % 32) / 8;
@@ -1252,16 +1254,16 @@ int set_reserved_sms(int k) {
   return g_reserved_sms.exchange(k, std::memory_order_relaxed);
 }
 
-bool supported(int n, int m, int d, int prec) {
+bool supported(int n, int m, int d, int prec, int nlab) {
   if (prec != 0 && prec != 1) return false;
   if (n <= 0 || m <= 0 || d <= 0) return false;
-  return plan_shape(d, prec).ok;
+  return plan_shape(d, prec, nlab).ok;
 }
 
 static inline int pad256(int r) { return (r + 255) & ~255; }
 
-size_t staged_bytes(int n, int m, int d, int prec) {
-  Shape s = plan_shape(d, prec);
+size_t staged_bytes(int n, int m, int d, int prec, int nlab) {
+  Shape s = plan_shape(d, prec, nlab);
   if (!s.ok) return 0;
   size_t per_row = (size_t)s.kp * sizeof(float);
   size_t b = 0;
@@ -1275,11 +1277,9 @@ size_t staged_bytes(int n, int m, int d, int prec) {
 cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
                   cudaStream_t st, bool run_kernels, const LabelCost* lab, float w_coef) {
   const int V = (lab && lab->V > 0) ? lab->V : 0;
-  const int d_real = d;
-  d = d_real + 3 * V;  // the engine sees the label table as 3V extra features (see stage_kernel)
-  Shape sh = plan_shape(d, prec);
+  Shape sh = plan_shape(d, prec, 3 * V);  // the label table rides along as 3V extra columns (see stage_kernel)
   if (!sh.ok) return cudaErrorNotSupported;
-  s.d = d; s.kc = sh.kc; s.kp = sh.kp; s.prec = prec;
+  s.d = d; s.nlab = 3 * V; s.kc = sh.kc; s.kp = sh.kp; s.prec = prec;
   char* p = (char*)(((uintptr_t)buf + 1023) & ~(uintptr_t)1023);
   const float* src[2] = {x, y};
   const int rows[2] = {n, m};
@@ -1293,7 +1293,7 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
     size_t total = (size_t)o.rows_pad * sh.kp;
     if (run_kernels)
       stage_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src[c], o.rows, o.rows_pad, d, sh.kc, sh.kp, prec,
-                                                                    o.opA, o.opB, d_real, V ? lab->lab[c] : nullptr,
+                                                                    o.opA, o.opB, V ? lab->lab[c] : nullptr,
                                                                     V ? lab->W : nullptr, V, c, w_coef);
   }
   s.part_stride = pad256(n > m ? n : m);
@@ -1311,7 +1311,7 @@ namespace {
 // One streaming pass over the staged operands: LSE (out_idx == nullptr) or running arg-max of the raw scores.
 cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, int* out_idx,
                         cudaStream_t st) {
-  Shape sh = plan_shape(s.d, s.prec);
+  Shape sh = plan_shape(s.d, s.prec, s.nlab);
   if (!sh.ok) return cudaErrorNotSupported;
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
@@ -1379,9 +1379,9 @@ struct PvShape {
   bool split, ok;
 };
 
-PvShape plan_pv(int d, int prec, int dv) {
+PvShape plan_pv(int d, int prec, int dv, int nlab = 0) {
   PvShape s{};
-  Shape sh = plan_shape(d, prec);
+  Shape sh = plan_shape(d, prec, nlab);
   s.ok = false;
   if (!sh.ok || dv <= 0) return s;
   s.split = (prec == 1);
@@ -1419,18 +1419,20 @@ cudaError_t launch_pv(const CUtensorMap* maps, const PvKernelParams& kp, int gri
 
 }  // namespace
 
-bool pv_supported(int d, int prec, int dv) { return (prec == 0 || prec == 1) && plan_pv(d, prec, dv).ok; }
+bool pv_supported(int d, int prec, int dv, int nlab) {
+  return (prec == 0 || prec == 1) && plan_pv(d, prec, dv, nlab).ok;
+}
 
-size_t pv_scratch_bytes(int nc, int d, int prec, int dv) {
-  PvShape s = plan_pv(d, prec, dv);
+size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab) {
+  PvShape s = plan_pv(d, prec, dv, nlab);
   if (!s.ok) return 0;
   size_t one = (size_t)s.nslices * s.dv_pad * pad256(nc) * sizeof(float);
   return (s.split ? 2 : 1) * ((one + 1023) & ~size_t(1023)) + 1024;
 }
 
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa, char* scratch, cudaStream_t st) {
-  Shape sh = plan_shape(s.d, s.prec);
-  PvShape ps = plan_pv(s.d, s.prec, pa.dv);
+  Shape sh = plan_shape(s.d, s.prec, s.nlab);
+  PvShape ps = plan_pv(s.d, s.prec, pa.dv, s.nlab);
   if (!sh.ok || !ps.ok || pa.rows2) return cudaErrorNotSupported;
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];

@@ -20,7 +20,7 @@ struct CloudOps {
 
 struct Staged {
   CloudOps cloud[2];  // 0 = x, 1 = y
-  int d = 0, kc = 0, kp = 0, prec = 0;
+  int d = 0, nlab = 0, kc = 0, kp = 0, prec = 0;  // nlab: label-table columns staged after the coordinates
   float* part_m = nullptr;  // [pieces, part_stride] partial scaled maxima of row blocks shared by several CTAs
   float* part_s = nullptr;  // [pieces, part_stride] partial sums
   int part_stride = 0;
@@ -30,12 +30,12 @@ struct Staged {
 // Streaming passes leave `k` SMs unused from now on (process-wide; returns the previous value).
 int set_reserved_sms(int k);
 
-bool supported(int n, int m, int d, int prec);
-size_t staged_bytes(int n, int m, int d, int prec);
+bool supported(int n, int m, int d, int prec, int nlab = 0);
+size_t staged_bytes(int n, int m, int d, int prec, int nlab = 0);
 // run_kernels = false only lays out the pointers inside `buf` (operands staged there by an earlier call
 // with the same sizes are re-used: row-sharded solvers stage once and step many times).
 // With a label cost (lab->V > 0) the operands get 3V extra columns that carry w_coef * W[label, label']
-// through the contraction; every size query for such a problem must then use d + 3V as the feature count.
+// through the contraction; every size query for such a problem must then pass nlab = 3V.
 cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, int m, int d, int prec,
                   cudaStream_t st, bool run_kernels = true, const LabelCost* lab = nullptr, float w_coef = 0.f);
 // One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
@@ -47,8 +47,8 @@ cudaError_t argmax(const Staged& s, int side, const StreamArgs& a, float* out_va
 
 // Plan-times-matrix pass on the tensor cores (same staged operands, hence bit-identical scores
 // to the LSE passes). `scratch` holds the transposed, TF32-split copy of V (pv_scratch_bytes).
-bool pv_supported(int d, int prec, int dv);
-size_t pv_scratch_bytes(int nc, int d, int prec, int dv);
+bool pv_supported(int d, int prec, int dv, int nlab = 0);
+size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab = 0);
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, char* scratch, cudaStream_t st);
 
 // Value of the device-global error word (non-zero once a bounded wait gave up); synchronises.

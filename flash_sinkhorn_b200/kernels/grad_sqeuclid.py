@@ -89,7 +89,7 @@ def sinkhorn_geomloss_online_grad_sqeuclid(
                             bool(compute_grad_x), bool(compute_grad_y), process_group)
     gx = torch.empty((n, d), device=dev, dtype=torch.float32) if compute_grad_x else None
     gy = torch.empty((m, d), device=dev, dtype=torch.float32) if compute_grad_y else None
-    ws = _lib.workspace(_lib.OP_GRAD, n, m, d + (3 * labels.V if labels else 0), prec, dev)
+    ws = _lib.workspace(_lib.OP_GRAD, n, m, d, prec, dev, labels.V if labels else 0)
     _lib.call(
         "fs_grad", dev,
         _lib.ptr(x32), _lib.ptr(y32), n, m, d,

@@ -168,7 +168,7 @@ def flashsinkhorn_symmetric_step(
     prec = _lib.precision_id(allow_tf32)
     f_out = torch.empty((n,), device=dev, dtype=torch.float32)
     g_out = torch.empty((m,), device=dev, dtype=torch.float32)
-    ws = _lib.workspace(_lib.OP_STEP, n, m, d + (3 * labels.V if labels else 0), prec, dev)
+    ws = _lib.workspace(_lib.OP_STEP, n, m, d, prec, dev, labels.V if labels else 0)
     _lib.call(
         "fs_symmetric_step", dev,
         _lib.ptr(x32), _lib.ptr(y32), n, m, d,

@@ -260,7 +260,7 @@ def sinkhorn_flashstyle_symmetric(
     f_pre = torch.empty((n,), device=dev, dtype=torch.float32) if want_pre else None
     g_pre = torch.empty((m,), device=dev, dtype=torch.float32) if want_pre else None
     iters = torch.zeros((1,), device=dev, dtype=torch.int32) if return_n_iters else None
-    ws = _lib.workspace(_lib.OP_SOLVE_SYMMETRIC, n, m, d + (3 * labels.V if labels else 0), prec, dev)
+    ws = _lib.workspace(_lib.OP_SOLVE_SYMMETRIC, n, m, d, prec, dev, labels.V if labels else 0)
     eps_arr = _eps_array(eps_list)
     _lib.call(
         "fs_solve_symmetric", dev,

@@ -101,7 +101,7 @@ int fs_set_reserved_sms(int k);
  * and kernels/sinkhorn_triton_grad_sqeuclid.py:225-236: the logit of entry (i, j) becomes
  *   (lambda_x * 2cs * x_i.y_j - lambda_y * cs * W[label_x_i, label_y_j]) / eps + bias_j.
  * A NULL pointer, V <= 0 or lambda_y == 0 means the plain squared-Euclidean cost. Entry points that take
- * this descriptor size their workspace with d + 3*V in place of d (the tensor-core engine carries the
+ * this descriptor size their workspace with fs_workspace_bytes_labels (the tensor-core engine carries the
  * table through the contraction as 3V extra operand columns). All pointers are device pointers. */
 typedef struct fs_label_cost {
   const int* label_x;    /* [n] class of every x point, in [0, V) */
@@ -114,6 +114,8 @@ typedef struct fs_label_cost {
 
 /* Scratch bytes needed by `op` (one of FS_OP_*) at these sizes. */
 size_t fs_workspace_bytes(int op, int n, int m, int d, int prec);
+/* The same for a call that passes an fs_label_cost with V = n_classes (0 = none). */
+size_t fs_workspace_bytes_labels(int op, int n, int m, int d, int prec, int n_classes);
 
 /* Row log-sum-exp potential update.
  *   out_i = -eps*damping * log sum_j exp( (2cs/eps) x_i.y_j + bias_j )

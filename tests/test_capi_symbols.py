@@ -55,7 +55,7 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
 def test_label_cost_descriptor_validation_and_workspace():
     """Host logic of the label-cost arguments (no GPU): the reference's activation rule and errors
     (kernels/sinkhorn_flashstyle_sqeuclid.py:1183-1208), the ctypes mirror of fs_label_cost, and the
-    workspace rule d -> d + 3V."""
+    class-count argument of the workspace query."""
     import torch
     from flash_sinkhorn_b200 import _lib
     cpu = torch.device("cpu")
@@ -73,6 +73,9 @@ def test_label_cost_descriptor_validation_and_workspace():
             mk(**bad)
     lib = _lib.load()
     plain = lib.fs_workspace_bytes(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_TF32)
-    labelled = lib.fs_workspace_bytes(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64 + 3 * 10, _lib.PREC_TF32)
-    assert labelled > plain
+    labelled = lib.fs_workspace_bytes_labels(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_TF32, 10)
+    assert labelled > plain == lib.fs_workspace_bytes_labels(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_TF32, 0)
+    # exact-fp32 mode: the label block is staged once (K = 3*64 + 3*5 + 3), so this stays on the tensor-core engine
+    exact = lib.fs_workspace_bytes_labels(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_FP32, 5)
+    assert exact > lib.fs_workspace_bytes(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_SIMT)
     assert lib.fs_set_reserved_sms(3) == 0 and lib.fs_set_reserved_sms(0) == 3
