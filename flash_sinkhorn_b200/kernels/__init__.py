@@ -22,6 +22,11 @@ __all__ = [
 
 _LAZY = {
     "log_weights": "flash_sinkhorn_b200.kernels._common",
+    "apply_lse_kernel_sqeuclid": "flash_sinkhorn_b200.kernels.sinkhorn_triton_ott_sqeuclid",
+    "apply_transport_from_potentials_sqeuclid": "flash_sinkhorn_b200.kernels.sinkhorn_triton_ott_sqeuclid",
+    "update_potential": "flash_sinkhorn_b200.kernels.sinkhorn_triton_ott_sqeuclid",
+    "apply_plan_vec_sqeuclid": "flash_sinkhorn_b200.kernels.apply_ott",
+    "apply_plan_mat_sqeuclid": "flash_sinkhorn_b200.kernels.apply_ott",
     "mat5_sqeuclid": "flash_sinkhorn_b200.kernels.apply_ott",
     "precompute_flashsinkhorn_inputs": "flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid",
     "compute_bias_f": "flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid",

@@ -260,6 +260,51 @@ def plan_ott(x, y, f, g, eps, cost_scale=1.0):
     return np.exp((f[:, None] + g[None, :] - C) / eps)
 
 
+def signed_lse_ott(x, y, f, g, eps, axis, vec=None):
+    """testing/reference_sinkhorn.py:12-62 and kernels/sinkhorn_triton_ott_sqeuclid.py:157-286, :482-690:
+    eps*log|sum exp((f_i+g_j-C_ij)/eps)*vec| minus the potential of the kept index (non-finite ones count as 0),
+    and the sign of the sum (all ones without vec; a zero sum gives -inf, sign 0). Cost is |x-y|^2."""
+    C = sqnorm(x)[:, None] + sqnorm(y)[None, :] - 2.0 * (x @ y.T)
+    logits = (f[:, None] + g[None, :] - C) / eps
+    own = f if axis == 1 else g
+    own = np.where(np.isfinite(own), own, 0.0)
+    if vec is None:
+        lse = _lse(logits, axis=axis)
+        return eps * lse - own, np.ones_like(lse)
+    with np.errstate(divide="ignore"):
+        logv = np.where(vec != 0, np.log(np.abs(vec)), -np.inf)
+    vals = logits + (logv[None, :] if axis == 1 else logv[:, None])
+    sg = np.sign(vec)
+    top = vals.max(axis=axis, keepdims=True)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        # an all-zero vec makes every term exp(-inf - (-inf)) = NaN; the comparisons below are then all
+        # False, which is how the reference ends up with (-inf, 0) for such rows
+        s = np.sum((sg[None, :] if axis == 1 else sg[:, None]) * np.exp(vals - top), axis=axis)
+        lse = np.where(np.abs(s) > 0, np.squeeze(top, axis=axis) + np.log(np.abs(s)), -np.inf)
+    return eps * lse - own, np.where(s > 0, 1.0, np.where(s < 0, -1.0, 0.0))
+
+
+def update_potential_ott(x, y, f, g, log_marginal, eps, axis):
+    """testing/reference_sinkhorn.py:65-68, kernels/sinkhorn_triton_ott_sqeuclid.py:693-709."""
+    lse, _ = signed_lse_ott(x, y, f, g, eps, axis)
+    return eps * log_marginal - np.where(np.isfinite(lse), lse, 0.0)
+
+
+def sinkhorn_potentials_ott(x, y, loga, logb, eps, n_iters):
+    """testing/reference_sinkhorn.py:71-82: zero start, g-update then f-update, log-marginals absorbed."""
+    f, g = np.zeros(x.shape[0], x.dtype), np.zeros(y.shape[0], y.dtype)
+    for _ in range(n_iters):
+        g = update_potential_ott(x, y, f, g, logb, eps, axis=0)
+        f = update_potential_ott(x, y, f, g, loga, eps, axis=1)
+    return f, g
+
+
+def apply_transport_ott(x, y, f, g, vec, eps, axis):
+    """testing/reference_sinkhorn.py:85-89, kernels/sinkhorn_triton_ott_sqeuclid.py:712-735: P vec or P^T vec."""
+    lse, sg = signed_lse_ott(x, y, f, g, eps, axis, vec=vec)
+    return sg * np.exp((lse + (f if axis == 1 else g)) / eps)
+
+
 def mat5(x, y, f_ott, g_ott, A, eps, cost_scale=1.0):
     """kernels/apply_ott.py:35-168: (-4cs/eps) sum_j P_ij (A_i.y_j) y_j."""
     P = plan_ott(x, y, f_ott, g_ott, eps, cost_scale)

@@ -349,6 +349,96 @@ def gen_c_transform():
     save("c_transform_small", **out)
 
 
+def gen_legacy():
+    """OTT-convention legacy surface: the signed log-sum-exp kernels of kernels/sinkhorn_triton_ott_sqeuclid.py
+    (interpreter run, manual blocks) next to the dense functions of testing/reference_sinkhorn.py:12-89 that the
+    reference's test_sinkhorn_triton.py compares them with; the deprecated OTT-convention plan applications of
+    kernels/apply_ott.py:213-450; the deprecated solver facade; and the trust-region CG of cg.py:201-369."""
+    import warnings
+
+    from flash_sinkhorn.cg import steihaug_cg
+    from flash_sinkhorn.kernels.apply_ott import apply_plan_mat_sqeuclid, apply_plan_vec_sqeuclid
+    from flash_sinkhorn.kernels.sinkhorn_triton_ott_sqeuclid import (
+        apply_lse_kernel_sqeuclid,
+        apply_transport_from_potentials_sqeuclid,
+        sinkhorn_potentials_sqeuclid,
+        update_potential,
+    )
+
+    warnings.simplefilter("ignore", DeprecationWarning)
+    man = dict(block_m=32, block_n=32, block_k=16)
+    n, m, d, eps = 37, 29, 8, 0.5
+    gen = torch.Generator().manual_seed(91)
+    x, y = torch.randn(n, d, generator=gen), 0.2 + torch.randn(m, d, generator=gen)
+    f, g = torch.randn(n, generator=gen), torch.randn(m, generator=gen)
+    vec_m, vec_n = torch.randn(m, generator=gen), torch.randn(n, generator=gen)
+    vec_m[3], vec_n[5] = 0.0, 0.0
+    out = dict(x=np32(x), y=np32(y), f=np32(f), g=np32(g), vec_m=np32(vec_m), vec_n=np32(vec_n), eps=np.float64(eps))
+    for axis, vec in ((1, vec_m), (0, vec_n)):
+        o, s = apply_lse_kernel_sqeuclid(x, y, f, g, eps, axis, **man)
+        out[f"lse_axis{axis}"], out[f"lse_sgn_axis{axis}"] = np32(o), np32(s)
+        o, s = apply_lse_kernel_sqeuclid(x, y, f, g, eps, axis, vec=vec, **man)
+        out[f"vlse_axis{axis}"], out[f"vlse_sgn_axis{axis}"] = np32(o), np32(s)
+        o, s = reference_sinkhorn.apply_lse_kernel_ref(x, y, f, g, eps, axis, vec=vec)
+        out[f"vlse_dense_axis{axis}"], out[f"vlse_dense_sgn_axis{axis}"] = np32(o), np32(s)
+    # all-positive and all-zero weight vectors: the sign is +1 everywhere, resp. 0 with -inf values
+    o, s = apply_lse_kernel_sqeuclid(x, y, f, g, eps, 1, vec=torch.zeros(m), **man)
+    out["zero_vec_lse"], out["zero_vec_sgn"] = np32(o), np32(s)
+
+    loga = torch.log_softmax(torch.randn(n, generator=gen), 0)
+    logb = torch.log_softmax(torch.randn(m, generator=gen), 0)
+    out["loga"], out["logb"] = np32(loga), np32(logb)
+    out["update_g"] = np32(update_potential(x, y, f, g, logb, eps, axis=0, **man))
+    out["update_f"] = np32(update_potential(x, y, f, g, loga, eps, axis=1, **man))
+    out["update_g_dense"] = np32(reference_sinkhorn.update_potential_ref(x, y, f, g, logb, eps, axis=0))
+
+    fo, go = reference_sinkhorn.sinkhorn_potentials_ref(x, y, loga, logb, eps, n_iters=6)
+    out["ott_f_dense"], out["ott_g_dense"] = np32(fo), np32(go)
+    ff, gf = sinkhorn_potentials_sqeuclid(x, y, loga, logb, eps, 6, autotune=False)
+    out["ott_f_facade"], out["ott_g_facade"] = np32(ff), np32(gf)
+    out["transport_axis1"] = np32(apply_transport_from_potentials_sqeuclid(x, y, fo, go, vec_m, eps, 1, **man))
+    out["transport_axis0"] = np32(apply_transport_from_potentials_sqeuclid(x, y, fo, go, vec_n, eps, 0, **man))
+    out["transport_dense_axis1"] = np32(
+        reference_sinkhorn.apply_transport_from_potentials_ref(x, y, fo, go, vec_m, eps, 1))
+
+    cs = 0.5
+    fh, gh = reference_sinkhorn.sinkhorn_potentials_ref(
+        x * math.sqrt(cs), y * math.sqrt(cs), loga, logb, eps, n_iters=6)  # OTT potentials for cost cs*|x-y|^2
+    mat_m, mat_n = torch.randn(m, d, generator=gen), torch.randn(n, d, generator=gen)
+    scale = torch.rand(m, generator=gen) + 0.5
+    out.update(cs=np.float64(cs), cs_f=np32(fh), cs_g=np32(gh), mat_m=np32(mat_m), mat_n=np32(mat_n),
+               scale=np32(scale))
+    out["dep_vec_axis1"] = np32(apply_plan_vec_sqeuclid(x, y, fh, gh, vec_m, eps=eps, axis=1, cost_scale=cs,
+                                                        log_a=loga, log_b=logb))
+    out["dep_vec_axis0"] = np32(apply_plan_vec_sqeuclid(x, y, fh, gh, vec_n, eps=eps, axis=0, cost_scale=cs))
+    out["dep_mat_axis1"] = np32(apply_plan_mat_sqeuclid(x, y, fh, gh, mat_m, eps=eps, axis=1, cost_scale=cs,
+                                                        scale=scale, log_a=loga, log_b=logb, autotune=False,
+                                                        block_d=16, **man))
+    out["dep_mat_axis0"] = np32(apply_plan_mat_sqeuclid(x, y, fh, gh, mat_n, eps=eps, axis=0, cost_scale=cs,
+                                                        autotune=False, block_d=16, **man))
+    save("legacy_ott_small", **out)
+
+    # Trust-region CG on small dense symmetric matrices (float64), one case per way of stopping.
+    cases = {}
+    for name, (shift, delta, max_iter, rtol) in {
+        "interior": (0.5, 50.0, 100, 1e-3), "boundary": (0.5, 0.3, 100, 1e-6), "negcurv": (-1.4, 1.0, 100, 1e-6),
+        "maxiter": (0.5, 50.0, 2, 1e-6),
+    }.items():
+        gen = torch.Generator().manual_seed(17)
+        B = torch.randn(30, 30, generator=gen, dtype=torch.float64)
+        H = B @ B.T / 30 + shift * torch.eye(30, dtype=torch.float64)
+        gr = torch.randn(30, generator=gen, dtype=torch.float64)
+        p, info = steihaug_cg(lambda v: H @ v, gr, delta, max_iter=max_iter, rtol=rtol, atol=1e-12)
+        print("steihaug", name, info)
+        cases.update({f"{name}_H": H.numpy(), f"{name}_g": gr.numpy(), f"{name}_p": p.numpy(),
+                      f"{name}_args": np.array([delta, max_iter, rtol], np.float64),
+                      f"{name}_reason": np.array(info.termination_reason),
+                      f"{name}_info": np.array([info.converged, info.iters, info.residual, info.hit_boundary,
+                                                info.negative_curvature_detected, info.predicted_reduction],
+                                               np.float64)})
+    save("steihaug_small", **cases)
+
+
 def gen_dense_reference():
     """The reference's dense oracles alone (no Triton): symmetric potentials, OTT alternating, gradients."""
     n, m, d = 128, 96, 32
@@ -406,10 +496,10 @@ def gen_config1():
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--skip-c1", action="store_true", help="skip the 4096x4096 dense solves (several minutes)")
-    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,labels,dense,c1")
+    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,labels,legacy,dense,c1")
     args = ap.parse_args()
     which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "implicit",
-                                                         "ctransform", "labels", "dense", "c1"}
+                                                         "ctransform", "labels", "legacy", "dense", "c1"}
     print("reference version", flash_sinkhorn.__version__, "from", os.path.dirname(flash_sinkhorn.__file__))
     if "dense" in which:
         gen_dense_reference()
@@ -427,6 +517,8 @@ if __name__ == "__main__":
         gen_c_transform()
     if "labels" in which:
         gen_label_cost()
+    if "legacy" in which:
+        gen_legacy()
     if "c1" in which and not args.skip_c1:
         gen_config1()
     sys.exit(0)

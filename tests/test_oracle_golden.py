@@ -240,3 +240,46 @@ def test_label_cost(name):
         want = float(z[f"{name}_loss_{tag}"])
         assert abs(r["loss"] - want) < 2e-5 * max(1.0, abs(want)), (debias, r["loss"], want)
         assert rel_err(r["grad_x"], z[f"{name}_loss_{tag}_grad_x"]) < 2e-4
+
+
+def test_legacy_ott_surface():
+    """Signed log-sum-exp, OTT-convention half-steps, solve and plan applications: the oracle against the
+    reference's Triton kernels (interpreter) and against its dense functions."""
+    z = load_golden("legacy_ott_small")
+    x, y, f, g, vm, vn = d64(z, "x", "y", "f", "g", "vec_m", "vec_n")
+    eps = float(z["eps"])
+    for axis, vec in ((1, vm), (0, vn)):
+        out, sgn = O.signed_lse_ott(x, y, f, g, eps, axis)
+        assert rel_err(out, z[f"lse_axis{axis}"]) < 2e-5 and np.all(sgn == 1.0)
+        assert np.all(z[f"lse_sgn_axis{axis}"] == 1.0)
+        out, sgn = O.signed_lse_ott(x, y, f, g, eps, axis, vec=vec)
+        # log|sum| is ill-conditioned where positive and negative parts nearly cancel: absolute tolerance
+        assert np.abs(out - z[f"vlse_axis{axis}"]).max() < 5e-4
+        assert np.abs(out - z[f"vlse_dense_axis{axis}"]).max() < 5e-4
+        assert np.array_equal(sgn, z[f"vlse_sgn_axis{axis}"]) and np.array_equal(sgn, z[f"vlse_dense_sgn_axis{axis}"])
+    out, sgn = O.signed_lse_ott(x, y, f, g, eps, 1, vec=np.zeros_like(vm))
+    assert np.all(np.isneginf(out)) and np.all(sgn == 0)
+    assert np.all(np.isneginf(z["zero_vec_lse"])) and np.all(z["zero_vec_sgn"] == 0)
+
+    la, lb = d64(z, "loga", "logb")
+    assert rel_err(O.update_potential_ott(x, y, f, g, lb, eps, 0), z["update_g"]) < 2e-5
+    assert rel_err(O.update_potential_ott(x, y, f, g, lb, eps, 0), z["update_g_dense"]) < 2e-5
+    assert rel_err(O.update_potential_ott(x, y, f, g, la, eps, 1), z["update_f"]) < 2e-5
+    fo, go = O.sinkhorn_potentials_ott(x, y, la, lb, eps, 6)
+    assert rel_err(fo, z["ott_f_dense"]) < 2e-5 and rel_err(go, z["ott_g_dense"]) < 2e-5
+    assert rel_err(fo, z["ott_f_facade"]) < 2e-5 and rel_err(go, z["ott_g_facade"]) < 2e-5
+    # the facade is the alternating solver in OTT convention
+    alt = O.solve_alternating(x, y, np.exp(la), np.exp(lb), [eps], 6, ott_convention=True)
+    assert rel_err(alt["f"], z["ott_f_facade"]) < 2e-5 and rel_err(alt["g"], z["ott_g_facade"]) < 2e-5
+    assert rel_err(O.apply_transport_ott(x, y, fo, go, vm, eps, 1), z["transport_axis1"]) < 1e-4
+    assert rel_err(O.apply_transport_ott(x, y, fo, go, vm, eps, 1), z["transport_dense_axis1"]) < 1e-4
+    assert rel_err(O.apply_transport_ott(x, y, fo, go, vn, eps, 0), z["transport_axis0"]) < 1e-4
+
+    # deprecated OTT-convention plan applications == products with the dense OTT plan
+    cs = float(z["cs"])
+    fh, gh, mm, mn, sc = d64(z, "cs_f", "cs_g", "mat_m", "mat_n", "scale")
+    P = O.plan_ott(x, y, fh, gh, eps, cs)
+    assert rel_err(P @ vm, z["dep_vec_axis1"]) < 1e-4
+    assert rel_err(P.T @ vn, z["dep_vec_axis0"]) < 1e-4
+    assert rel_err(P @ (mm * sc[:, None]), z["dep_mat_axis1"]) < 1e-4
+    assert rel_err(P.T @ mn, z["dep_mat_axis0"]) < 1e-4
