@@ -439,6 +439,53 @@ def gen_legacy():
     save("steihaug_small", **cases)
 
 
+def gen_signatures():
+    """Parameter names, kinds and defaults of every public callable of the reference's import surface, as
+    JSON (tests/test_import_surface.py compares the package's own signatures with it)."""
+    import importlib
+    import inspect
+    import json
+    import warnings
+
+    surface = {
+        "samples_loss": ["SamplesLoss"],
+        "cg": ["conjugate_gradient", "steihaug_cg"],
+        "hvp": ["geomloss_to_ott_potentials", "hvp_x_sqeuclid", "hvp_x_sqeuclid_from_potentials",
+                "inverse_hvp_x_sqeuclid_from_potentials"],
+        "implicit_grad": ["implicit_grad_x", "implicit_grad_x_from_potentials"],
+        "c_transform": ["c_transform_fwd", "c_transform_cost"],
+        "sinkhorn_solvers": ["sinkhorn_flashstyle_alternating", "sinkhorn_flashstyle_symmetric"],
+        "kernels._common": ["dampening", "log_weights", "max_diameter", "epsilon_schedule"],
+        "kernels.sinkhorn_flashstyle_sqeuclid": [
+            "flashsinkhorn_lse", "flashsinkhorn_lse_fused", "flashsinkhorn_symmetric_step",
+            "precompute_flashsinkhorn_inputs", "compute_bias_f", "compute_bias_g",
+            "shifted_to_standard_potentials", "standard_to_shifted_potentials"],
+        "kernels.apply_flash": ["apply_plan_vec_flashstyle", "apply_plan_mat_flashstyle"],
+        "kernels.apply_ott": ["mat5_sqeuclid", "apply_plan_vec_sqeuclid", "apply_plan_mat_sqeuclid"],
+        "kernels.sinkhorn_triton_grad_sqeuclid": ["sinkhorn_geomloss_online_grad_sqeuclid"],
+        "kernels.c_transform_sqeuclid": ["c_transform_kernel"],
+        "kernels.sinkhorn_triton_ott_sqeuclid": ["sinkhorn_potentials_sqeuclid", "apply_lse_kernel_sqeuclid",
+                                                 "update_potential", "apply_transport_from_potentials_sqeuclid"],
+        "kernels.sinkhorn_triton_geomloss_sqeuclid": ["sinkhorn_geomloss_online_potentials_sqeuclid",
+                                                      "geomloss_to_ott_potentials", "ott_to_geomloss_potentials"],
+    }
+    table = {}
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        for module, names in surface.items():
+            mod = importlib.import_module("flash_sinkhorn." + module)
+            for name in names:
+                obj = getattr(mod, name)
+                fn = obj.__init__ if inspect.isclass(obj) else obj
+                table[f"{module}:{name}"] = [
+                    [p.name, p.kind.name, None if p.default is inspect.Parameter.empty else repr(p.default)]
+                    for p in inspect.signature(fn).parameters.values() if p.name != "self"]
+    path = os.path.join(HERE, "api_signatures.json")
+    with open(path, "w") as fh:
+        json.dump(table, fh, sort_keys=True, separators=(",", ":"))
+    print(f"wrote {path} ({os.path.getsize(path)} bytes, {len(table)} callables)")
+
+
 def gen_dense_reference():
     """The reference's dense oracles alone (no Triton): symmetric potentials, OTT alternating, gradients."""
     n, m, d = 128, 96, 32
@@ -496,10 +543,10 @@ def gen_config1():
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--skip-c1", action="store_true", help="skip the 4096x4096 dense solves (several minutes)")
-    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,labels,legacy,dense,c1")
+    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,labels,legacy,signatures,dense,c1")
     args = ap.parse_args()
     which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "implicit",
-                                                         "ctransform", "labels", "legacy", "dense", "c1"}
+                                                         "ctransform", "labels", "legacy", "signatures", "dense", "c1"}
     print("reference version", flash_sinkhorn.__version__, "from", os.path.dirname(flash_sinkhorn.__file__))
     if "dense" in which:
         gen_dense_reference()
@@ -519,6 +566,8 @@ if __name__ == "__main__":
         gen_label_cost()
     if "legacy" in which:
         gen_legacy()
+    if "signatures" in which:
+        gen_signatures()
     if "c1" in which and not args.skip_c1:
         gen_config1()
     sys.exit(0)

@@ -81,3 +81,42 @@ def test_retired_kernel_entry_points_raise():
     mod = importlib.import_module(PKG + ".kernels.sinkhorn_triton_geomloss_sqeuclid")
     with pytest.raises(NotImplementedError):
         mod._geomloss_symmetric_step_sqeuclid()
+
+
+def _signature_cases():
+    import json
+    import os
+
+    from conftest import GOLDEN_DIR
+    with open(os.path.join(GOLDEN_DIR, "api_signatures.json")) as fh:
+        return sorted(json.load(fh).items())
+
+
+@pytest.mark.parametrize("key,params", _signature_cases(), ids=[k for k, _ in _signature_cases()])
+def test_signatures_match_reference(key, params):
+    """Every parameter of the reference's callable exists here with the same kind and default, positional
+    parameters in the same order; anything added here is optional. A callable that takes ``**kwargs`` may
+    absorb keyword-only parameters it forwards untouched."""
+    import inspect
+
+    module, name = key.split(":")
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", DeprecationWarning)
+        obj = getattr(importlib.import_module(f"{PKG}.{module}"), name)
+    fn = obj.__init__ if inspect.isclass(obj) else obj
+    own = {p.name: p for p in inspect.signature(fn).parameters.values() if p.name != "self"}
+    absorbs = any(p.kind is p.VAR_KEYWORD for p in own.values())
+    for pname, kind, default in params:
+        if pname not in own:
+            assert absorbs and kind in ("KEYWORD_ONLY", "VAR_KEYWORD"), f"{key}: parameter {pname} missing"
+            continue
+        assert own[pname].kind.name == kind, f"{key}: {pname} is {own[pname].kind.name}, reference {kind}"
+        have = None if own[pname].default is inspect.Parameter.empty else repr(own[pname].default)
+        assert have == default, f"{key}: default of {pname} is {have}, reference {default}"
+    positional = [p for p, kind, _ in params if kind == "POSITIONAL_OR_KEYWORD"]
+    own_positional = [p.name for p in own.values() if p.kind is p.POSITIONAL_OR_KEYWORD]
+    assert own_positional[:len(positional)] == positional, key
+    known = {p for p, _, _ in params}
+    for pname, p in own.items():
+        if pname not in known and p.kind not in (p.VAR_KEYWORD, p.VAR_POSITIONAL):
+            assert p.default is not inspect.Parameter.empty, f"{key}: extra parameter {pname} must be optional"
