@@ -1257,6 +1257,12 @@ int set_reserved_sms(int k) {
 bool supported(int n, int m, int d, int prec, int nlab) {
   if (prec != 0 && prec != 1) return false;
   if (n <= 0 || m <= 0 || d <= 0) return false;
+  // The streaming kernel numbers its (row block, column tile) items with 32-bit integers: with 128-row
+  // blocks and 64-column tiles (the smallest it uses) both orientations must stay below 2^31 items,
+  // i.e. n*m below about 1.7e13. Larger problems go to the CUDA-core engine, which has no such product.
+  const long long blocks_n = ((long long)n + 127) / 128, blocks_m = ((long long)m + 127) / 128;
+  const long long tiles_n = ((long long)n + 63) / 64, tiles_m = ((long long)m + 63) / 64;
+  if (blocks_n * tiles_m >= (1ll << 31) || blocks_m * tiles_n >= (1ll << 31)) return false;
   return plan_shape(d, prec, nlab).ok;
 }
 

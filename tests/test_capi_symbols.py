@@ -79,3 +79,23 @@ def test_label_cost_descriptor_validation_and_workspace():
     exact = lib.fs_workspace_bytes_labels(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_FP32, 5)
     assert exact > lib.fs_workspace_bytes(_lib.OP_SOLVE_SYMMETRIC, 5000, 4000, 64, _lib.PREC_SIMT)
     assert lib.fs_set_reserved_sms(3) == 0 and lib.fs_set_reserved_sms(0) == 3
+
+
+def test_workspace_sizes_at_the_largest_shapes():
+    """Host-side size logic only. The tcgen05 kernel numbers its (row block, column tile) items with 32-bit
+    integers, so problems with about 1.7e13 entries or more must be planned for the CUDA-core engine (no staged
+    operands: a far smaller workspace); sizes must never wrap around 2^32 or come out zero."""
+    from flash_sinkhorn_b200 import _lib
+    lib = _lib.load()
+    big = lib.fs_workspace_bytes(_lib.OP_LSE, 4_000_000, 4_000_000, 64, _lib.PREC_TF32)
+    over = lib.fs_workspace_bytes(_lib.OP_LSE, 4_300_000, 4_300_000, 64, _lib.PREC_TF32)
+    assert big > 2 * 4_000_000 * 64 * 4  # staged operands of both clouds
+    assert 0 < over < big // 10  # one vector of scratch, no staging
+    # a long thin problem stays on the tensor-core engine whichever side is long
+    for n, m in ((16_000_000, 1000), (1000, 16_000_000)):
+        assert lib.fs_workspace_bytes(_lib.OP_LSE, n, m, 64, _lib.PREC_TF32) > 16_000_000 * 64 * 4
+    # config 3 of the benchmark list (1e6 x 1e6, d = 3) and config 5 (d = 2048) have non-zero plans in every op
+    for op in range(9):
+        assert lib.fs_workspace_bytes(op, 1_000_000, 1_000_000, 3, _lib.PREC_TF32) > 0
+        assert lib.fs_workspace_bytes(op, 16384, 16384, 2048, _lib.PREC_FP32) > 0
+    assert lib.fs_workspace_bytes(_lib.OP_LSE, 0, 5, 3, 0) == 0 and lib.fs_workspace_bytes(_lib.OP_LSE, 5, 5, 0, 0) == 0
