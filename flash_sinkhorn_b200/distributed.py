@@ -1,4 +1,4 @@
-"""Row-sharded (multi-GPU) symmetric Sinkhorn: one process per GPU, ``torch.distributed`` collectives.
+"""Row-sharded (multi-GPU) Sinkhorn solves: one process per GPU, ``torch.distributed`` collectives.
 
 The reference package is single-GPU. Here every rank holds the full clouds, weights and potentials
 (they are O((n+m) d)); the n x m work of every step is split by rows: rank r produces rows
@@ -8,8 +8,10 @@ Because every rank then holds identical full vectors, early-stop decisions are i
 without a further collective, and results are bit-identical to the single-GPU engine (same kernels,
 same per-row arithmetic).
 
-The loop itself (:func:`run_symmetric_sharded`) is engine-agnostic - it gets the step and the gather
-as callables - so it is unit-tested on CPU with ``gloo`` and a dense CPU step function.
+The loops themselves (:func:`run_symmetric_sharded`, :func:`run_alternating_sharded`) are engine-agnostic -
+they get the step and the gather as callables - so they are unit-tested on CPU with ``gloo`` and a dense
+CPU step function. The alternating (Gauss-Seidel) solver shards the same way, with one all-gather after
+every half-step.
 """
 from __future__ import annotations
 
@@ -257,6 +259,117 @@ def symmetric_solve_sharded(x, y, log_a, log_b, eps_list, *, group, **kw):
     """CUDA engine behind :func:`run_symmetric_sharded`. Returns standard potentials like the 1-GPU solver."""
     return symmetric_solve_sharded_many([dict(x=x, y=y, log_a=log_a, log_b=log_b, eps_list=eps_list, **kw)],
                                         group=group)[0]
+
+
+def run_alternating_sharded(
+    n: int,
+    m: int,
+    f_hat0: torch.Tensor,
+    g_hat0: torch.Tensor,
+    eps_list: Sequence[float],
+    iters_per_eps: int,
+    *,
+    ott_convention: bool,
+    threshold: Optional[float],
+    check_every: int,
+    world: int,
+    rank: int,
+    half_fn: Callable,
+    gather_fn: Callable,
+):
+    """Row-sharded Gauss-Seidel (alternating) schedule: every half-step needs the COMPLETE result of the
+    previous one, so each is followed by its all-gather before the next starts (nothing to overlap inside
+    one problem; the n x m work of each half is still split ``world`` ways).
+
+    ``half_fn(side, f_cur, g_cur, out, eps, (lo, hi))`` must fill rows ``[lo, hi)`` of ``out`` with the new
+    potential of ``side`` ("f": from ``g_cur``; "g": from ``f_cur``), ``out`` never aliasing the inputs.
+    GeomLoss convention runs f then g, the OTT convention g then f (reference sinkhorn_solvers.py:188-259).
+    ``eps_list`` x ``iters_per_eps`` is the annealed form (one stage = the reference's fixed-eps loop).
+    Early stop as in the reference (:264-270): every ``check_every`` iterations, against the potentials of
+    the previous check (the initial ones at first); identical on all ranks since the vectors are.
+    Returns ``(f_hat, g_hat, iterations)``.
+    """
+    sf, sg = shard_layout(n, world), shard_layout(m, world)
+    rows = {"f": shard_range(n, world, rank), "g": shard_range(m, world, rank)}
+    mk = lambda size, src: torch.zeros(size, dtype=src.dtype, device=src.device)
+    buf = {"f": [mk(world * sf, f_hat0), mk(world * sf, f_hat0)], "g": [mk(world * sg, g_hat0), mk(world * sg, g_hat0)]}
+    buf["f"][0][:n].copy_(f_hat0)
+    buf["g"][0][:m].copy_(g_hat0)
+    cur = {"f": 0, "g": 0}
+    shard = {"f": sf, "g": sg}
+    order = ("g", "f") if ott_convention else ("f", "g")
+
+    def half(side, eps):
+        out = buf[side][cur[side] ^ 1]
+        half_fn(side, buf["f"][cur["f"]], buf["g"][cur["g"]], out, float(eps), rows[side])
+        wait = gather_fn(out, shard[side])
+        if wait is not None:
+            wait()
+        cur[side] ^= 1
+
+    prev = (f_hat0.clone(), g_hat0.clone())
+    used = 0
+    stop = False
+    for eps in eps_list:
+        for _ in range(int(iters_per_eps)):
+            for side in order:
+                half(side, eps)
+            used += 1
+            if threshold is not None and used % check_every == 0:
+                f_now, g_now = buf["f"][cur["f"]][:n], buf["g"][cur["g"]][:m]
+                change = max(float((f_now - prev[0]).abs().max()), float((g_now - prev[1]).abs().max()))
+                if change < threshold:
+                    stop = True
+                    break
+                prev[0].copy_(f_now)
+                prev[1].copy_(g_now)
+        if stop:
+            break
+    return buf["f"][cur["f"]][:n].clone(), buf["g"][cur["g"]][:m].clone(), used
+
+
+def alternating_solve_sharded(x, y, log_a, log_b, eps_list, iters_per_eps, *, cost_scale, rho_x, rho_y,
+                              ott_convention, threshold, check_every, prec, group):
+    """CUDA engine behind :func:`run_alternating_sharded`: a half-step is ``fs_symmetric_step_range`` with
+    weight 1, one empty row range and no shift correction (the alternating solver has none). In the OTT
+    convention the log-weights stay out of the soft-min and ``eps*log w`` is added to the produced rows.
+    Returns standard potentials ``(f, g, iterations)`` like the 1-GPU solver."""
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels._common import dampening
+
+    n, d = x.shape
+    m = y.shape[0]
+    dev = x.device
+    gather, world, rank = _gather_inplace(group)
+    alpha = cost_scale * x.pow(2).sum(dim=1)
+    beta = cost_scale * y.pow(2).sum(dim=1)
+    ws = _lib.workspace(_lib.OP_STEP, n, m, d, prec, dev)
+    zeros_a, zeros_b = torch.zeros_like(log_a), torch.zeros_like(log_b)
+    in_a, in_b = (zeros_a, zeros_b) if ott_convention else (log_a, log_b)
+    # the entry point wants an output for both sides; the side with the empty range is never written
+    spare = {"f": torch.empty(n, device=dev, dtype=torch.float32), "g": torch.empty(m, device=dev, dtype=torch.float32)}
+    state = {"staged": False}
+
+    def half_fn(side, f_cur, g_cur, out, eps, rng):
+        lo, hi = rng
+        f_out, g_out = (out, spare["g"]) if side == "f" else (spare["f"], out)
+        ranges = (lo, hi, 0, 0) if side == "f" else (0, 0, lo, hi)
+        _lib.call(
+            "fs_symmetric_step_range", dev,
+            _lib.ptr(x), _lib.ptr(y), n, m, d, _lib.ptr(f_cur), _lib.ptr(g_cur), _lib.ptr(in_a), _lib.ptr(in_b),
+            _lib.ptr(f_out), _lib.ptr(g_out), None, None,
+            eps, 1.0, dampening(eps, rho_x), dampening(eps, rho_y), float(cost_scale),
+            ranges[0], ranges[1], ranges[2], ranges[3], 0 if state["staged"] else 1,
+            prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
+        )
+        state["staged"] = True
+        if ott_convention and hi > lo:
+            out[lo:hi].add_((log_a if side == "f" else log_b)[lo:hi], alpha=eps)
+
+    fh, gh, used = run_alternating_sharded(
+        n, m, -alpha, -beta, eps_list, iters_per_eps, ott_convention=ott_convention, threshold=threshold,
+        check_every=check_every, world=world, rank=rank, half_fn=half_fn, gather_fn=gather)
+    return fh + alpha, gh + beta, used
 
 
 def grad_sharded(x, y, a, b, log_a, log_b, f, g, grad_scale, eps, cost_scale, prec, want_x, want_y, group):

@@ -92,6 +92,7 @@ def sinkhorn_flashstyle_alternating(
     eps_list: Optional[Sequence[float]] = None,
     iters_per_eps: Optional[int] = None,
     tile_mask: Optional[torch.Tensor] = None,
+    process_group=None,
 ):
     """Gauss-Seidel Sinkhorn at fixed ``eps``: f from g, then g from the new f.
 
@@ -103,6 +104,9 @@ def sinkhorn_flashstyle_alternating(
     Extensions without a reference counterpart: ``eps_list`` + ``iters_per_eps`` run an
     annealed sequence of fixed-eps stages, each warm-started from the previous one, and
     ``tile_mask`` (bool ``[ceil(n/128), ceil(m/128)]``) drops 128x128 tiles from both soft-mins.
+    ``process_group``: a ``torch.distributed`` group with one rank per GPU and the same inputs on every
+    rank; the rows of every half-step are split over the ranks and all-gathered
+    (:func:`flash_sinkhorn_b200.distributed.alternating_solve_sharded`); not available with ``tile_mask``.
     """
     n, d = x.shape
     m = y.shape[0]
@@ -120,6 +124,16 @@ def sinkhorn_flashstyle_alternating(
     x32, y32 = _lib.f32c(x), _lib.f32c(y)
     log_a, log_b = log_weights(a).contiguous(), log_weights(b).contiguous()
     prec = _lib.precision_id(allow_tf32)
+    if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
+        if tile_mask is not None:
+            raise NotImplementedError("tile_mask is not available in the multi-GPU sharded alternating solver.")
+        from flash_sinkhorn_b200.distributed import alternating_solve_sharded
+
+        f, g, used = alternating_solve_sharded(
+            x32, y32, log_a.float(), log_b.float(), stages, per_stage, cost_scale=float(cost_scale), rho_x=rho_x,
+            rho_y=rho_y, ott_convention=bool(ott_convention), threshold=threshold, check_every=int(check_every),
+            prec=prec, group=process_group)
+        return (f, g, used) if return_n_iters else (f, g)
     f = torch.empty((n,), device=dev, dtype=torch.float32)
     g = torch.empty((m,), device=dev, dtype=torch.float32)
     iters = torch.zeros((1,), device=dev, dtype=torch.int32)

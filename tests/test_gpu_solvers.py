@@ -1,4 +1,6 @@
 """Solver / SamplesLoss / HVP parity on the GPU against fixtures made by the reference and the CPU oracle."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -352,3 +354,54 @@ def test_label_cost_vs_reference(monkeypatch, mode, name):
     with pytest.raises(ValueError):
         sinkhorn_flashstyle_symmetric(x, y, a, b, eps=eps, n_iters=3, use_epsilon_scaling=False,
                                       label_x=lx + 100, label_y=ly, label_cost_matrix=W, lambda_y=1.0)
+
+
+def test_sharded_alternating_engine_on_a_one_rank_group():
+    """The multi-GPU alternating path (half-steps through fs_symmetric_step_range + all-gather) on a one-rank
+    NCCL group: against the reference fixtures and against the single-launch-sequence 1-GPU solver. The
+    two-rank loop itself is covered on CPU (tests/test_sharded_gloo.py)."""
+    import socket
+
+    import torch.distributed as dist
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.distributed import alternating_solve_sharded
+    from flash_sinkhorn_b200.kernels._common import log_weights
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    own_group = not dist.is_initialized()
+    if own_group:
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+    try:
+        z = load_golden("solvers_small")
+        x, y, a, b, bn = (dev(z[k]) for k in ("x", "y", "a", "b", "b_normalised"))
+        la, lb, lbn = log_weights(a).contiguous(), log_weights(b).contiguous(), log_weights(bn).contiguous()
+        for prec, tol in ((_lib.PREC_SIMT, 2e-4), (_lib.PREC_FP32, 2e-4), (_lib.PREC_TF32, 2e-2)):
+            for conv in (False, True):
+                for rho in (None, 2.0):
+                    f, g, k = alternating_solve_sharded(
+                        x, y, la, lb, [0.4], 12, cost_scale=0.5, rho_x=rho, rho_y=rho, ott_convention=conv,
+                        threshold=None, check_every=5, prec=prec, group=dist.group.WORLD)
+                    tag = f"alt_{'ott' if conv else 'geo'}_{'bal' if rho is None else 'unb'}"
+                    assert k == 12
+                    assert rel(host(f), z[tag + "_f"]) < tol and rel(host(g), z[tag + "_g"]) < tol, (prec, tag)
+        # early stop: same iteration count and potentials as the reference; annealed stages as the 1-GPU solver
+        f, g, k = alternating_solve_sharded(x, y, la, lbn, [5.0], 80, cost_scale=1.0, rho_x=None, rho_y=None,
+                                            ott_convention=False, threshold=1e-4, check_every=3,
+                                            prec=_lib.PREC_FP32, group=dist.group.WORLD)
+        assert k == int(z["alt_early_iters"]) and rel(host(f), z["alt_early_f"]) < 2e-4
+        stages = [4.0, 2.0, 1.0, 0.5]
+        f, g, k = alternating_solve_sharded(x, y, la, lb, stages, 5, cost_scale=1.0, rho_x=1.5, rho_y=None,
+                                            ott_convention=False, threshold=None, check_every=5,
+                                            prec=_lib.PREC_FP32, group=dist.group.WORLD)
+        f1, g1, k1 = sinkhorn_flashstyle_alternating(x, y, a, b, n_iters=5, eps_list=stages, iters_per_eps=5,
+                                                     rho_x=1.5, allow_tf32=False, return_n_iters=True)
+        assert k == k1 == 20
+        assert rel(host(f), host(f1)) < 1e-5 and rel(host(g), host(g1)) < 1e-5
+        assert _lib.load().fs_device_error() == 0
+    finally:
+        if own_group:
+            dist.destroy_process_group()

@@ -135,3 +135,80 @@ def _check(tmp_path, idx, name, case, z, world):
     # matches the fixture the reference produced for the same solve
     if name == "unbalanced_schedule":
         assert np.abs(ranks[0]["f"] - z["sym_unbal_fused_f"]).max() / np.abs(z["sym_unbal_fused_f"]).max() < 3e-5
+
+
+# ---------------------------------------------------------------- alternating (Gauss-Seidel) solver
+ALT_CASES = {
+    "geomloss_damped": dict(b="b", cs=0.5, rho_x=1.0, rho_y=None, ott=False, threshold=None, check_every=5,
+                            eps_list=[0.8], iters=12),
+    "ott_balanced": dict(b="b_normalised", cs=1.0, rho_x=None, rho_y=None, ott=True, threshold=None, check_every=5,
+                         eps_list=[0.6], iters=9),
+    "annealed_early_stop": dict(b="b_normalised", cs=1.0, rho_x=None, rho_y=None, ott=False, threshold=1e-3,
+                                check_every=3, eps_list=[8.0, 4.0, 2.0], iters=40),
+}
+
+
+def _alt_worker(rank, world, port, case, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import flash_sinkhorn_b200.distributed as D
+        D.SHARD_ALIGN = 8
+        D.shard_layout.__defaults__ = (8,)
+        D.shard_range.__defaults__ = (8,)
+        z = load_golden("solvers_small")
+        x, y = z["x"].astype(np.float64), z["y"].astype(np.float64)
+        a, b = z["a"].astype(np.float64), z[case["b"]].astype(np.float64)
+        n, m = x.shape[0], y.shape[0]
+        cs, rx, ry, ott = case["cs"], case["rho_x"], case["rho_y"], case["ott"]
+        alpha, beta = cs * O.sqnorm(x), cs * O.sqnorm(y)
+        la, lb = O.log_weights(a), O.log_weights(b)
+        calls = []
+
+        def half_fn(side, f_cur, g_cur, out, eps, rng):
+            lo, hi = rng
+            calls.append(side)
+            assert out.data_ptr() not in (f_cur.data_ptr(), g_cur.data_ptr())
+            if side == "f":
+                pot, logw_in, rows, cols, damp, logw_out = g_cur[:m].numpy(), lb, x[lo:hi], y, O.dampening(eps, rx), la
+            else:
+                pot, logw_in, rows, cols, damp, logw_out = f_cur[:n].numpy(), la, y[lo:hi], x, O.dampening(eps, ry), lb
+            if ott:
+                new = eps * logw_out[lo:hi] + O.lse_update_fused(rows, cols, pot, np.zeros_like(logw_in), eps, cs, damp)
+            else:
+                new = O.lse_update_fused(rows, cols, pot, logw_in, eps, cs, damp)
+            out[lo:hi] = torch.from_numpy(new)
+
+        def gather_fn(buf, shard):
+            dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard].clone())
+
+        fh, gh, used = D.run_alternating_sharded(
+            n, m, torch.from_numpy(-alpha), torch.from_numpy(-beta), case["eps_list"], case["iters"],
+            ott_convention=ott, threshold=case["threshold"], check_every=case["check_every"], world=world, rank=rank,
+            half_fn=half_fn, gather_fn=gather_fn)
+        assert calls[:2] == (["g", "f"] if ott else ["f", "g"]) and len(calls) == 2 * used
+        np.savez(os.path.join(out_dir, f"alt_rank{rank}.npz"), f=fh.numpy() + alpha, g=gh.numpy() + beta, used=used)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", sorted(ALT_CASES))
+def test_two_rank_alternating_loop_equals_unsharded_oracle(tmp_path, name):
+    case = ALT_CASES[name]
+    world = 2
+    mp.spawn(_alt_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True)
+    z = load_golden("solvers_small")
+    x, y = z["x"].astype(np.float64), z["y"].astype(np.float64)
+    a, b = z["a"].astype(np.float64), z[case["b"]].astype(np.float64)
+    want = O.solve_alternating(x, y, a, b, case["eps_list"], case["iters"], cost_scale=case["cs"],
+                               rho_x=case["rho_x"], rho_y=case["rho_y"], ott_convention=case["ott"],
+                               threshold=case["threshold"], check_every=case["check_every"])
+    ranks = [np.load(tmp_path / f"alt_rank{r}.npz") for r in range(world)]
+    for r in ranks:
+        assert int(r["used"]) == want["n_iters"]
+        np.testing.assert_allclose(r["f"], want["f"], rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(r["g"], want["g"], rtol=1e-12, atol=1e-12)
+    assert np.array_equal(ranks[0]["f"], ranks[1]["f"]) and np.array_equal(ranks[0]["g"], ranks[1]["g"])
+    if name == "annealed_early_stop":
+        assert want["n_iters"] < 120
