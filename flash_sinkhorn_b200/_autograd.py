@@ -132,6 +132,7 @@ class _SinkhornCostFn(torch.autograd.Function):
             f_cost, g_cost = sinkhorn_flashstyle_alternating(
                 x, y, a, b, eps=eps, n_iters=len(eps_list), cost_scale=config.cost_scale,
                 rho_x=config.rho_x, rho_y=config.rho_y, allow_tf32=config.allow_tf32,
+                process_group=config.process_group,
             )
             f_grad, g_grad = f_cost, g_cost
             plain_dual = True  # the reference's alternating branch always returns <a,f>+<b,g>

@@ -340,7 +340,7 @@ class SamplesLoss(torch.nn.Module):
                 f, g = sinkhorn_flashstyle_alternating(
                     parsed.x, parsed.y, parsed.a, parsed.b, eps=float(sched[-1]), n_iters=len(sched),
                     cost_scale=self.cost_scale, reach_x=self.reach_x, reach_y=self.reach_y,
-                    allow_tf32=self.allow_tf32,
+                    allow_tf32=self.allow_tf32, process_group=self.process_group,
                 )
             else:
                 f, g = self._symmetric_potentials(parsed.x, parsed.y, parsed.a, parsed.b, label_x, label_y)
