@@ -5,8 +5,9 @@ The reference package is single-GPU. Here every rank holds the full clouds, weig
 ``[r*shard_f, (r+1)*shard_f)`` of the new f and the matching slice of the new g, then the slices are
 all-gathered (two in-place all-gathers of n resp. m floats per step, NCCL over NVLink on GPUs).
 Because every rank then holds identical full vectors, early-stop decisions are identical everywhere
-without a further collective, and results are bit-identical to the single-GPU engine (same kernels,
-same per-row arithmetic).
+without a further collective. Results equal the single-GPU engine's up to rounding: the kernels are the
+same, but the streaming pass cuts its column range by the number of row blocks it is given, so the order
+in which a row's partial sums are merged depends on the shard size.
 
 The loops themselves (:func:`run_symmetric_sharded`, :func:`run_alternating_sharded`) are engine-agnostic -
 they get the step and the gather as callables - so they are unit-tested on CPU with ``gloo`` and a dense
