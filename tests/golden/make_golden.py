@@ -486,6 +486,131 @@ def gen_signatures():
     print(f"wrote {path} ({os.path.getsize(path)} bytes, {len(table)} callables)")
 
 
+HOST_CTOR_CASES = [
+    dict(),
+    dict(blur=0.1, reach=2.0, reach_x=0.5, half_cost=True),
+    dict(blur=0.2, reach=1.5),
+    dict(reach_x=1.0),
+    dict(reach_y=3.0, debias=True),
+    dict(backend="alternating", use_epsilon_scaling=False, eps=0.1, n_iters=7),
+    dict(backend="alternating"),
+    dict(backend="alternating", use_epsilon_scaling=False),
+    dict(backend="triton"),
+    dict(backend="auto", use_flashstyle=False),
+    dict(backend="keops"),
+    dict(loss="gaussian"),
+    dict(p=1),
+    dict(reach=-1.0),
+    dict(reach_x=0.0),
+    dict(reach_y=-2.0),
+    dict(use_epsilon_scaling=False, eps=0.25, n_iters=9, potentials=True, normalize=False),
+    dict(eps_list=[1.0, 0.5, 0.25], n_iters=2),
+    dict(diameter=3.0, blur=0.3, scaling=0.7, threshold=1e-3, inner_iterations=4),
+    dict(last_extrapolation=False, allow_tf32=False, hvp_max_cg_iter=20, hvp_tau2=1e-4),
+    dict(lambda_x=0.7, lambda_y=1.8),
+    dict(backend="alternating", use_epsilon_scaling=False, eps=0.1, n_iters=7, label_cost_matrix="eye3"),
+]
+
+HOST_ARG_CASES = [
+    ("xy", dict(normalize=True)),
+    ("axby", dict(normalize=True)),
+    ("axby", dict(normalize=False)),
+    ("axby_col", dict(normalize=True)),
+    ("batched_xy", dict(normalize=True)),
+    ("batched_axby", dict(normalize=True)),
+    ("batched_axby_col", dict(normalize=False)),
+    ("three_args", dict(normalize=True)),
+    ("int_x", dict(normalize=True)),
+    ("not_tensor", dict(normalize=True)),
+    ("bad_ndim", dict(normalize=True)),
+    ("batched_x_flat_y", dict(normalize=True)),
+    ("batch_mismatch", dict(normalize=True)),
+    ("dim_mismatch", dict(normalize=True)),
+    ("bad_a", dict(normalize=True)),
+    ("bad_b_batched", dict(normalize=True)),
+]
+
+
+def host_arg_case(name):
+    """Inputs of one ``_process_args`` case; tests/test_host_api.py rebuilds them with the same seeded draws."""
+    g = torch.Generator().manual_seed(5)
+    x, y = torch.randn(6, 3, generator=g), torch.randn(4, 3, generator=g)
+    a, b = torch.rand(6, generator=g) + 0.1, torch.rand(4, generator=g) + 0.1
+    xb, yb = torch.randn(2, 6, 3, generator=g), torch.randn(2, 4, 3, generator=g)
+    ab, bb = torch.rand(2, 6, generator=g) + 0.1, torch.rand(2, 4, generator=g) + 0.1
+    return {
+        "xy": (x, y), "axby": (a, x, b, y), "axby_col": (a[:, None], x, b[:, None], y),
+        "batched_xy": (xb, yb), "batched_axby": (ab, xb, bb, yb),
+        "batched_axby_col": (ab[..., None], xb, bb[..., None], yb),
+        "three_args": (a, x, y), "int_x": (x.long(), y), "not_tensor": (x.tolist(), y),
+        "bad_ndim": (x[0], y[0]), "batched_x_flat_y": (xb, y), "batch_mismatch": (xb, yb[:1]),
+        "dim_mismatch": (x, y[:, :2]), "bad_a": (a[:5], x, b, y), "bad_b_batched": (ab, xb, bb[:, :3], yb),
+    }[name]
+
+
+def gen_host_api():
+    """Host logic of SamplesLoss that needs no device: what the constructor accepts, warns about and derives
+    (samples_loss.py:260-414), how ``_process_args`` parses and normalises the call forms (:73-191), and the
+    schedule ``_eps_list_for_inputs`` builds (:451-470). Outcomes are stored as JSON."""
+    import json
+    import warnings
+
+    from flash_sinkhorn.samples_loss import _process_args
+
+    def plain(v):
+        if torch.is_tensor(v):
+            return {"tensor": list(v.shape)}
+        return v
+
+    ctor = []
+    for kw in HOST_CTOR_CASES:
+        real = {k: (torch.eye(3) if v == "eye3" else v) for k, v in kw.items()}
+        with warnings.catch_warnings(record=True) as caught:
+            warnings.simplefilter("always")
+            try:
+                obj = SamplesLoss(real.pop("loss", "sinkhorn"), **real)
+                attrs = {k: plain(v) for k, v in vars(obj).items() if not k.startswith("_") and k != "training"}
+                out = {"attrs": attrs}
+            except Exception as e:  # noqa: BLE001 - the exception type IS the recorded outcome
+                out = {"error": type(e).__name__}
+        out["warnings"] = sorted({w.category.__name__ for w in caught})
+        ctor.append({"kwargs": kw, **out})
+
+    parsed = []
+    for name, opt in HOST_ARG_CASES:
+        try:
+            p = _process_args(*host_arg_case(name), **opt)
+            out = {"batched": bool(p.batched), "x_shape": list(p.x.shape), "y_shape": list(p.y.shape),
+                   "a": p.a.double().tolist(), "b": p.b.double().tolist(),
+                   "a_view_shape": list(p.a_view_shape), "b_view_shape": list(p.b_view_shape)}
+        except Exception as e:  # noqa: BLE001
+            out = {"error": type(e).__name__}
+        parsed.append({"case": name, "options": opt, **out})
+
+    g = torch.Generator().manual_seed(6)
+    x, y = torch.randn(50, 4, generator=g), 0.5 + torch.randn(40, 4, generator=g)
+    sched = []
+    for kw in (dict(blur=0.3, scaling=0.6), dict(blur=0.3, scaling=0.6, n_iters=4), dict(diameter=3.0, blur=0.2),
+               dict(use_epsilon_scaling=False, eps=0.25, n_iters=9), dict(eps_list=[1.0, 0.5, 0.25], n_iters=2),
+               dict(use_epsilon_scaling=False), dict(blur=0.3, n_iters=0)):
+        try:
+            out = {"eps_list": [float(e) for e in SamplesLoss("sinkhorn", **kw)._eps_list_for_inputs(x, y)]}
+        except Exception as e:  # noqa: BLE001
+            out = {"error": type(e).__name__}
+        sched.append({"kwargs": kw, **out})
+    path = os.path.join(HERE, "host_api.json")
+    with open(path, "w") as fh:
+        json.dump({"constructor": ctor, "process_args": parsed, "schedule": sched,
+                   "schedule_x": x.tolist(), "schedule_y": y.tolist()}, fh, sort_keys=True, separators=(",", ":"))
+    print(f"wrote {path} ({os.path.getsize(path)} bytes)")
+    for c in ctor:
+        print("  ctor", c["kwargs"], c.get("error", "ok"), c["warnings"])
+    for c in parsed:
+        print("  args", c["case"], c.get("error", "ok"))
+    for c in sched:
+        print("  sched", c["kwargs"], c.get("error", len(c.get("eps_list", []))))
+
+
 def gen_dense_reference():
     """The reference's dense oracles alone (no Triton): symmetric potentials, OTT alternating, gradients."""
     n, m, d = 128, 96, 32
@@ -543,10 +668,10 @@ def gen_config1():
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--skip-c1", action="store_true", help="skip the 4096x4096 dense solves (several minutes)")
-    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,labels,legacy,signatures,dense,c1")
+    ap.add_argument("--only", default="", help="comma list of: kernels,solvers,loss,hvp,implicit,ctransform,labels,legacy,signatures,hostapi,dense,c1")
     args = ap.parse_args()
     which = set(args.only.split(",")) if args.only else {"kernels", "solvers", "loss", "hvp", "implicit",
-                                                         "ctransform", "labels", "legacy", "signatures", "dense", "c1"}
+                                                         "ctransform", "labels", "legacy", "signatures", "hostapi", "dense", "c1"}
     print("reference version", flash_sinkhorn.__version__, "from", os.path.dirname(flash_sinkhorn.__file__))
     if "dense" in which:
         gen_dense_reference()
@@ -568,6 +693,8 @@ if __name__ == "__main__":
         gen_legacy()
     if "signatures" in which:
         gen_signatures()
+    if "hostapi" in which:
+        gen_host_api()
     if "c1" in which and not args.skip_c1:
         gen_config1()
     sys.exit(0)
