@@ -94,3 +94,30 @@ def test_cpu_tensors_are_refused():
     x, y = torch.randn(5, 2), torch.randn(4, 2)
     with pytest.raises(ValueError, match="CUDA"):
         SamplesLoss("sinkhorn")(x, y)
+
+
+def test_marginal_penalty_precedence():
+    """Side-specific values win over the two-sided ones, reach means rho = reach**2, and giving both spellings
+    of the same quantity is an error (reference sinkhorn_solvers.py:108-130)."""
+    from flash_sinkhorn_b200.kernels._common import dampening, resolve_marginal_penalties as res
+    assert res(None, None, None, None, None, None) == (None, None)
+    assert res(2.0, None, None, None, None, None) == (2.0, 2.0)
+    assert res(None, 3.0, None, None, None, None) == (9.0, 9.0)
+    assert res(2.0, None, 5.0, None, None, None) == (5.0, 2.0)
+    assert res(2.0, None, None, None, None, 0.5) == (2.0, 0.25)
+    assert res(None, 3.0, None, 7.0, 2.0, None) == (4.0, 7.0)
+    assert res(None, None, None, None, 1.5, None) == (2.25, None)
+    for bad in ((1.0, 1.0, None, None, None, None), (None, None, 1.0, None, 1.0, None),
+                (None, None, None, 1.0, None, 1.0)):
+        with pytest.raises(ValueError):
+            res(*bad)
+    assert dampening(0.5, None) == 1.0 and dampening(0.5, 2.0) == pytest.approx(0.8)
+
+
+def test_epsilon_schedule_argument_checks():
+    from flash_sinkhorn_b200.kernels._common import epsilon_schedule
+    for bad in ((0.0, 0.1, 0.5), (1.0, 0.0, 0.5), (1.0, 0.1, 1.0), (1.0, 0.1, 0.0)):
+        with pytest.raises(ValueError):
+            epsilon_schedule(*bad)
+    sched = epsilon_schedule(4.0, 0.5, 0.5)
+    assert sched[0] == 16.0 and sched[-1] == 0.25 and all(a >= b for a, b in zip(sched, sched[1:]))
