@@ -50,6 +50,8 @@ SIGNATURES = {
     "fs_micro_exp_rate": (c_double, [c_int, c_int]),
     "fs_micro_mma_cycles": (c_double, [c_int, c_int]),
     "fs_set_reserved_sms": (c_int, [c_int]),
+    "fs_set_cta_limit": (c_int, [c_int]),
+    "fs_plan_ctas": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "fs_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "fs_workspace_bytes_labels": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "fs_lse": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_float, c_float, c_float, c_int, _P, c_size_t, _P]),

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "lib", "libflashsinkhorn_b200.so")
-SOURCES = ["fs_api.cu", "fs_simt.cu", "fs_tc.cu", "fs_static.cu", "fs_micro.cu"]
+SOURCES = ["fs_api.cu", "fs_simt.cu", "fs_tc.cu", "fs_tck.cu", "fs_static.cu", "fs_micro.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

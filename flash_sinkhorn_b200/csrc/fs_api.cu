@@ -200,7 +200,7 @@ struct Problem {
   cudaError_t argmin(int side, const float* bias, float* out_val, int* out_idx) const {
     StreamArgs s = stream_args(side, bias, nullptr, 1.0f);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (use_tc) return tc::argmax(staged, side, s, out_val, out_idx, st);
+    if (use_tc && !tc::k_streamed(d, prec, nlab)) return tc::argmax(staged, side, s, out_val, out_idx, st);
     return simt_argmin(s, out_val, out_idx, st);
   }
   // Weighted pass. With a row normaliser R (log2 LSE of the same scores, from lse()) and the tensor-core
@@ -229,8 +229,23 @@ struct Problem {
       return tc::pv(staged, side, s, p, pv_scratch, st);
     return simt_pv(s, p, st);
   }
+  // Row normaliser R (written) followed by the matrix pass over the same scores: gradient, plan-times-matrix.
+  cudaError_t lse_pv(int side, const float* pot, const float* logw, float eps, float* R, PvArgs pa) const {
+    pa.R = R;
+    if (use_tc && mat_streamed && !pa.rows2 && !csr_rp[0]) {
+      StreamArgs s = stream_args(side, pot, logw, eps);
+      g_launches.fetch_add(3, std::memory_order_relaxed);
+      return tc::kstream_mat(staged, side, s, pa, R, pv_scratch, pv_scratch_bytes, st);
+    }
+    LseEpilogue ep;
+    ep.lse2 = R;
+    cudaError_t e = lse(side, pot, logw, eps, ep);
+    if (e != cudaSuccess) return e;
+    return pv(side, pot, logw, eps, pa);
+  }
   char* pv_scratch = nullptr;  // transposed copy of V for the tensor-core matrix pass
   size_t pv_scratch_bytes = 0;
+  bool mat_streamed = false;   // wide matrix passes of a K-streamed problem: scores kept, weights materialised
 };
 
 int check_common(const void* x, const void* y, int n, int m, int d, float eps, float cost_scale, int prec) {
@@ -269,10 +284,36 @@ int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int 
                                 -p.lab.lam_w / (2.0f * cs));
       if (e != cudaSuccess) return fail(FS_ERR_CUDA, "staging tcgen05 operands failed: %s", cudaGetErrorString(e));
     }
-    if (pv_dv > 0 && tc::pv_supported(d, prec, pv_dv, p.nlab)) {
-      p.pv_scratch_bytes = tc::pv_scratch_bytes(n > m ? n : m, d, prec, pv_dv, p.nlab);
-      p.pv_scratch = ws.take<char>(p.pv_scratch_bytes);
-      if (!measure_only && ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small");
+    // Scratch of the matrix pass (transposed V; scores and weights for K-streamed problems). When only sizes
+    // are asked for, the matrix may later have any width up to pv_dv, so the largest need is reported; a run
+    // takes the scratch only if it fits and otherwise leaves it null (the CUDA-core engine then serves the pass).
+    if (pv_dv > 0) {
+      const int nm = n > m ? n : m;
+      size_t need = 0;
+      if (tc::k_streamed(d, prec, p.nlab) && pv_dv > 1) {
+        if (tc::kstream_mat_supported(pv_dv)) {
+          need = tc::kstream_mat_scratch(nm, nm, pv_dv, prec);
+          p.mat_streamed = true;
+        }
+      } else if (measure_only) {
+        const int cand[5] = {32, 64, 96, 128, pv_dv};
+        for (int c : cand)
+          if (c <= pv_dv && tc::pv_supported(d, prec, c, p.nlab)) {
+            const size_t b = tc::pv_scratch_bytes(nm, d, prec, c, p.nlab);
+            if (b > need) need = b;
+          }
+      } else if (tc::pv_supported(d, prec, pv_dv, p.nlab)) {
+        need = tc::pv_scratch_bytes(nm, d, prec, pv_dv, p.nlab);
+      }
+      if (need > 0) {
+        if (measure_only) {
+          ws.take<char>(need);
+        } else if (ws.off + ((need + 255) & ~size_t(255)) <= ws.cap) {
+          p.pv_scratch_bytes = need;
+          p.pv_scratch = ws.take<char>(need);
+        }
+      }
+      if (!p.pv_scratch) p.mat_streamed = false;
     }
   }
   return FS_OK;
@@ -324,11 +365,17 @@ using namespace fs;
 
 extern "C" {
 
-int fs_version(void) { return 100; }
+int fs_version(void) { return 200; }  // 0.2.0
 
 long long fs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int fs_device_error(void) { return tc::read_error_flag(); }
+
+int fs_set_cta_limit(int k) { return tc::set_cta_limit(k); }
+
+int fs_plan_ctas(int n_row_blocks, int n_col_tiles, int sms, int reserved, int limit) {
+  return tc::plan_ctas(n_row_blocks, n_col_tiles, sms, reserved, limit);
+}
 
 const char* fs_last_error(void) { return g_err; }
 
@@ -668,15 +715,14 @@ int fs_apply_mat(const float* x, const float* y, int n, int m, int d, const floa
   (void)nr;
   const float* cpot = side == 0 ? g_hat : f_hat;
   const float* clw = side == 0 ? log_b : log_a;
-  LseEpilogue ep;
-  ep.lse2 = R;
-  FS_CUDA(p.lse(side, cpot, clw, eps, ep));
+  // The normaliser R and the weights must come from the same engine (bit-identical scores).
+  if (p.use_tc && !p.pv_scratch) p.use_tc = false;
   PvArgs a;
-  a.R = R; a.V = mat; a.dv = dv; a.colscale = scale; a.epilogue = PV_APPLY;
+  a.V = mat; a.dv = dv; a.colscale = scale; a.epilogue = PV_APPLY;
   a.rowpot = side == 0 ? f_hat : g_hat;
   a.rowlogw = side == 0 ? log_a : log_b;
   a.out = out;
-  FS_CUDA(p.pv(side, cpot, clw, eps, a));
+  FS_CUDA(p.lse_pv(side, cpot, clw, eps, R, a));
   return FS_OK;
 }
 
@@ -709,24 +755,18 @@ int fs_grad(const float* x, const float* y, int n, int m, int d, const float* a,
   if (grad_x) {
     sqnorm_kernel<<<g1(m * 32), 256, 0, st>>>(y, m, d, cost_scale, Rm);
     axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, g, -1.f, Rm, gh);
-    LseEpilogue ep;
-    ep.lse2 = Rn;
-    FS_CUDA(p.lse(0, gh, log_b, eps, ep));
     PvArgs pa;
-    pa.R = Rn; pa.V = y; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = a; pa.gs = grad_scale;
+    pa.V = y; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = a; pa.gs = grad_scale;
     pa.coef = 2.f * cost_scale; pa.out = grad_x;
-    FS_CUDA(p.pv(0, gh, log_b, eps, pa));
+    FS_CUDA(p.lse_pv(0, gh, log_b, eps, Rn, pa));
   }
   if (grad_y) {
     sqnorm_kernel<<<g1(n * 32), 256, 0, st>>>(x, n, d, cost_scale, Rn);
     axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, f, -1.f, Rn, fh);
-    LseEpilogue ep;
-    ep.lse2 = Rm;
-    FS_CUDA(p.lse(1, fh, log_a, eps, ep));
     PvArgs pa;
-    pa.R = Rm; pa.V = x; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = b; pa.gs = grad_scale;
+    pa.V = x; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = b; pa.gs = grad_scale;
     pa.coef = 2.f * cost_scale; pa.out = grad_y;
-    FS_CUDA(p.pv(1, fh, log_a, eps, pa));
+    FS_CUDA(p.lse_pv(1, fh, log_a, eps, Rm, pa));
   }
   FS_CUDA(cudaGetLastError());
   return FS_OK;
@@ -821,24 +861,18 @@ extern "C" int fs_grad_range(const float* x, const float* y, int n, int m, int d
   if (grad_x && x_end > x_begin) {
     sqnorm_kernel<<<g1(m * 32), 256, 0, st>>>(y, m, d, cost_scale, Rm);
     axpby_kernel<<<g1(m), 256, 0, st>>>(m, 1.f, g, -1.f, Rm, gh);
-    LseEpilogue ep;
-    ep.lse2 = Rn;
-    FS_CUDA(p.lse(0, gh, log_b, eps, ep));
     PvArgs pa;
-    pa.R = Rn; pa.V = y; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = a; pa.gs = grad_scale;
+    pa.V = y; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = a; pa.gs = grad_scale;
     pa.coef = 2.f * cost_scale; pa.out = grad_x;
-    FS_CUDA(p.pv(0, gh, log_b, eps, pa));
+    FS_CUDA(p.lse_pv(0, gh, log_b, eps, Rn, pa));
   }
   if (grad_y && y_end > y_begin) {
     sqnorm_kernel<<<g1(n * 32), 256, 0, st>>>(x, n, d, cost_scale, Rn);
     axpby_kernel<<<g1(n), 256, 0, st>>>(n, 1.f, f, -1.f, Rn, fh);
-    LseEpilogue ep;
-    ep.lse2 = Rm;
-    FS_CUDA(p.lse(1, fh, log_a, eps, ep));
     PvArgs pa;
-    pa.R = Rm; pa.V = x; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = b; pa.gs = grad_scale;
+    pa.V = x; pa.dv = d; pa.epilogue = PV_GRAD; pa.roww = b; pa.gs = grad_scale;
     pa.coef = 2.f * cost_scale; pa.out = grad_y;
-    FS_CUDA(p.pv(1, fh, log_a, eps, pa));
+    FS_CUDA(p.lse_pv(1, fh, log_a, eps, Rm, pa));
   }
   FS_CUDA(cudaGetLastError());
   return FS_OK;

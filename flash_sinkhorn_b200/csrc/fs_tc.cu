@@ -23,6 +23,7 @@
 // CTA-wide abort flag, the CTA drains its outstanding copies and MMAs (bounded again),
 // frees its TMEM and returns; a device-global error word records the event.
 #include "fs_tc.cuh"
+#include "fs_ptx.cuh"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -38,200 +39,6 @@ namespace tc {
 __device__ int g_tc_error = 0;  // non-zero once any bounded wait gave up (read by fs_device_error)
 
 namespace {
-
-constexpr float kMaskBias = -1.2676506e30f;  // -2^100: bias of padded columns (finite: survives the MMA)
-constexpr float kRunInit = -1.0e30f;         // initial running max (above the mask, below any real logit)
-constexpr long long kSpinLimit = 1ll << 28;  // ~0.14 s of SM cycles per wait (a tile takes microseconds)
-constexpr int kSmemMin = 120 * 1024;         // force one CTA per SM (TMEM is allocated per CTA)
-constexpr int kSmemMax = 227 * 1024;
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or about
-// `ns` nanoseconds pass, so a waiting single-lane role neither burns issue slots nor wakes up late.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ns)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait. Returns false (and raises *abort_flag) if the budget runs out or another
-// thread of the CTA already aborted. `park_ns` > 0 selects the parking form of try_wait (producer / MMA
-// lanes, which spend most of their time waiting and share a scheduler with soft-max warps).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned park_ns = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    if (park_ns ? mbar_try_wait_hint(bar, parity, park_ns) : mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kSpinLimit) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-// Teardown wait: bounded, ignores the abort flag (used to let in-flight copies / MMAs land).
-__device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity) {
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kSpinLimit) return;
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D[tmem] (+)= A[smem desc] x B[smem desc]^T, M=128, N from idesc, K=8 (tf32)
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  // the wait takes r[] as read-write operands: no use of the data can be scheduled above it
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Same load without the wait: the caller overlaps it with arithmetic and calls tmem_ld_wait() before use.
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-// Wait for the outstanding TMEM loads. The destination registers are passed through the asm as
-// read-write operands so that no use of them can be scheduled above the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float r;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-__device__ __forceinline__ float to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
-
-// Shared-memory matrix descriptor, K-major operand (PTX "tcgen05 matrix descriptor"):
-//   [0,14) start address >> 4, [16,30) leading byte offset >> 4 (unused for swizzled K-major: 1),
-//   [32,46) stride byte offset >> 4 (distance between 8-row groups), [46,48) version = 1,
-//   [61,64) layout: 2 = 128-byte swizzle, 6 = 32-byte swizzle.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t sbo_bytes, uint32_t layout) {
-  uint32_t lo = ((saddr & 0x3FFFFu) >> 4) | (1u << 16);
-  uint32_t hi = (sbo_bytes >> 4) | (1u << 14) | (layout << 29);
-  return ((uint64_t)hi << 32) | lo;
-}
-
-// Same descriptor assembled from a running low word (address >> 4, leading-offset field = 1) and a
-// constant high word; lets the MMA-issuing lane advance operands with one integer add.
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
-__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
-  uint64_t d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
-  return d;
-}
-constexpr uint32_t kDescHi128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8-row groups 1024 B apart, 128 B swizzle
-constexpr uint32_t kDescHi32 = (256u >> 4) | (1u << 14) | (6u << 29);    // 8-row groups 256 B apart, 32 B swizzle
-
-// Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major, M=128:
-//   [4,6) D format = 1 (f32), [7,10) A format = 2 (tf32), [10,13) B format = 2 (tf32),
-//   [17,23) N >> 3, [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
 
 struct KernelParams {
   int nr, nc;        // end of the row range / valid columns
@@ -705,41 +512,6 @@ struct PvKernelParams {
   const int* skip;       // device flag: non-zero => whole launch is a no-op
 };
 
-__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// Round-to-nearest (ties away) onto the 10-bit TF32 mantissa with two integer operations; the conversion
-// instruction shares the quarter-rate pipe with ex2, which the weights already saturate. Works on the
-// magnitude, so it is valid for either sign; the inputs here are finite weights in [0, ~1].
-__device__ __forceinline__ float round_tf32_pos(float w) {
-  return __uint_as_float((__float_as_uint(w) + 0x1000u) & 0xffffe000u);
-}
-
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
-        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
-        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
-        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
-        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
-        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
-        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
-        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-      : "memory");
-}
 
 constexpr int kNSW = 3;  // S/W buffers of the plan-times-matrix kernel
 
@@ -1150,25 +922,16 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
   return fn;
 }
 
-// 2-D fp32 tensor [rows, kp] (kp contiguous), box = [box_k floats, box_rows rows].
 bool encode_map(CUtensorMap* map, const float* base, int rows, int kp, int box_k, int box_rows,
                 CUtensorMapSwizzle swz) {
-  auto enc = get_encode();
-  if (!enc) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)kp * sizeof(float)};
-  cuuint32_t box[2] = {(cuuint32_t)box_k, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  return detail::encode_map(map, base, rows, kp, box_k, box_rows, swz);
 }
 
 struct Shape {
   int kc, kp, nfull, ntail, nhalf, bn, nstage;
   size_t smem;
   bool ok;
+  bool streamed;  // the row operand does not fit in shared memory: K-streamed kernels (fs_tck.cu) take the pass
 };
 
 // nlab = label-table columns (3 per class), staged once in either precision mode: their values are exact in TF32.
@@ -1193,6 +956,10 @@ Shape plan_shape(int d, int prec, int nlab = 0) {
     s.ok = true;
     break;
   }
+  if (!s.ok) {  // any K: both operands stream through shared memory in K chunks
+    s.ok = true;
+    s.streamed = true;
+  }
   return s;
 }
 
@@ -1208,23 +975,51 @@ cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUten
 }
 
 constexpr int kMaxChunks = 16;
-constexpr int kNumSMs = 148;
 
-// CTAs of an LSE pass. The nblk*ntiles (row block, column tile) items are cut into equal contiguous ranges,
-// one per CTA: a single wave of at most one CTA per SM, at least ~4 tiles each, and no row block shared by
-// more than kMaxChunks CTAs (that many partial slots exist per row).
 std::atomic<int> g_reserved_sms{0};
+std::atomic<int> g_cta_limit{0};
 
-int pick_ctas(int nblk, int ntiles) {
+}  // namespace
+
+namespace detail {
+
+// 2-D fp32 tensor [rows, kp] (kp contiguous), box = [box_k floats, box_rows rows].
+bool encode_map(CUtensorMap* map, const float* base, long long rows, long long kp, int box_k, int box_rows,
+                CUtensorMapSwizzle swz) {
+  auto enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)kp * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)box_k, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// SMs of the current device (cached per device index; 148 on B200).
+int sm_count() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+  cache[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+
+// CTAs of a streaming pass. The nblk*ntiles (row block, column tile) items are cut into equal contiguous
+// ranges, one per CTA: a single wave of at most one CTA per SM, at least ~4 tiles each, and no row block
+// shared by more than kMaxChunks CTAs (that many partial slots exist per row).
+int pick_ctas_for(int nblk, int ntiles, int sms, int reserved, int limit) {
   const long long total = (long long)nblk * ntiles;
   // SMs left free on request (a collective running next to the pass needs a few: a CTA of this kernel
   // fills its SM, and one that has to wait for the collective to leave delays the whole single wave).
-  long long g = kNumSMs - g_reserved_sms.load(std::memory_order_relaxed);
+  long long g = sms - reserved;
   if (g < 1) g = 1;
-  if (const char* env = getenv("FLASH_SINKHORN_B200_CTAS")) {  // diagnostics: force the CTA count
-    int c = atoi(env);
-    if (c >= 1 && c <= kNumSMs) g = c;
-  }
+  if (limit >= 1 && limit < g) g = limit;
   if (g > (total + 3) / 4) g = (total + 3) / 4;
   if (g > total) g = total;
   if (g < 1) g = 1;
@@ -1246,13 +1041,41 @@ int pick_ctas(int nblk, int ntiles) {
   return (int)g;
 }
 
+void launch_bias(const CloudOps& colc, int kc, int kp, const float* pot, const float* logw, float inv_eps,
+                 float inv_scale2, const Ctrl* ctrl, cudaStream_t st) {
+  bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, kc, kp, pot, logw, inv_eps, inv_scale2,
+                                                       ctrl);
+}
+
+int pick_ctas(int nblk, int ntiles) {
+  return pick_ctas_for(nblk, ntiles, sm_count(), g_reserved_sms.load(std::memory_order_relaxed),
+                       g_cta_limit.load(std::memory_order_relaxed));
+}
+
+}  // namespace detail
+
+namespace {
+using detail::pick_ctas;
 }  // namespace
 
 int set_reserved_sms(int k) {
+  const int sms = detail::sm_count();
   if (k < 0) k = 0;
-  if (k > kNumSMs - 1) k = kNumSMs - 1;
+  if (k > sms - 1) k = sms - 1;
   return g_reserved_sms.exchange(k, std::memory_order_relaxed);
 }
+
+int set_cta_limit(int k) {
+  if (k < 0) k = 0;
+  return g_cta_limit.exchange(k, std::memory_order_relaxed);
+}
+
+int plan_ctas(int nblk, int ntiles, int sms, int reserved, int limit) {
+  if (nblk <= 0 || ntiles <= 0 || sms <= 0) return 0;
+  return detail::pick_ctas_for(nblk, ntiles, sms, reserved < 0 ? 0 : reserved, limit);
+}
+
+bool k_streamed(int d, int prec, int nlab) { return plan_shape(d, prec, nlab).streamed; }
 
 bool supported(int n, int m, int d, int prec, int nlab) {
   if (prec != 0 && prec != 1) return false;
@@ -1266,7 +1089,7 @@ bool supported(int n, int m, int d, int prec, int nlab) {
   return plan_shape(d, prec, nlab).ok;
 }
 
-static inline int pad256(int r) { return (r + 255) & ~255; }
+using detail::pad256;
 
 size_t staged_bytes(int n, int m, int d, int prec, int nlab) {
   Shape s = plan_shape(d, prec, nlab);
@@ -1319,9 +1142,10 @@ cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const Ls
                         cudaStream_t st) {
   Shape sh = plan_shape(s.d, s.prec, s.nlab);
   if (!sh.ok) return cudaErrorNotSupported;
+  const bool am = out_idx != nullptr;
+  if (sh.streamed) return am ? cudaErrorNotSupported : kstream_lse(s, side, a, e, nullptr, 0, st);
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
-  const bool am = out_idx != nullptr;
   // LSE: logit = scale2 * (x.y + bias/scale2). Arg-max: cost = -2cs * (x.y - bias/(2cs)), so the column
   // "bias" staged next to y is -bias/(2cs) (a.pot holds the raw bias, no log-weights) and scale2 = -2cs.
   const float scale2 = am ? -2.0f * a.cost_scale : (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;
@@ -1389,7 +1213,7 @@ PvShape plan_pv(int d, int prec, int dv, int nlab = 0) {
   PvShape s{};
   Shape sh = plan_shape(d, prec, nlab);
   s.ok = false;
-  if (!sh.ok || dv <= 0) return s;
+  if (!sh.ok || sh.streamed || dv <= 0) return s;
   s.split = (prec == 1);
   s.bn = s.split ? 64 : 128;
   // TMEM: 3 S/W buffers of 128 columns leave 128 for O, so wider V goes in slices of 128 columns.
@@ -1426,10 +1250,13 @@ cudaError_t launch_pv(const CUtensorMap* maps, const PvKernelParams& kp, int gri
 }  // namespace
 
 bool pv_supported(int d, int prec, int dv, int nlab) {
-  return (prec == 0 || prec == 1) && plan_pv(d, prec, dv, nlab).ok;
+  if (prec != 0 && prec != 1) return false;
+  if (plan_shape(d, prec, nlab).streamed) return dv == 1;  // wide V: kstream_mat, asked for separately
+  return plan_pv(d, prec, dv, nlab).ok;
 }
 
 size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab) {
+  if (plan_shape(d, prec, nlab).streamed) return dv == 1 ? (size_t)pad256(nc) * sizeof(float) + 1024 : 0;
   PvShape s = plan_pv(d, prec, dv, nlab);
   if (!s.ok) return 0;
   size_t one = (size_t)s.nslices * s.dv_pad * pad256(nc) * sizeof(float);
@@ -1438,6 +1265,8 @@ size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab) {
 
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa, char* scratch, cudaStream_t st) {
   Shape sh = plan_shape(s.d, s.prec, s.nlab);
+  if (sh.ok && sh.streamed)
+    return (pa.dv == 1 && !pa.rows2) ? kstream_vec(s, side, a, pa, scratch, st) : cudaErrorNotSupported;
   PvShape ps = plan_pv(s.d, s.prec, pa.dv, s.nlab);
   if (!sh.ok || !ps.ok || pa.rows2) return cudaErrorNotSupported;
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
@@ -1582,10 +1411,14 @@ double micro_mma_cycles(int n_cols, bool a_in_tmem) {
   }
 }
 
+int read_error_flag_k();  // fs_tck.cu: the K-streamed kernels keep their own word (no relocatable device code)
+
 int read_error_flag() {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
+  const int k = read_error_flag_k();
+  if (k < 0) return -1;
+  return (v | k) ? 1 : 0;
 }
 
 }  // namespace tc

@@ -9,6 +9,8 @@
 #pragma once
 #include "fs_common.cuh"
 
+#include <cuda.h>
+
 namespace fs {
 namespace tc {
 
@@ -29,6 +31,11 @@ struct Staged {
 
 // Streaming passes leave `k` SMs unused from now on (process-wide; returns the previous value).
 int set_reserved_sms(int k);
+// Streaming passes use at most `k` CTAs from now on (0 = no limit; returns the previous value). Test knob.
+int set_cta_limit(int k);
+// CTA count a streaming pass over nblk row blocks x ntiles column tiles would get on a device with `sms`
+// SMs of which `reserved` are left free and with CTA limit `limit` (0 = none). Pure host arithmetic.
+int plan_ctas(int nblk, int ntiles, int sms, int reserved, int limit);
 
 bool supported(int n, int m, int d, int prec, int nlab = 0);
 size_t staged_bytes(int n, int m, int d, int prec, int nlab = 0);
@@ -50,6 +57,39 @@ cudaError_t argmax(const Staged& s, int side, const StreamArgs& a, float* out_va
 bool pv_supported(int d, int prec, int dv, int nlab = 0);
 size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab = 0);
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, char* scratch, cudaStream_t st);
+
+// ---- K-streamed passes (fs_tck.cu) --------------------------------------------------------------------
+// When the K-padded 128-row operand does not fit in shared memory (large d, or moderate d in the 3xTF32
+// mode) both operands stream through shared memory in 32-float K chunks and the score tile accumulates in
+// TMEM over the chunks. lse() and pv() route there by themselves; the functions below are their back ends.
+bool k_streamed(int d, int prec, int nlab = 0);
+// Soft-min pass; with s_out != nullptr the raw scores of rows [row_begin, nr) are also stored, row r at
+// s_out + (r - row_begin) * ld_s (the matrix pass turns them into weights instead of recomputing them).
+cudaError_t kstream_lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, float* s_out,
+                        long long ld_s, cudaStream_t st);
+// out_i = 2^(rowterm_i + R_i) * sum_j 2^(t_ij - R_i) v_j with the known normaliser p.R (p.dv == 1).
+cudaError_t kstream_vec(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, char* scratch,
+                        cudaStream_t st);
+// Whole matrix pass for wide V: per chunk of rows one soft-min pass that keeps its scores, an elementwise
+// pass that turns them into TF32 weights, and a K-streamed GEMM against the transposed V. Writes the row
+// normalisers to R_out ([nr] floats) on the way. `scratch` must hold kstream_mat_scratch() bytes.
+bool kstream_mat_supported(int dv);
+size_t kstream_mat_scratch(int nr, int nc, int dv, int prec);
+cudaError_t kstream_mat(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, float* R_out,
+                        char* scratch, size_t scratch_bytes, cudaStream_t st);
+
+// Shared host helpers of the two translation units.
+namespace detail {
+bool encode_map(CUtensorMap* map, const float* base, long long rows, long long kp, int box_k, int box_rows,
+                CUtensorMapSwizzle swz);
+int pick_ctas(int nblk, int ntiles);
+int sm_count();
+// Writes the column bias of a pass (divided by the logit scale, split into three TF32 pieces) into the bias
+// columns of the column operand.
+void launch_bias(const CloudOps& colc, int kc, int kp, const float* pot, const float* logw, float inv_eps,
+                 float inv_scale2, const Ctrl* ctrl, cudaStream_t st);
+inline int pad256(int r) { return (r + 255) & ~255; }
+}  // namespace detail
 
 // Value of the device-global error word (non-zero once a bounded wait gave up); synchronises.
 int read_error_flag();

@@ -56,7 +56,7 @@ enum {
   FS_OP_SCHUR = 8
 };
 
-/* Library/ABI version (major*10000 + minor*100 + patch). */
+/* Library/ABI version (major*10000 + minor*100 + patch); 200 = 0.2.0. */
 int fs_version(void);
 
 /* Message of the calling thread's most recent non-FS_OK return ("" if none). */
@@ -96,6 +96,16 @@ double fs_micro_mma_cycles(int n_cols, int a_in_tmem);
  * must wait for the collective's CTAs to leave its SM delays the whole pass; k = 2 costs ~1 % when nothing
  * else runs. Returns the previous value; 0 restores the default. */
 int fs_set_reserved_sms(int k);
+
+/* Test knob (no reference counterpart): streaming passes of this process use at most k CTAs from now on
+ * (0 = no limit, the default). Returns the previous value. Lets tests force the work split of a pass (one
+ * CTA covering many row blocks, many CTAs sharing one) without touching the environment. */
+int fs_set_cta_limit(int k);
+
+/* Host arithmetic only (no reference counterpart): the CTA count a streaming pass over n_row_blocks x
+ * n_col_tiles work items gets on a device with `sms` SMs when `reserved` of them are left free and the CTA
+ * limit is `limit` (0 = none). At most 16 CTAs ever share a row block. Returns 0 on non-positive sizes. */
+int fs_plan_ctas(int n_row_blocks, int n_col_tiles, int sms, int reserved, int limit);
 
 /* Optional label-augmented ground cost (OTDD), reference kernels/sinkhorn_flashstyle_sqeuclid.py:545-560
  * and kernels/sinkhorn_triton_grad_sqeuclid.py:225-236: the logit of entry (i, j) becomes

@@ -153,8 +153,17 @@ def test_lse_work_split_shapes(monkeypatch, n, m, ctas):
     torch.logsumexp answer (fp32-exact mode) and run-to-run identical bits."""
     from flash_sinkhorn_b200 import _lib
     from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse
-    if ctas is not None:
-        monkeypatch.setenv("FLASH_SINKHORN_B200_CTAS", str(ctas))
+    lib = _lib.load()
+    previous = lib.fs_set_cta_limit(0 if ctas is None else ctas)
+    try:
+        _check_lse_work_split(n, m)
+    finally:
+        lib.fs_set_cta_limit(previous)
+
+
+def _check_lse_work_split(n, m):
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse
     g = torch.Generator().manual_seed(n + 3 * m)
     d, eps = 16, 0.25
     x = (torch.randn(n, d, generator=g) / 4).cuda()
