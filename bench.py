@@ -13,6 +13,7 @@ half-step ("strong" scaling: total work fixed, `value` counts every entry once).
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -97,14 +98,302 @@ def cpu_reference_sample(n, m, d, eps, seconds_budget=20.0):
                       f"(row-chunked, {dt:.1f} s)"}, dt, ent
 
 
+# ---------------------------------------------------------------------------------------------------------
+# The other benchmark configurations (--config 3 | 3csr | 4 | 5). Same contract line; the default run is config 2.
+# ---------------------------------------------------------------------------------------------------------
+def make_config3(n, seed=2):
+    """64-component Gaussian mixture in 3-D (centres U[-1,1]^3, std 0.05), points sorted by component."""
+    import torch
+    gen = torch.Generator().manual_seed(seed)
+    centres = torch.rand(64, 3, generator=gen) * 2 - 1
+    out = []
+    for _ in range(2):
+        lab = torch.sort(torch.randint(0, 64, (n,), generator=gen)).values
+        out.append((centres[lab] + 0.05 * torch.randn(n, 3, generator=gen), lab))
+    return centres, out[0], out[1]
+
+
+def config3_tile_mask(centres, lab_x, lab_y, n, m, radius=0.5):
+    """Keep a 128 x 128 tile pair when some component present in the row tile and some component present in the
+    column tile have centres closer than `radius` (labels are sorted, so a tile holds a contiguous label range)."""
+    import torch
+    near = (torch.cdist(centres, centres) < radius).to(torch.int32)
+    pre = torch.zeros(65, 65, dtype=torch.int32)
+    pre[1:, 1:] = near.cumsum(0).cumsum(1)
+
+    def ranges(lab, rows):
+        nt = (rows + 127) // 128
+        lo = lab[::128][:nt]
+        hi = lab[torch.clamp(torch.arange(nt) * 128 + 127, max=rows - 1)]
+        return lo.long(), hi.long() + 1
+
+    xl, xh = ranges(lab_x, n)
+    yl, yh = ranges(lab_y, m)
+    cnt = pre[xh][:, yh] - pre[xl][:, yh] - pre[xh][:, yl] + pre[xl][:, yl]
+    return cnt > 0
+
+
+def bench_extra(args):
+    """Configs 3 (annealed alternating, 1e6 x 1e6 x 3, dense or block-sparse), 4 (unbalanced, early stop, gradient,
+    20-iteration HVP at 100k x 80k x 128) and 5 (semi-unbalanced, 16384^2 x 2048, forward + grad_x)."""
+    import torch
+    import torch.distributed as dist
+    from flash_sinkhorn_b200 import SamplesLoss, _lib
+    from flash_sinkhorn_b200.kernels._common import epsilon_schedule, max_diameter
+    from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse_fused
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating, sinkhorn_flashstyle_symmetric
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD if world > 1 else None
+    lib = _lib.load()
+    cfg = args.config
+    tf32 = not args.fp32
+    extra = {}
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+
+    # ---- per-config workload: pinned host inputs, a resident step, an end-to-end step, the entry count ----
+    if cfg in ("3", "3csr"):
+        n = m = args.n if args.n is not None else 1000000
+        d = 3
+        centres, (xh, lx), (yh, ly) = make_config3(n)
+        host_in = [xh.pin_memory(), yh.pin_memory()]
+        a_w = torch.full((n,), 1.0 / n, device=dev)
+        b_w = torch.full((m,), 1.0 / m, device=dev)
+        sched = epsilon_schedule(max_diameter(xh, yh), 0.01, 0.5)
+        mask = config3_tile_mask(centres, lx, ly, n, m) if cfg == "3csr" else None
+        if mask is None:
+            pass_entries = float(n) * m
+        else:
+            rows = torch.full((mask.shape[0],), 128.0, dtype=torch.float64)
+            cols = torch.full((mask.shape[1],), 128.0, dtype=torch.float64)
+            rows[-1] = n - 128 * (mask.shape[0] - 1)
+            cols[-1] = m - 128 * (mask.shape[1] - 1)
+            pass_entries = float(rows @ mask.double() @ cols)
+            extra["tile_density"] = float(mask.double().mean())
+        iters_per = 10
+        per_step = 2.0 * iters_per * len(sched) * pass_entries
+        workload = (f"config3{'csr' if mask is not None else ''}: annealed alternating Sinkhorn n=m={n} d=3, 64-component "
+                    f"mixture sorted by component, eps from diameter^2 to 1e-4 (scaling 0.5, {len(sched)} stages x {iters_per} "
+                    f"iterations){', 128x128 tiles kept where centres are closer than 0.5' if mask is not None else ''}")
+
+        def solve(x, y, stages):
+            return sinkhorn_flashstyle_alternating(x, y, a_w, b_w, eps_list=stages, iters_per_eps=iters_per,
+                                                   tile_mask=mask, allow_tf32=tf32, process_group=group)
+
+        step_resident = lambda x, y: solve(x, y, sched)
+        warm_step = lambda x, y: solve(x, y, sched[:1])  # one stage (20 passes) per warm-up step
+        out_host = [torch.empty(n).pin_memory(), torch.empty(m).pin_memory()]
+        kernel_fn = lambda x, y: sinkhorn_flashstyle_alternating(x, y, a_w, b_w, eps=sched[-1], n_iters=2, tile_mask=mask,
+                                                                 allow_tf32=tf32)
+        kernel_entries, kernel_name = 4 * pass_entries, "alternating half-step (one soft-min pass), mean of 4"
+        flop_per_entry = 2 * d
+    elif cfg == "5":
+        n = m = args.n if args.n is not None else 16384
+        d = args.d if args.d is not None else 2048
+        gen = torch.Generator().manual_seed(4)
+        xh = torch.nn.functional.normalize(torch.randn(n, d, generator=gen), dim=1)
+        yh = torch.nn.functional.normalize(torch.randn(m, d, generator=gen), dim=1)
+        host_in = [xh.pin_memory(), yh.pin_memory()]
+        iters = 50
+        loss_fn = SamplesLoss("sinkhorn", blur=0.05, reach_x=1.0, reach_y=None, half_cost=True, use_epsilon_scaling=False,
+                              eps=0.0025, n_iters=iters, allow_tf32=tf32, process_group=group)
+        per_step = 2.0 * (iters + 2) * n * m + float(n) * m
+        workload = (f"config5: semi-unbalanced Sinkhorn n=m={n} d={d}, unit-sphere rows, blur=0.05 reach_x=1 half_cost, "
+                    f"{iters} fixed iterations, forward + grad_x")
+
+        def step_resident(x, y):
+            xs = x.detach().requires_grad_(True)
+            val = loss_fn(xs, y)
+            (gx,) = torch.autograd.grad(val, xs)
+            return val, gx
+
+        warm_step = step_resident
+        out_host = [torch.empty(n, d).pin_memory()]
+        lb = torch.full((m,), -math.log(m), device=dev)
+        kernel_fn = lambda x, y: flashsinkhorn_lse_fused(x, y, -0.5 * (y * y).sum(1), lb, 0.0025, cost_scale=0.5,
+                                                         allow_tf32=tf32)
+        kernel_entries, kernel_name = float(n) * m, "row soft-min pass (K-streamed tcgen05), n*m entries per launch"
+        flop_per_entry = 2 * d
+    else:  # config 4
+        if world > 1:
+            raise SystemExit("config 4 includes the Hessian-vector product, which is single-GPU: run it with --gpus 1")
+        n, m, d = 100000, 80000, 128
+        if args.n is not None:
+            n, m = args.n, int(args.n * 0.8)
+        gen = torch.Generator().manual_seed(3)
+        xh = torch.randn(n, d, generator=gen)
+        yh = 1.5 * torch.randn(m, d, generator=gen)
+        a_w = torch.softmax(torch.randn(n, generator=gen), 0).to(dev)
+        b_w = (1.3 * torch.softmax(torch.randn(m, generator=gen), 0)).to(dev)
+        vh = torch.randn(n, d, generator=gen)
+        host_in = [xh.pin_memory(), yh.pin_memory(), vh.pin_memory()]
+        cg_iters = 20
+        kw = dict(blur=0.2, reach=1.0, use_epsilon_scaling=False, eps=0.04, n_iters=500, threshold=1e-3)
+        loss_fn = SamplesLoss("sinkhorn", normalize=False, inner_iterations=10, hvp_max_cg_iter=cg_iters,
+                              allow_tf32=tf32, **kw)
+
+        def step_resident(x, y, v):
+            xs = x.detach().requires_grad_(True)
+            val = loss_fn(a_w, xs, b_w, y)
+            (gx,) = torch.autograd.grad(val, xs, create_graph=True)
+            (hv,) = torch.autograd.grad((gx * v).sum(), xs)
+            return val, gx.detach(), hv
+
+        warm_step = step_resident
+        out_host = [torch.empty(n, d).pin_memory(), torch.empty(n, d).pin_memory()]
+        # steps the early stop leaves (same solve, run once outside the timed region)
+        x0, y0 = xh.to(dev), yh.to(dev)
+        used = sinkhorn_flashstyle_symmetric(x0, y0, a_w, b_w, check_every=10, return_n_iters=True, allow_tf32=tf32,
+                                             **kw)[-1]
+        del x0, y0
+        extra["solver_steps_used"] = int(used)
+        hvp_passes = 6 + 2 * cg_iters + 4  # the reference's launch count: vector passes, 3 matrix passes, Mat5
+        per_step = (2.0 * used + 1 + hvp_passes) * n * m
+        extra["entries_note"] = (f"{used} Jacobi steps x 2 soft-mins + 1 gradient pass + {hvp_passes} plan passes of the "
+                                 f"HVP (reference accounting, {cg_iters} CG iterations), n*m entries each")
+        workload = (f"config4: unbalanced Sinkhorn n={n} m={m} d={d}, masses 1.0/1.3, blur=0.2 reach=1, n_iters=500 "
+                    f"threshold=1e-3 inner_iterations=10, loss + grad_x + HVP ({cg_iters} CG iterations)")
+        la = b_w.log()
+        kernel_fn = lambda x, y, v=None: flashsinkhorn_lse_fused(x, y, -(y * y).sum(1), la, 0.04, allow_tf32=tf32)
+        kernel_entries, kernel_name = float(n) * m, "row soft-min pass of the solve, n*m entries per launch"
+        flop_per_entry = 2 * d
+
+    dev_in = [t.to(dev) for t in host_in]
+
+    def step_e2e():
+        ins = [t.to(dev, non_blocking=True) for t in host_in]
+        outs = step_resident(*ins)
+        outs = outs if isinstance(outs, (tuple, list)) else (outs,)
+        big = [o for o in outs if o.ndim > 0]
+        for dst, src in zip(out_host, big):
+            dst.copy_(src, non_blocking=True)
+        scal = [o for o in outs if o.ndim == 0]
+        return float(scal[0].item()) if scal else float(big[0][0].item())  # device->host read closes the step
+
+    for _ in range(args.warmup):
+        warm_step(*dev_in)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    launches0 = lib.fs_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        outs = step_resident(*dev_in)
+    e1.record()
+    barrier()
+    launches = lib.fs_launch_count() - launches0
+    ms = e0.elapsed_time(e1)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        result = step_e2e()
+    t1.record()
+    barrier()
+    ms_e2e = t0.elapsed_time(t1)
+    clocks = sampler.stop()
+
+    # parts of a config-4 step, timed one by one (solve with early stop / gradient / HVP)
+    if cfg == "4":
+        x, y, v = dev_in
+        k0, k1, k2, k3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        xs = x.detach().requires_grad_(True)
+        k0.record()
+        val = loss_fn(a_w, xs, b_w, y)
+        k1.record()
+        (gx,) = torch.autograd.grad(val, xs, create_graph=True)
+        k2.record()
+        (hv,) = torch.autograd.grad((gx * v).sum(), xs)
+        k3.record()
+        torch.cuda.synchronize()
+        extra.update(solve_ms=k0.elapsed_time(k1), grad_ms=k1.elapsed_time(k2), hvp_ms=k2.elapsed_time(k3))
+        del gx, hv, val, xs
+
+    # dominant kernel, timed alone on the launching stream (rank 0's GPU; single-GPU launch)
+    for _ in range(3):
+        kernel_fn(*dev_in)
+    reps = 5
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    k0.record()
+    for _ in range(reps):
+        kernel_fn(*dev_in)
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / reps
+    barrier()
+
+    times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = times.tolist()
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        exp_peak = float(lib.fs_micro_exp_rate(0, 32))
+        bf16 = peaks.get("bf16_tflops_sustained", 1400.0) * 1e12
+        tc_flops = bf16 / 2  # TF32 dense = half the measured bf16 rate
+        mult = 1 if tf32 else 3
+        tc_peak_entries = tc_flops / (flop_per_entry * mult)
+        achieved = kernel_entries / (kernel_ms * 1e-3)
+        tensor_bound = tc_peak_entries < exp_peak
+        if tensor_bound:
+            roof = {"bound": "tensor", "achieved": achieved * flop_per_entry * mult / 1e12, "peak": tc_flops / 1e12,
+                    "unit": "TFLOP/s", "frac": achieved * flop_per_entry * mult / tc_flops}
+        else:
+            roof = {"bound": "exp", "achieved": achieved, "peak": exp_peak, "unit": "entries/s", "frac": achieved / exp_peak}
+        roof.update({"traffic": None, "kernel": kernel_name, "kernel_ms": kernel_ms,
+                     "flop_per_entry": flop_per_entry * mult, "entries_per_s": achieved,
+                     "peak_source": "of measured: tensor = bf16 sustained (MEASURED_PEAKS.json) / 2 for TF32; exp = "
+                                    "ex2.approx rate from fs_micro_exp_rate(0,32) on this GPU"})
+        total = per_step * args.steps
+        h2d = sum(t.numel() * 4 for t in host_in)
+        d2h = sum(t.numel() * 4 for t in out_host) + 4
+        line = {
+            "metric": "cost_entries_per_sec", "value": total / (ms * 1e-3), "unit": "entries/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "tf32 products, f32 accumulate/exp" if tf32 else "f32 (3xTF32 products)", "data": "synthetic",
+            "config": {"workload": workload, "entries_per_step": per_step,
+                       "parallelism": (f"rows sharded over {world} GPUs, all-gather per half-step" if world > 1 else "single GPU"),
+                       "l2": "not flushed: operands are re-streamed from L2/HBM by design, the passes are compute-bound",
+                       "result": result, **extra},
+            "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "entries/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+        }
+        if not args.skip_cpu and world == 1:
+            cb, _, _ = cpu_reference_sample(min(n, 50000), min(m, 50000), d, 0.05, seconds_budget=10.0)
+            line["cpu_baseline"] = cb
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--n", type=int, default=50000)
-    ap.add_argument("--d", type=int, default=64)
+    ap.add_argument("--config", default="2", choices=["2", "3", "3csr", "4", "5"],
+                    help="benchmark configuration (default 2, the one the headline metric is quoted on)")
+    ap.add_argument("--n", type=int, default=None)
+    ap.add_argument("--d", type=int, default=None)
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--no-debias", action="store_true")
     ap.add_argument("--fp32", action="store_true", help="3xTF32 exact-fp32 mode instead of TF32")
@@ -112,6 +401,14 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="only time the dominant kernels (one LSE pass, one gradient pass); small, for profilers")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = {"2": 3, "3": 1, "3csr": 1, "4": 1, "5": 3}[args.config]
+    if args.config != "2" and args.impl == "b200":
+        return bench_extra(args)
+    if args.n is None:
+        args.n = 50000
+    if args.d is None:
+        args.d = 64
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -66,6 +66,12 @@ SIGNATURES = {
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
          c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P],
     ),
+    "fs_symmetric_step_range_tiles": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
+         c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+         c_int, _P, c_size_t, _P],
+    ),
     "fs_grad_range": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float,

@@ -193,7 +193,10 @@ struct Problem {
   cudaError_t lse(int side, const float* pot, const float* logw, float eps, const LseEpilogue& ep) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (use_tc) return tc::lse(staged, side, s, ep, st);
+    // Block-sparse tile lists run on the tensor cores when the shape has a 128 x 128 tile plan and the row
+    // range starts on a tile boundary; otherwise the CUDA-core engine walks the list.
+    const bool tiles_ok = !s.tile_row_ptr || (tc::csr_supported(d, prec, nlab) && (s.row_begin & 127) == 0);
+    if (use_tc && tiles_ok) return tc::lse(staged, side, s, ep, st);
     return simt_lse(s, ep, st);
   }
   // Hard c-transform: min_j(-2cs x_i.y_j + bias_j) and its smallest arg-min, rows of `side`.
@@ -605,8 +608,7 @@ int fs_solve_alternating(const float* x, const float* y, int n, int m, int d, co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  // Block-sparse tile lists are taken by the CUDA-core engine only.
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, tile_row_ptr ? FS_PREC_SIMT : prec, st, false));
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
   p.csr_rp[0] = tile_row_ptr; p.csr_ci[0] = tile_col_idx;
   p.csr_rp[1] = tile_row_ptr_t; p.csr_ci[1] = tile_col_idx_t;
   SolveBufs b;
@@ -812,6 +814,24 @@ extern "C" int fs_symmetric_step_range(const float* x, const float* y, int n, in
                                        float damp_f, float damp_g, float cost_scale, int f_begin, int f_end,
                                        int g_begin, int g_end, int restage, int prec, void* wsp, size_t ws_bytes,
                                        void* stream) {
+  return fs_symmetric_step_range_tiles(x, y, n, m, d, f_hat, g_hat, log_a, log_b, f_out, g_out, alpha_x, beta_y, eps,
+                                       w, damp_f, damp_g, cost_scale, f_begin, f_end, g_begin, g_end, restage,
+                                       nullptr, nullptr, nullptr, nullptr, prec, wsp, ws_bytes, stream);
+}
+
+extern "C" int fs_symmetric_step_range_tiles(const float* x, const float* y, int n, int m, int d, const float* f_hat,
+                                             const float* g_hat, const float* log_a, const float* log_b,
+                                             float* f_out, float* g_out, const float* alpha_x, const float* beta_y,
+                                             float eps, float w, float damp_f, float damp_g, float cost_scale,
+                                             int f_begin, int f_end, int g_begin, int g_end, int restage,
+                                             const int* tile_row_ptr, const int* tile_col_idx,
+                                             const int* tile_row_ptr_t, const int* tile_col_idx_t, int prec,
+                                             void* wsp, size_t ws_bytes, void* stream) {
+  if ((tile_row_ptr != nullptr) != (tile_row_ptr_t != nullptr) || (tile_row_ptr != nullptr) != (tile_col_idx != nullptr) ||
+      (tile_row_ptr_t != nullptr) != (tile_col_idx_t != nullptr))
+    return fail(FS_ERR_BAD_ARG, "tile lists: pass all four CSR arrays (tile list and its transpose) or none");
+  if (tile_row_ptr && ((f_begin & 127) || (g_begin & 127)))
+    return fail(FS_ERR_BAD_ARG, "with tile lists the row ranges must start on multiples of 128");
   FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
   if (!f_hat || !g_hat || !log_a || !log_b || !f_out || !g_out)
     return fail(FS_ERR_BAD_ARG, "potentials, log-weights and outputs must be non-null");
@@ -825,6 +845,8 @@ extern "C" int fs_symmetric_step_range(const float* x, const float* y, int n, in
   FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, 0, restage != 0));
   p.row_lo[0] = f_begin; p.row_hi[0] = f_end;
   p.row_lo[1] = g_begin; p.row_hi[1] = g_end;
+  p.csr_rp[0] = tile_row_ptr; p.csr_ci[0] = tile_col_idx;
+  p.csr_rp[1] = tile_row_ptr_t; p.csr_ci[1] = tile_col_idx_t;
   LseEpilogue ef;
   ef.damping = damp_f; ef.old = f_hat; ef.w = w; ef.out = f_out;
   if (alpha_x && damp_f < 1.f) { ef.shift = alpha_x; ef.shiftcoef = w * (1.f - damp_f); }

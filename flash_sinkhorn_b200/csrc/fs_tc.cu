@@ -59,6 +59,11 @@ struct KernelParams {
   int part_stride;
   int* tickets;  // one counter per row block, zero between launches
   int* out_idx;  // AM kernels: arg-max column per row (values go to ep.out, multiplied by scale2)
+  // CSR kernels: block-sparse list of kept (128-row block, 128-column tile) pairs. csr_rp points at the entry
+  // of the first row block of this launch's row range (nblk + 1 entries are read), csr_ci is the whole
+  // column-tile array (indexed with the values of csr_rp).
+  const int* csr_rp;
+  const int* csr_ci;
 };
 
 // Soft-max warpgroups per 128-row half: each takes half of every tile's 32-column chunks (more warps per
@@ -67,7 +72,9 @@ constexpr int kParts = 2;
 
 // AM = false: online log-sum-exp of the scaled scores (potential update). AM = true: running maximum of the
 // raw scores and the smallest column attaining it (hard c-transform); no exponentials at all.
-template <int NHALF, int BN, bool AM>
+// CSR = true: the item list is the list of kept tiles (row block after row block, NHALF = 1, BN = 128) instead
+// of all nblk x ntiles pairs; everything else - contiguous ranges per CTA, segments, ticketed merge - is the same.
+template <int NHALF, int BN, bool AM, bool CSR = false>
 __global__ void __launch_bounds__(128 + 128 * NHALF * kParts, 1)
 tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constant__ CUtensorMap mapA_tail,
               const __grid_constant__ CUtensorMap mapB_full, const __grid_constant__ CUtensorMap mapB_tail,
@@ -76,14 +83,44 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int BM = 128 * NHALF;
   // This CTA's items [w_begin, w_end) of the flattened (row block, column tile) list.
-  const long long total_items = (long long)p.nblk * p.ntiles;
-  const int w_begin = (int)((total_items * blockIdx.x) / gridDim.x);
-  const int w_end = (int)((total_items * (blockIdx.x + 1)) / gridDim.x);
+  static_assert(!CSR || (NHALF == 1 && BN == 128 && !AM), "tile lists are over 128 x 128 tiles");
+  const int rp0 = CSR ? p.csr_rp[0] : 0;
+  const long long total_items = CSR ? (long long)(p.csr_rp[p.nblk] - rp0) : (long long)p.nblk * p.ntiles;
+  // CTAs that share the items. A sparse list may hold few tiles per CTA; G is then lowered so that a row block
+  // (at most ntiles items) is never cut into more pieces than there are partial slots (16).
+  int G = (int)gridDim.x;
+  if (CSR) {
+    long long cap = (12 * total_items) / (p.ntiles > 0 ? p.ntiles : 1);
+    if (cap > total_items) cap = total_items;  // no CTA without items inside the list: pieces are counted by owner
+    if (cap < 1) cap = 1;
+    if (cap < G) G = (int)cap;
+  }
+  const bool has_work = (int)blockIdx.x < G && total_items > 0;
+  const int w_begin = has_work ? (int)((total_items * blockIdx.x) / G) : 0;
+  const int w_end = has_work ? (int)((total_items * (blockIdx.x + 1)) / G) : 0;
+  // Items of row block b are [row_start(b), row_end(b)); blk_of(w) = row block holding item w.
+  auto row_start = [&](int b) { return CSR ? p.csr_rp[b] - rp0 : b * p.ntiles; };
+  auto row_end = [&](int b) { return CSR ? p.csr_rp[b + 1] - rp0 : (b + 1) * p.ntiles; };
+  auto blk_of = [&](int w) {
+    if (!CSR) return w / p.ntiles;
+    int lo = 0, hi = p.nblk - 1;  // smallest b with row_end(b) > w
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (p.csr_rp[mid + 1] - rp0 > w) hi = mid; else lo = mid + 1;
+    }
+    return lo;
+  };
+  auto next_blk = [&](int b, int w) {  // row block of item w, known to lie after row block b
+    ++b;
+    if (CSR) while (row_end(b) <= w) ++b;
+    return b;
+  };
+  auto col_of = [&](int w, int b) { return CSR ? p.csr_ci[rp0 + w] : w - b * p.ntiles; };
   // First item of CTA c; CTA holding item t (largest c whose first item is <= t).
-  auto cta_first = [&](int c) { return (int)((total_items * c) / gridDim.x); };
+  auto cta_first = [&](int c) { return (int)((total_items * c) / G); };
   auto cta_of = [&](int t) {
-    int c = (int)(((long long)t * gridDim.x) / total_items);
-    while (c + 1 < (int)gridDim.x && cta_first(c + 1) <= t) ++c;
+    int c = (int)(((long long)t * G) / total_items);
+    while (c + 1 < G && cta_first(c + 1) <= t) ++c;
     while (c > 0 && cta_first(c) > t) --c;
     return c;
   };
@@ -163,9 +200,10 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       };
       int pre = 0;  // column tiles of the current segment that were already issued during the previous one
 #pragma unroll 1
+      int blk = has_work ? blk_of(w_begin) : 0;
+#pragma unroll 1
       for (int w = w_begin; ok && w < w_end; ++seg) {
-        const int blk = w / p.ntiles, j0 = w - blk * p.ntiles;
-        const int j1 = (p.ntiles - j0 < w_end - w) ? p.ntiles : j0 + (w_end - w);
+        const int seg_end = row_end(blk) < w_end ? row_end(blk) : w_end;
         const int row0 = p.row_begin + blk * BM;
         // The row operand of the previous segment must have been read by its last MMA.
         if (!mbar_wait(bar(A_EMPTY), (seg & 1) ^ 1, abort_flag, 2000)) break;
@@ -180,17 +218,18 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
                         row0 + h * 128, bar(A_FULL));
         }
 #pragma unroll 1
-        for (int j = j0 + pre; ok && j < j1; ++j) ok = load_b(j);
-        w += j1 - j0;
+        for (int t = w + pre; ok && t < seg_end; ++t) ok = load_b(col_of(t, blk));
+        w = seg_end;
         // Next segment (another row block, columns from 0): its first column tiles do not need the new row
         // operand, so they go into ring slots as this segment's tiles retire - every slot waited for here
         // holds a tile of this or an earlier segment, which the MMA lane consumes without the next A.
         pre = 0;
         if (ok && w < w_end) {
-          const int nnext = (p.ntiles < w_end - w) ? p.ntiles : (w_end - w);
+          blk = next_blk(blk, w);
+          const int nnext = (row_end(blk) < w_end ? row_end(blk) : w_end) - w;
           const int npre = nnext < p.nstage ? nnext : p.nstage;
 #pragma unroll 1
-          for (; ok && pre < npre; ++pre) ok = load_b(pre);
+          for (; ok && pre < npre; ++pre) ok = load_b(col_of(w + pre, blk));
         }
       }
       if (*abort_flag) {  // let every copy we issued land before the CTA goes away
@@ -211,9 +250,10 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       bool ok = true;
       int jt = 0, seg = 0;  // column tiles processed so far by this CTA (ring / buffer position), segment count
 #pragma unroll 1
+      int blk = has_work ? blk_of(w_begin) : 0;
+#pragma unroll 1
       for (int w = w_begin; ok && w < w_end; ++seg) {
-        const int blk = w / p.ntiles, j0 = w - blk * p.ntiles;
-        const int nseg = (p.ntiles - j0 < w_end - w) ? (p.ntiles - j0) : (w_end - w);
+        const int nseg = (row_end(blk) < w_end ? row_end(blk) : w_end) - w;
         if (!mbar_wait(bar(A_FULL), seg & 1, abort_flag, 2000)) break;
         tc_fence_after();
 #pragma unroll 1
@@ -253,6 +293,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         }
         umma_commit(bar(A_EMPTY));  // the row operand may be replaced once every MMA issued so far retired
         w += nseg;
+        if (w < w_end) blk = next_blk(blk, w);
       }
       if (*abort_flag) {  // wait (bounded) for every MMA issued by this lane before TMEM is freed
         umma_commit(bar(DRAIN + h));
@@ -272,7 +313,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // 2^(off_old - off_new) and the final off_run + log2(s_run) are exact identities in fp32.
     float m_run = kRunInit, off_run = __fmul_rn(scale, kRunInit), s_run = 0.f;
     int idx_run = 0;   // AM: column of the running maximum m_run
-    int col_tile = w_begin % p.ntiles;  // AM: column tile of the chunk being consumed
+    int col_tile = CSR ? 0 : w_begin % p.ntiles;  // AM: column tile of the chunk being consumed
     bool ok = true;
     constexpr int CH = BN / 32 / kParts;  // 32-column chunks of a tile owned by this warpgroup
     const int total = (w_end - w_begin) * CH;  // chunks of all segments; g / CH counts the CTA's tiles
@@ -343,6 +384,28 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         if (lane == 0) mbar_arrive(bar(S_EMPTY + h * 2 + (j & 1)));
       }
     };
+    // Epilogue of a finished row: raw log2 normaliser and / or the damped, averaged potential update.
+    auto store_lse = [&](int r, float lse2) {
+      const LseEpilogue& ep = p.ep;
+      if (ep.lse2) ep.lse2[r] = lse2;
+      if (ep.out) {
+        float cand = -p.eps * ep.damping * (lse2 * kLn2);
+        float o = ep.w * cand;
+        if (ep.old) o += (1.0f - ep.w) * ep.old[r];
+        if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
+        if (ep.addvec) o += ep.addcoef * ep.addvec[r];
+        ep.out[r] = o;
+      }
+    };
+    // A row block without any kept tile is visited by no item: its rows get the empty soft-min (log-sum of
+    // nothing = -inf), written by the CTAs in turn before they start on their items.
+    if (CSR && part == 0) {
+#pragma unroll 1
+      for (int b = blockIdx.x; b < p.nblk; b += gridDim.x) {
+        const int r = p.row_begin + b * BM + h * 128 + q * 32 + lane;
+        if (row_end(b) == row_start(b) && r < p.nr) store_lse(r, -INFINITY);
+      }
+    }
     // End of a segment (the part of one row block this CTA covers): merge the two column parts, then either
     // finish the rows (the block is ours alone) or publish the (offset, sum) pair per row; the CTA that
     // publishes last (ticket counter per row block) merges all pairs in piece order - the result does not
@@ -367,7 +430,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           off_run = on;
         }
       }
-      const int c_lo = cta_of(blk * p.ntiles), c_hi = cta_of((blk + 1) * p.ntiles - 1);
+      const int c_lo = cta_of(row_start(blk)), c_hi = cta_of(row_end(blk) - 1);
       const int pieces = c_hi - c_lo + 1, piece = (int)blockIdx.x - c_lo;
       bool finish = pieces == 1;
       if (pieces > 1) {
@@ -412,17 +475,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           p.out_idx[r] = idx_run;
         }
       } else if (finish && live && part == 0 && r < p.nr && !*abort_flag) {
-        const LseEpilogue& ep = p.ep;
-        float lse2 = off_run + log2f(fmaxf(s_run, 1e-40f));
-        if (ep.lse2) ep.lse2[r] = lse2;
-        if (ep.out) {
-          float cand = -p.eps * ep.damping * (lse2 * kLn2);
-          float o = ep.w * cand;
-          if (ep.old) o += (1.0f - ep.w) * ep.old[r];
-          if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
-          if (ep.addvec) o += ep.addcoef * ep.addvec[r];
-          ep.out[r] = o;
-        }
+        store_lse(r, off_run + log2f(fmaxf(s_run, 1e-40f)));
       }
       // merge_off / merge_sum / last_flag are re-used by the next segment
       asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
@@ -432,25 +485,26 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       idx_run = 0;
     };
     // Segment bookkeeping: seg_w = first item of the current segment, seg_end_g = its last chunk + 1.
-    int seg_w = w_begin;
-    auto seg_len = [&](int w) {
-      const int j0 = w % p.ntiles;
-      return (p.ntiles - j0 < w_end - w) ? (p.ntiles - j0) : (w_end - w);
+    int seg_w = w_begin, seg_blk = has_work ? blk_of(w_begin) : 0;
+    auto seg_len = [&]() { return (row_end(seg_blk) < w_end ? row_end(seg_blk) : w_end) - seg_w; };
+    auto next_seg = [&]() {  // step to the segment after the current one (if any)
+      seg_w += seg_len();
+      if (seg_w < w_end) seg_blk = next_blk(seg_blk, seg_w);
     };
-    int seg_end_g = seg_len(seg_w) * CH;
+    int seg_end_g = has_work ? seg_len() * CH : 0;
     auto consumed = [&](int g) {  // chunk g has been folded in: close the segment if it was its last chunk
       if (AM && g % CH == CH - 1) ++col_tile;
       if (g + 1 == seg_end_g) {
-        finalize(seg_w / p.ntiles, true);
-        seg_w += seg_len(seg_w);
-        if (seg_w < w_end) seg_end_g += seg_len(seg_w) * CH;
+        finalize(seg_blk, true);
+        next_seg();
+        if (seg_w < w_end) seg_end_g += seg_len() * CH;
         if (AM) col_tile = 0;  // every later segment starts a new row block at column 0
       }
     };
     // Software pipeline, two register buffers: the load of chunk g+1 is in flight while chunk g is consumed
     // (also across a segment boundary: the next row block's first scores load during the finalisation).
     uint32_t ra[32], rb[32];
-    ok = issue(0, ra);
+    ok = total > 0 && issue(0, ra);
 #pragma unroll 1
     for (int g = 0; ok && g < total; g += 2) {
       landed(g, ra);
@@ -472,8 +526,8 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // After an abort: keep the barrier sequence of the remaining segments (no data is written).
 #pragma unroll 1
     while (seg_w < w_end) {
-      finalize(seg_w / p.ntiles, false);
-      seg_w += seg_len(seg_w);
+      finalize(seg_blk, false);
+      next_seg();
     }
   }
 
@@ -963,10 +1017,25 @@ Shape plan_shape(int d, int prec, int nlab = 0) {
   return s;
 }
 
-template <int NHALF, int BN, bool AM>
+// Tile lists are over 128 x 128 tiles: one 128-row half per CTA, 128-column tiles.
+Shape plan_shape_csr(int d, int prec, int nlab) {
+  Shape s = plan_shape(d, prec, nlab);
+  if (!s.ok || s.streamed) { s.ok = false; return s; }
+  const size_t row_bytes = (size_t)s.kp * 4, budget = kSmemMax - 4096;
+  const size_t a = 128 * row_bytes, b = 128 * row_bytes;
+  if (a + 2 * b > budget) { s.ok = false; return s; }
+  int ns = (int)((budget - a) / b);
+  if (ns > 4) ns = 4;
+  s.nhalf = 1; s.bn = 128; s.nstage = ns;
+  s.smem = a + ns * b + 4096;
+  if (s.smem < (size_t)kSmemMin) s.smem = kSmemMin;
+  return s;
+}
+
+template <int NHALF, int BN, bool AM, bool CSR = false>
 cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUtensorMap& mb_f,
                    const CUtensorMap& mb_t, const KernelParams& kp, dim3 grid, size_t smem, cudaStream_t st) {
-  auto kern = tc_lse_kernel<NHALF, BN, AM>;
+  auto kern = tc_lse_kernel<NHALF, BN, AM, CSR>;
   // Per device (context) attribute; cheap enough to set on every launch.
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
   if (e != cudaSuccess) return e;
@@ -1077,6 +1146,10 @@ int plan_ctas(int nblk, int ntiles, int sms, int reserved, int limit) {
 
 bool k_streamed(int d, int prec, int nlab) { return plan_shape(d, prec, nlab).streamed; }
 
+bool csr_supported(int d, int prec, int nlab) {
+  return (prec == 0 || prec == 1) && plan_shape_csr(d, prec, nlab).ok;
+}
+
 bool supported(int n, int m, int d, int prec, int nlab) {
   if (prec != 0 && prec != 1) return false;
   if (n <= 0 || m <= 0 || d <= 0) return false;
@@ -1140,9 +1213,11 @@ namespace {
 // One streaming pass over the staged operands: LSE (out_idx == nullptr) or running arg-max of the raw scores.
 cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, int* out_idx,
                         cudaStream_t st) {
-  Shape sh = plan_shape(s.d, s.prec, s.nlab);
+  const bool csr = a.tile_row_ptr != nullptr;
+  Shape sh = csr ? plan_shape_csr(s.d, s.prec, s.nlab) : plan_shape(s.d, s.prec, s.nlab);
   if (!sh.ok) return cudaErrorNotSupported;
   const bool am = out_idx != nullptr;
+  if (csr && (am || !a.tile_col_idx || (a.row_begin & 127))) return cudaErrorNotSupported;
   if (sh.streamed) return am ? cudaErrorNotSupported : kstream_lse(s, side, a, e, nullptr, 0, st);
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
@@ -1177,7 +1252,10 @@ cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const Ls
   kp.nblk = nblk;
   kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride; kp.tickets = s.tickets;
   kp.out_idx = out_idx;
+  kp.csr_rp = csr ? a.tile_row_ptr + a.row_begin / 128 : nullptr;
+  kp.csr_ci = a.tile_col_idx;
   dim3 grid(pick_ctas(nblk, kp.ntiles));
+  if (csr) return launch<1, 128, false, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
   if (am) {
     if (sh.nhalf == 2) return launch<2, 128, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
     if (sh.bn == 128) return launch<1, 128, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);

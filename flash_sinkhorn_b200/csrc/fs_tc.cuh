@@ -63,6 +63,9 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, 
 // mode) both operands stream through shared memory in 32-float K chunks and the score tile accumulates in
 // TMEM over the chunks. lse() and pv() route there by themselves; the functions below are their back ends.
 bool k_streamed(int d, int prec, int nlab = 0);
+// lse() takes a block-sparse list of kept 128 x 128 tiles (StreamArgs::tile_row_ptr / tile_col_idx) for these
+// shapes; the row range must then start on a multiple of 128.
+bool csr_supported(int d, int prec, int nlab = 0);
 // Soft-min pass; with s_out != nullptr the raw scores of rows [row_begin, nr) are also stored, row r at
 // s_out + (r - row_begin) * ld_s (the matrix pass turns them into weights instead of recomputing them).
 cudaError_t kstream_lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, float* s_out,

@@ -36,6 +36,25 @@ def shard_range(rows: int, world: int, rank: int, align: int = SHARD_ALIGN) -> T
     return min(rows, rank * shard), min(rows, (rank + 1) * shard)
 
 
+def balanced_tile_ranges(row_ptr, rows: int, world: int, tile: int = SHARD_ALIGN):
+    """Row ranges ``[(lo, hi)] * world`` for a block-sparse pass: contiguous runs of ``tile``-row blocks whose
+    numbers of kept tiles (CSR ``row_ptr`` over the row blocks, host values) are as equal as a cut at block
+    boundaries allows. Rank r gets the blocks whose cumulative kept-tile count falls in the r-th of ``world``
+    equal parts; empty ranges are possible when there are fewer blocks than ranks."""
+    rp = [int(v) for v in row_ptr]
+    nblk = len(rp) - 1
+    total = rp[-1] - rp[0]
+    cuts = [0]
+    b = 0
+    for r in range(1, world):
+        target = rp[0] + (total * r) / world
+        while b < nblk and (rp[b] + rp[b + 1]) / 2.0 < target:  # block goes to the side its middle lies on
+            b += 1
+        cuts.append(b)
+    cuts.append(nblk)
+    return [(min(rows, cuts[r] * tile), min(rows, cuts[r + 1] * tile)) for r in range(world)]
+
+
 def sharded_steps(
     n: int,
     m: int,
@@ -277,6 +296,7 @@ def run_alternating_sharded(
     rank: int,
     half_fn: Callable,
     gather_fn: Callable,
+    ranges: Optional[dict] = None,
 ):
     """Row-sharded Gauss-Seidel (alternating) schedule: every half-step needs the COMPLETE result of the
     previous one, so each is followed by its all-gather before the next starts (nothing to overlap inside
@@ -288,8 +308,15 @@ def run_alternating_sharded(
     ``eps_list`` x ``iters_per_eps`` is the annealed form (one stage = the reference's fixed-eps loop).
     Early stop as in the reference (:264-270): every ``check_every`` iterations, against the potentials of
     the previous check (the initial ones at first); identical on all ranks since the vectors are.
+    ``ranges`` (optional) = ``{"f": [(lo, hi)] * world, "g": [...]}``: explicit, possibly unequal row ranges per
+    rank (block-sparse passes are split by kept tiles, see :func:`balanced_tile_ranges`). The gather then goes
+    through a padded staging buffer with one equal-sized slot per rank.
     Returns ``(f_hat, g_hat, iterations)``.
     """
+    if ranges is not None:
+        return _run_alternating_ranges(n, m, f_hat0, g_hat0, eps_list, iters_per_eps, ott_convention=ott_convention,
+                                       threshold=threshold, check_every=check_every, world=world, rank=rank,
+                                       half_fn=half_fn, gather_fn=gather_fn, ranges=ranges)
     sf, sg = shard_layout(n, world), shard_layout(m, world)
     rows = {"f": shard_range(n, world, rank), "g": shard_range(m, world, rank)}
     mk = lambda size, src: torch.zeros(size, dtype=src.dtype, device=src.device)
@@ -329,11 +356,62 @@ def run_alternating_sharded(
     return buf["f"][cur["f"]][:n].clone(), buf["g"][cur["g"]][:m].clone(), used
 
 
+def _run_alternating_ranges(n, m, f_hat0, g_hat0, eps_list, iters_per_eps, *, ott_convention, threshold,
+                            check_every, world, rank, half_fn, gather_fn, ranges):
+    """:func:`run_alternating_sharded` with explicit row ranges per rank. Rank r writes its rows into slot r of
+    a ``[world, longest range]`` staging buffer, the slots are all-gathered, and every rank copies each slot
+    back to its rows of the full vector."""
+    size = {"f": n, "g": m}
+    full = {"f": [f_hat0.clone(), f_hat0.clone()], "g": [g_hat0.clone(), g_hat0.clone()]}
+    cur = {"f": 0, "g": 0}
+    slot = {sd: max(1, max(hi - lo for lo, hi in ranges[sd])) for sd in ("f", "g")}
+    stage = {sd: torch.zeros(world * slot[sd], dtype=f_hat0.dtype, device=f_hat0.device) for sd in ("f", "g")}
+    order = ("g", "f") if ott_convention else ("f", "g")
+
+    def half(side, eps):
+        out = full[side][cur[side] ^ 1]
+        lo, hi = ranges[side][rank]
+        half_fn(side, full["f"][cur["f"]], full["g"][cur["g"]], out, float(eps), (lo, hi))
+        if hi > lo:
+            stage[side][rank * slot[side]: rank * slot[side] + (hi - lo)].copy_(out[lo:hi])
+        wait = gather_fn(stage[side], slot[side])
+        if wait is not None:
+            wait()
+        for r, (rlo, rhi) in enumerate(ranges[side]):
+            if rhi > rlo and r != rank:
+                out[rlo:rhi].copy_(stage[side][r * slot[side]: r * slot[side] + (rhi - rlo)])
+        cur[side] ^= 1
+
+    prev = (f_hat0.clone(), g_hat0.clone())
+    used = 0
+    stop = False
+    for eps in eps_list:
+        for _ in range(int(iters_per_eps)):
+            for side in order:
+                half(side, eps)
+            used += 1
+            if threshold is not None and used % check_every == 0:
+                f_now, g_now = full["f"][cur["f"]][:size["f"]], full["g"][cur["g"]][:size["g"]]
+                change = max(float((f_now - prev[0]).abs().max()), float((g_now - prev[1]).abs().max()))
+                if change < threshold:
+                    stop = True
+                    break
+                prev[0].copy_(f_now)
+                prev[1].copy_(g_now)
+        if stop:
+            break
+    return full["f"][cur["f"]].clone(), full["g"][cur["g"]].clone(), used
+
+
 def alternating_solve_sharded(x, y, log_a, log_b, eps_list, iters_per_eps, *, cost_scale, rho_x, rho_y,
-                              ott_convention, threshold, check_every, prec, group):
+                              ott_convention, threshold, check_every, prec, group, tile_csr=None,
+                              tile_row_counts=None):
     """CUDA engine behind :func:`run_alternating_sharded`: a half-step is ``fs_symmetric_step_range`` with
     weight 1, one empty row range and no shift correction (the alternating solver has none). In the OTT
     convention the log-weights stay out of the soft-min and ``eps*log w`` is added to the produced rows.
+    ``tile_csr`` = the four device CSR arrays of a block-sparse tile list and of its transpose (as
+    ``fs_solve_alternating`` takes them) and ``tile_row_counts`` = ``(row_ptr, row_ptr_t)`` as host sequences:
+    the rows of every half-step are then split so that each rank gets about the same number of kept tiles.
     Returns standard potentials ``(f, g, iterations)`` like the 1-GPU solver."""
     from flash_sinkhorn_b200 import _lib
     from flash_sinkhorn_b200.kernels._common import dampening
@@ -345,6 +423,12 @@ def alternating_solve_sharded(x, y, log_a, log_b, eps_list, iters_per_eps, *, co
     alpha = cost_scale * x.pow(2).sum(dim=1)
     beta = cost_scale * y.pow(2).sum(dim=1)
     ws = _lib.workspace(_lib.OP_STEP, n, m, d, prec, dev)
+    ranges = None
+    csr = (None, None, None, None)
+    if tile_csr is not None:
+        csr = tuple(tile_csr)
+        ranges = {"f": balanced_tile_ranges(tile_row_counts[0], n, world),
+                  "g": balanced_tile_ranges(tile_row_counts[1], m, world)}
     zeros_a, zeros_b = torch.zeros_like(log_a), torch.zeros_like(log_b)
     in_a, in_b = (zeros_a, zeros_b) if ott_convention else (log_a, log_b)
     # the entry point wants an output for both sides; the side with the empty range is never written
@@ -354,13 +438,14 @@ def alternating_solve_sharded(x, y, log_a, log_b, eps_list, iters_per_eps, *, co
     def half_fn(side, f_cur, g_cur, out, eps, rng):
         lo, hi = rng
         f_out, g_out = (out, spare["g"]) if side == "f" else (spare["f"], out)
-        ranges = (lo, hi, 0, 0) if side == "f" else (0, 0, lo, hi)
+        rr = (lo, hi, 0, 0) if side == "f" else (0, 0, lo, hi)
         _lib.call(
-            "fs_symmetric_step_range", dev,
+            "fs_symmetric_step_range_tiles", dev,
             _lib.ptr(x), _lib.ptr(y), n, m, d, _lib.ptr(f_cur), _lib.ptr(g_cur), _lib.ptr(in_a), _lib.ptr(in_b),
             _lib.ptr(f_out), _lib.ptr(g_out), None, None,
             eps, 1.0, dampening(eps, rho_x), dampening(eps, rho_y), float(cost_scale),
-            ranges[0], ranges[1], ranges[2], ranges[3], 0 if state["staged"] else 1,
+            rr[0], rr[1], rr[2], rr[3], 0 if state["staged"] else 1,
+            _lib.ptr(csr[0]), _lib.ptr(csr[1]), _lib.ptr(csr[2]), _lib.ptr(csr[3]),
             prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
         )
         state["staged"] = True
@@ -369,7 +454,7 @@ def alternating_solve_sharded(x, y, log_a, log_b, eps_list, iters_per_eps, *, co
 
     fh, gh, used = run_alternating_sharded(
         n, m, -alpha, -beta, eps_list, iters_per_eps, ott_convention=ott_convention, threshold=threshold,
-        check_every=check_every, world=world, rank=rank, half_fn=half_fn, gather_fn=gather)
+        check_every=check_every, world=world, rank=rank, half_fn=half_fn, gather_fn=gather, ranges=ranges)
     return fh + alpha, gh + beta, used
 
 

@@ -45,6 +45,9 @@ def _eps_array(eps_list: Sequence[float]):
     return arr
 
 
+_CSR_CACHE: dict = {}
+
+
 def tile_mask_to_csr(mask: torch.Tensor, device: torch.device):
     """Boolean ``[ceil(n/128), ceil(m/128)]`` tile mask -> CSR arrays of the mask and of its transpose.
 
@@ -53,6 +56,11 @@ def tile_mask_to_csr(mask: torch.Tensor, device: torch.device):
     """
     if mask.ndim != 2:
         raise ValueError("tile mask must be 2D")
+    # The conversion walks the whole mask on the host (61M tiles at n = m = 1e6); a solve that is repeated with
+    # the same, unmodified mask tensor re-uses the arrays of the previous call.
+    key = (mask.data_ptr(), mask._version, tuple(mask.shape), str(mask.device), str(device))
+    if _CSR_CACHE.get("key") == key:
+        return _CSR_CACHE["csr"]
     mk = mask.to(device="cpu", dtype=torch.bool)
 
     def one(mt: torch.Tensor):
@@ -64,6 +72,9 @@ def tile_mask_to_csr(mask: torch.Tensor, device: torch.device):
 
     rp, ci = one(mk)
     rpt, cit = one(mk.t().contiguous())
+    _CSR_CACHE.update(key=key, csr=(rp, ci, rpt, cit), mask=mask,  # holding the mask keeps its address from being re-used
+                      counts=([0] + torch.cumsum(mk.sum(dim=1), dim=0).tolist(),
+                              [0] + torch.cumsum(mk.sum(dim=0), dim=0).tolist()))
     return rp, ci, rpt, cit
 
 
@@ -106,7 +117,8 @@ def sinkhorn_flashstyle_alternating(
     ``tile_mask`` (bool ``[ceil(n/128), ceil(m/128)]``) drops 128x128 tiles from both soft-mins.
     ``process_group``: a ``torch.distributed`` group with one rank per GPU and the same inputs on every
     rank; the rows of every half-step are split over the ranks and all-gathered
-    (:func:`flash_sinkhorn_b200.distributed.alternating_solve_sharded`); not available with ``tile_mask``.
+    (:func:`flash_sinkhorn_b200.distributed.alternating_solve_sharded`); with ``tile_mask`` the split is by kept
+    tiles, so that every rank gets the same share of the work whatever the sparsity pattern.
     """
     n, d = x.shape
     m = y.shape[0]
@@ -124,25 +136,26 @@ def sinkhorn_flashstyle_alternating(
     x32, y32 = _lib.f32c(x), _lib.f32c(y)
     log_a, log_b = log_weights(a).contiguous(), log_weights(b).contiguous()
     prec = _lib.precision_id(allow_tf32)
-    if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
-        if tile_mask is not None:
-            raise NotImplementedError("tile_mask is not available in the multi-GPU sharded alternating solver.")
-        from flash_sinkhorn_b200.distributed import alternating_solve_sharded
-
-        f, g, used = alternating_solve_sharded(
-            x32, y32, log_a.float(), log_b.float(), stages, per_stage, cost_scale=float(cost_scale), rho_x=rho_x,
-            rho_y=rho_y, ott_convention=bool(ott_convention), threshold=threshold, check_every=int(check_every),
-            prec=prec, group=process_group)
-        return (f, g, used) if return_n_iters else (f, g)
-    f = torch.empty((n,), device=dev, dtype=torch.float32)
-    g = torch.empty((m,), device=dev, dtype=torch.float32)
-    iters = torch.zeros((1,), device=dev, dtype=torch.int32)
     csr = (None, None, None, None)
     if tile_mask is not None:
         nt, mt = (n + 127) // 128, (m + 127) // 128
         if tuple(tile_mask.shape) != (nt, mt):
             raise ValueError(f"tile_mask must have shape ({nt}, {mt})")
         csr = tile_mask_to_csr(tile_mask, dev)
+    if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
+        from flash_sinkhorn_b200.distributed import alternating_solve_sharded
+
+        tiles = {}
+        if tile_mask is not None:  # rows are then split by kept tiles, not by row count
+            tiles = dict(tile_csr=csr, tile_row_counts=_CSR_CACHE["counts"])
+        f, g, used = alternating_solve_sharded(
+            x32, y32, log_a.float(), log_b.float(), stages, per_stage, cost_scale=float(cost_scale), rho_x=rho_x,
+            rho_y=rho_y, ott_convention=bool(ott_convention), threshold=threshold, check_every=int(check_every),
+            prec=prec, group=process_group, **tiles)
+        return (f, g, used) if return_n_iters else (f, g)
+    f = torch.empty((n,), device=dev, dtype=torch.float32)
+    g = torch.empty((m,), device=dev, dtype=torch.float32)
+    iters = torch.zeros((1,), device=dev, dtype=torch.int32)
     ws = _lib.workspace(_lib.OP_SOLVE_ALTERNATING, n, m, d, prec, dev)
     eps_arr = _eps_array(stages)
     _lib.call(

@@ -180,6 +180,21 @@ int fs_symmetric_step_range(const float* x, const float* y, int n, int m, int d,
                             int f_begin, int f_end, int g_begin, int g_end, int restage,
                             int prec, void* ws, size_t ws_bytes, void* stream);
 
+/* The same with a block-sparse list of kept 128 x 128 tiles (CSR over the 128-row blocks of x, and the
+ * transposed list over the blocks of y, as fs_solve_alternating takes them; all four NULL = dense). No
+ * reference counterpart. Row ranges must start on multiples of 128; a multi-GPU caller cuts them so that
+ * every rank gets about the same number of kept tiles rather than of rows. */
+int fs_symmetric_step_range_tiles(const float* x, const float* y, int n, int m, int d,
+                                  const float* f_hat, const float* g_hat,
+                                  const float* log_a, const float* log_b,
+                                  float* f_out, float* g_out,
+                                  const float* alpha_x, const float* beta_y,
+                                  float eps, float w, float damp_f, float damp_g, float cost_scale,
+                                  int f_begin, int f_end, int g_begin, int g_end, int restage,
+                                  const int* tile_row_ptr, const int* tile_col_idx,
+                                  const int* tile_row_ptr_t, const int* tile_col_idx_t,
+                                  int prec, void* ws, size_t ws_bytes, void* stream);
+
 /* Row-sharded form of fs_grad: rows [x_begin, x_end) of grad_x and [y_begin, y_end) of grad_y. */
 int fs_grad_range(const float* x, const float* y, int n, int m, int d,
                   const float* a, const float* b, const float* log_a, const float* log_b,

@@ -1,0 +1,171 @@
+"""Oracle-backed parity at the full sizes of the benchmark configurations, by sampled rows and columns.
+
+The dense oracle cannot hold an n x m matrix at these sizes, but a few hundred rows of it are cheap: for rows i
+drawn at random, everything the streaming kernels produce for row i - the soft-min of a potential update, a row of
+the gradient, a row of a plan application - is recomputed in fp64 from the full column cloud (O(rows * m * d)) and
+compared with what the GPU wrote for that row. The inputs of each check are the GPU's own potentials, so every
+check isolates ONE pass of the path at its real size, eps and iteration count.
+
+Tolerances (relative to the largest magnitude among the sampled outputs): exact mode (3xTF32) against fp64 on
+the fp32 inputs; TF32 mode against fp64 on the TF32-ROUNDED inputs (round-to-nearest onto 10 mantissa bits, as
+the staging kernels do): the engine evaluates the exact problem of the rounded points, which is the statement the
+1e-3 gradient bar of TF32 mode is about. Against fp64 on the unrounded points TF32 mode differs by the rounding
+of the inputs themselves, amplified by 2*cs/eps (a property of TF32 products, not of this implementation).
+"""
+import math
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROWS = 192  # sampled rows / columns per check
+VERBOSE = bool(os.environ.get("FS_PARITY_VERBOSE"))
+
+
+@pytest.fixture(autouse=True)
+def _need_cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+def tf32_round(t):
+    i = t.contiguous().view(torch.int32)
+    return ((i + 0x1000) & ~0x1FFF).view(torch.float32)
+
+
+def relmax(got, want):
+    return float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp_min(1e-300))
+
+
+def sample(n, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randperm(n, generator=g)[: min(k, n)].cuda()
+
+
+def softmin_rows(xs, y, pot, logw, eps, cs):
+    """fp64: -eps * LSE_j[(pot_j - cs|xs_i - y_j|^2)/eps + logw_j] for the sampled rows xs."""
+    xs, y = xs.double(), y.double()
+    cost = cs * ((xs * xs).sum(1, keepdim=True) + (y * y).sum(1)[None] - 2.0 * xs @ y.T)
+    return -eps * torch.logsumexp((pot.double()[None] - cost) / eps + logw.double()[None], dim=1)
+
+
+def bary_rows(xs, y, pot, logw, eps, cs):
+    """fp64 soft-min barycentres sum_j w_ij y_j / sum_j w_ij of the sampled rows."""
+    xs, y = xs.double(), y.double()
+    cost = cs * ((xs * xs).sum(1, keepdim=True) + (y * y).sum(1)[None] - 2.0 * xs @ y.T)
+    w = torch.softmax((pot.double()[None] - cost) / eps + logw.double()[None], dim=1)
+    return w @ y
+
+
+def plan_rows(xs, fs, y, g, logw_rows, logw_cols, eps, cs):
+    xs, y = xs.double(), y.double()
+    cost = cs * ((xs * xs).sum(1, keepdim=True) + (y * y).sum(1)[None] - 2.0 * xs @ y.T)
+    return torch.exp((fs.double()[:, None] + g.double()[None] - cost) / eps + logw_rows.double()[:, None]
+                     + logw_cols.double()[None])
+
+
+def check(name, got, want, tol, log):
+    err = relmax(got, want)
+    log.append(f"{name}: {err:.2e} (tol {tol:.0e})")
+    return err <= tol
+
+
+def run_symmetric_checks(x, y, a, b, *, eps, n_iters, cs, tf32, rho_x=None, rho_y=None, tol_pot, tol_grad, tol_mat,
+                         threshold=None, tag=""):
+    """Solve on the GPU, then check on sampled rows / columns: the last (extrapolation) step of the solver as a
+    soft-min of the pre-extrapolation potentials, the gradient rows at those potentials, and plan-times-matrix rows."""
+    from flash_sinkhorn_b200.kernels._common import dampening, log_weights
+    from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_mat_flashstyle
+    from flash_sinkhorn_b200.kernels.grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_symmetric
+    n, d = x.shape
+    m = y.shape[0]
+    kw = dict(rho_x=rho_x, rho_y=rho_y) if (rho_x or rho_y) else {}
+    f, g, f_pre, g_pre = sinkhorn_flashstyle_symmetric(
+        x, y, a, b, use_epsilon_scaling=False, eps=eps, n_iters=n_iters, cost_scale=cs, allow_tf32=tf32,
+        return_prelast=True, threshold=threshold, check_every=10, **kw)
+    assert torch.isfinite(f).all() and torch.isfinite(g).all()
+    xr, yr = (tf32_round(x), tf32_round(y)) if tf32 else (x, y)
+    la, lb = log_weights(a), log_weights(b)
+    ri, cj = sample(n, ROWS, 1), sample(m, ROWS, 2)
+    log, ok = [], True
+    # 1. last solver step (weight 1): f = lam_f * softmin(g_pre) - shift correction, at full size and real eps
+    lam_f, lam_g = dampening(eps, rho_x), dampening(eps, rho_y)
+    alpha, beta = cs * (x.double() ** 2).sum(1), cs * (y.double() ** 2).sum(1)
+    # the engine works with shifted potentials and the points it staged: rebuild the same quantity in fp64
+    gh_pre = g_pre.double() - beta
+    fh_pre = f_pre.double() - alpha
+    ar, br = cs * (xr.double() ** 2).sum(1), cs * (yr.double() ** 2).sum(1)
+    # engine: f_hat_new = lam * (-eps LSE) - (1 - lam) * alpha with -eps LSE = softmin over the staged (rounded)
+    # points minus their own squared norm; f = f_hat_new + alpha (alpha from the unrounded points)
+    want_f = lam_f * (softmin_rows(xr[ri], yr, gh_pre + br, lb, eps, cs) - ar[ri] + alpha[ri])
+    ok &= check(f"{tag} f rows (last step)", f[ri], want_f, tol_pot, log)
+    want_g = lam_g * (softmin_rows(yr[cj], xr, fh_pre + ar, la, eps, cs) - br[cj] + beta[cj])
+    ok &= check(f"{tag} g cols (last step)", g[cj], want_g, tol_pot, log)
+    # 2. gradient rows at the pre-extrapolation potentials
+    gx, gy = sinkhorn_geomloss_online_grad_sqeuclid(x, y, a, b, f_pre, g_pre, eps=eps, cost_scale=cs, allow_tf32=tf32)
+    # the barycentre is formed from the staged points, the point it is subtracted from is the caller's
+    want_gx = 2 * cs * a[ri].double()[:, None] * (x[ri].double() - bary_rows(xr[ri], yr, gh_pre + br, lb, eps, cs))
+    want_gy = 2 * cs * b[cj].double()[:, None] * (y[cj].double() - bary_rows(yr[cj], xr, fh_pre + ar, la, eps, cs))
+    ok &= check(f"{tag} grad_x rows", gx[ri], want_gx, tol_grad, log)
+    ok &= check(f"{tag} grad_y rows", gy[cj], want_gy, tol_grad, log)
+    # 3. plan-times-matrix rows (dv = d, as the reference API requires) at the final potentials
+    gen = torch.Generator().manual_seed(7)
+    V = torch.randn(m, d, generator=gen).cuda()
+    fh, gh = (f.double() - alpha).float(), (g.double() - beta).float()
+    pm = apply_plan_mat_flashstyle(x, y, fh, gh, la, lb, V, eps=eps, axis=1, cost_scale=cs, allow_tf32=tf32)
+    P = plan_rows(xr[ri], fh.double()[ri] + ar[ri], yr, gh.double() + br, la[ri], lb, eps, cs)
+    ok &= check(f"{tag} (P V) rows", pm[ri], P @ V.double(), tol_mat, log)
+    if VERBOSE or not ok:
+        print("\n".join(log))
+    assert ok, "\n".join(log)
+
+
+@pytest.mark.parametrize("tf32", [True, False])
+def test_config2_sampled_rows(tf32):
+    """n = m = 50,000, d = 64, eps = 0.01, 100 iterations (the benchmarked setting)."""
+    gen = torch.Generator().manual_seed(1)
+    n = m = 50000
+    x = torch.randn(n, 64, generator=gen).cuda()
+    y = (0.5 + torch.randn(m, 64, generator=gen)).cuda()
+    a, b = torch.full((n,), 1.0 / n).cuda(), torch.full((m,), 1.0 / m).cuda()
+    run_symmetric_checks(x, y, a, b, eps=0.01, n_iters=100, cs=1.0, tf32=tf32, tol_pot=2e-5, tol_grad=1e-3,
+                         tol_mat=5e-3 if tf32 else 1e-3, tag=f"C2 tf32={tf32}")
+
+
+@pytest.mark.parametrize("tf32", [True, False])
+def test_config1_sampled_rows(tf32):
+    """n = m = 4096, d = 64, eps = 0.01, half cost, 100 iterations."""
+    gen = torch.Generator().manual_seed(0)
+    n = m = 4096
+    x, y = torch.randn(n, 64, generator=gen).cuda(), torch.randn(m, 64, generator=gen).cuda()
+    a, b = torch.full((n,), 1.0 / n).cuda(), torch.full((m,), 1.0 / m).cuda()
+    run_symmetric_checks(x, y, a, b, eps=0.01, n_iters=100, cs=0.5, tf32=tf32, tol_pot=2e-5, tol_grad=1e-3,
+                         tol_mat=5e-3 if tf32 else 1e-3, tag=f"C1 tf32={tf32}")
+
+
+@pytest.mark.parametrize("tf32", [True, False])
+def test_config5_sampled_rows(tf32):
+    """n = m = 16384, d = 2048, unit-sphere rows, eps = 0.0025, half cost, reach_x = 1, 50 iterations."""
+    gen = torch.Generator().manual_seed(4)
+    n = m = 16384
+    x = torch.nn.functional.normalize(torch.randn(n, 2048, generator=gen), dim=1).cuda()
+    y = torch.nn.functional.normalize(torch.randn(m, 2048, generator=gen), dim=1).cuda()
+    a, b = torch.full((n,), 1.0 / n).cuda(), torch.full((m,), 1.0 / m).cuda()
+    run_symmetric_checks(x, y, a, b, eps=0.0025, n_iters=50, cs=0.5, tf32=tf32, rho_x=1.0, tol_pot=2e-5, tol_grad=1e-3,
+                         tol_mat=5e-3 if tf32 else 1e-3, tag=f"C5 tf32={tf32}")
+
+
+def test_config4_sampled_rows():
+    """n = 100,000, m = 80,000, d = 128, masses 1.0 / 1.3, eps = 0.04, reach = 1, early stop (TF32 mode, as the
+    solve and the gradient of that configuration run)."""
+    gen = torch.Generator().manual_seed(3)
+    n, m, d = 100000, 80000, 128
+    x = torch.randn(n, d, generator=gen).cuda()
+    y = (1.5 * torch.randn(m, d, generator=gen)).cuda()
+    a = torch.softmax(torch.randn(n, generator=gen), 0).cuda()
+    b = (1.3 * torch.softmax(torch.randn(m, generator=gen), 0)).cuda()
+    run_symmetric_checks(x, y, a, b, eps=0.04, n_iters=500, cs=1.0, tf32=True, rho_x=1.0, rho_y=1.0, threshold=1e-3,
+                         tol_pot=2e-5, tol_grad=1e-3, tol_mat=5e-3, tag="C4 tf32")

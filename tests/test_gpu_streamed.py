@@ -1,0 +1,226 @@
+"""K-streamed tensor-core passes (feature dimensions whose operands do not fit in shared memory) and block-sparse
+tile lists on the tensor cores, against dense fp64 on the same inputs.
+
+The reference switches to a separate tiled kernel for large d (kernels/sinkhorn_triton_grad_sqeuclid.py:406-791,
+switch at :962-1000) and tests it for d in {1025, 2048, 4096} (testing/test_geomloss_sinkhorn_triton.py:255-322);
+here every streaming entry point is checked at such shapes. Tolerances: 2e-4 in the exact (3xTF32) mode; in TF32
+mode the engine solves the exact problem for the TF32-rounded points, so it is compared with fp64 on inputs
+rounded the same way (round-to-nearest onto 10 mantissa bits) - 2e-3 on soft-mins, plan-times-vector and
+gradients, 1e-2 on plan-times-matrix (weights and matrix are rounded to TF32 once more for the second product).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev, host, rel
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _need_cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+def _tf32(t):
+    i = t.contiguous().view(torch.int32)
+    return ((i + 0x1000) & ~0x1FFF).view(torch.float32)
+
+
+def _r(got, want):
+    return float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp_min(1e-30))
+
+
+SHAPES = [(700, 900, 300), (700, 900, 128), (600, 1100, 2048), (257, 130, 515), (1, 300, 1025), (300, 1, 260)]
+
+
+@pytest.mark.parametrize("tf32", [False, True])
+@pytest.mark.parametrize("n,m,d", SHAPES)
+def test_streamed_passes_vs_dense_fp64(n, m, d, tf32):
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_mat_flashstyle, apply_plan_vec_flashstyle
+    from flash_sinkhorn_b200.kernels.grad_sqeuclid import sinkhorn_geomloss_online_grad_sqeuclid
+    from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse
+    g = torch.Generator().manual_seed(n + m + d)
+    x = (torch.randn(n, d, generator=g) / d**0.5).cuda()
+    y = (torch.randn(m, d, generator=g) / d**0.5 + 0.1).cuda()
+    bias = torch.randn(m, generator=g).cuda()
+    eps = 0.05
+    t_lse, t_vec, t_mat = (2e-3, 2e-3, 1e-2) if tf32 else (2e-4, 2e-4, 2e-4)
+    xr, yr = (_tf32(x), _tf32(y)) if tf32 else (x, y)
+    dot = xr.double() @ yr.double().T
+    want = -eps * torch.logsumexp((2.0 / eps) * dot + bias.double()[None], dim=1)
+    got = flashsinkhorn_lse(x, y, bias, eps, allow_tf32=tf32)
+    assert _r(got, want) < t_lse
+    assert torch.equal(got, flashsinkhorn_lse(x, y, bias, eps, allow_tf32=tf32))  # run-to-run identical bits
+    # a consistent pair of potentials: f_hat is the soft-min of g_hat, so P has row sums a
+    a = torch.softmax(torch.randn(n, generator=g), 0).cuda()
+    b = torch.softmax(torch.randn(m, generator=g), 0).cuda()
+    la, lb = a.log(), b.log()
+    gh = -(y**2).sum(1) + 0.01 * torch.randn(m, generator=g).cuda()
+    fh = flashsinkhorn_lse(x, y, gh / eps + lb, eps, allow_tf32=False)
+    S = (2 * dot + fh.double()[:, None] + gh.double()[None]) / eps + la.double()[:, None] + lb.double()[None]
+    P = S.exp()
+    v, u = torch.randn(m, generator=g).cuda(), torch.randn(n, generator=g).cuda()
+    kw = dict(eps=eps, allow_tf32=tf32)
+    assert _r(apply_plan_vec_flashstyle(x, y, fh, gh, la, lb, v, axis=1, **kw), P @ v.double()) < t_vec
+    assert _r(apply_plan_vec_flashstyle(x, y, fh, gh, la, lb, u, axis=0, **kw), P.T @ u.double()) < t_vec
+    V, U = torch.randn(m, d, generator=g).cuda(), torch.randn(n, d, generator=g).cuda()
+    sc = torch.rand(m, generator=g).cuda()
+    assert _r(apply_plan_mat_flashstyle(x, y, fh, gh, la, lb, V, axis=1, scale=sc, **kw),
+              P @ (V.double() * sc.double()[:, None])) < t_mat
+    assert _r(apply_plan_mat_flashstyle(x, y, fh, gh, la, lb, U, axis=0, **kw), P.T @ U.double()) < t_mat
+    f, gp = fh + (x**2).sum(1), gh + (y**2).sum(1)
+    gx, gy = sinkhorn_geomloss_online_grad_sqeuclid(x, y, a, b, f, gp, eps=eps, allow_tf32=tf32)
+    Wx = torch.softmax(S - la.double()[:, None], dim=1)
+    Wy = torch.softmax((S - lb.double()[None]).T, dim=1)
+    assert _r(gx, 2 * a.double()[:, None] * (xr.double() - Wx @ yr.double())) < t_vec
+    assert _r(gy, 2 * b.double()[:, None] * (yr.double() - Wy @ xr.double())) < t_vec
+    assert _lib.load().fs_device_error() == 0
+
+
+def test_large_d_solver_and_loss_match_the_cuda_core_engine(monkeypatch):
+    """Semi-unbalanced SamplesLoss at d = 1100 (forward, grad_x): the K-streamed tensor-core path in exact mode
+    against the CUDA-core fp32 engine on the same inputs (the engines share no kernel)."""
+    from flash_sinkhorn_b200 import SamplesLoss
+    g = torch.Generator().manual_seed(11)
+    n, m, d = 500, 640, 1100
+    x = torch.nn.functional.normalize(torch.randn(n, d, generator=g), dim=1).cuda()
+    y = torch.nn.functional.normalize(torch.randn(m, d, generator=g), dim=1).cuda()
+    out = {}
+    for mode in ("simt", "fp32", "tf32"):
+        monkeypatch.setenv("FLASH_SINKHORN_B200_PREC", mode)
+        xs = x.clone().requires_grad_(True)
+        val = SamplesLoss("sinkhorn", blur=0.2, reach_x=1.0, half_cost=True, use_epsilon_scaling=False, eps=0.04,
+                          n_iters=20, allow_tf32=(mode == "tf32"))(xs, y)
+        (gx,) = torch.autograd.grad(val, xs)
+        out[mode] = (float(val), gx)
+    assert abs(out["fp32"][0] - out["simt"][0]) <= 2e-5 * abs(out["simt"][0])
+    assert _r(out["fp32"][1], out["simt"][1]) < 3e-4
+    assert abs(out["tf32"][0] - out["simt"][0]) <= 1e-4 * abs(out["simt"][0])
+    assert _r(out["tf32"][1], out["simt"][1]) < 3e-2
+
+
+def _masked_lse(x, y, pot, logw, eps, keep):
+    t = (2.0 / eps) * (x.double() @ y.double().T) + (pot.double() / eps + logw.double())[None]
+    t = torch.where(keep, t, torch.full_like(t, -float("inf")))
+    return -eps * torch.logsumexp(t, dim=1)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "tf32", "simt"])
+@pytest.mark.parametrize("n,m,density,limit", [(300, 260, 0.7, 0), (3000, 2600, 0.3, 0), (3000, 2600, 0.3, 5),
+                                               (5000, 900, 0.15, 0), (1300, 4000, 0.05, 148)])
+def test_tile_lists_vs_dense_masked_fp64(monkeypatch, mode, n, m, density, limit):
+    """Block-sparse alternating solve (kept 128 x 128 tiles as a CSR list, on the tensor cores in the fp32 and
+    tf32 modes) against a dense masked fp64 loop: a few Gauss-Seidel iterations at two eps values. The masks
+    always keep the diagonal band and hold at least one row block with a single kept tile; the forced CTA
+    limits make one CTA cover many row blocks and many CTAs share one."""
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating
+    monkeypatch.setenv("FLASH_SINKHORN_B200_PREC", mode)
+    g = torch.Generator().manual_seed(n + m)
+    d = 3
+    x = (torch.rand(n, d, generator=g) * 2 - 1).cuda()
+    y = (torch.rand(m, d, generator=g) * 2 - 1).cuda()
+    a = torch.full((n,), 1.0 / n).cuda()
+    b = torch.full((m,), 1.0 / m).cuda()
+    nt, mt = (n + 127) // 128, (m + 127) // 128
+    mask = torch.rand(nt, mt, generator=g) < density
+    for i in range(nt):  # every row and column block keeps the tile on the (stretched) diagonal
+        mask[i, min(mt - 1, i * mt // nt)] = True
+    for j in range(mt):
+        mask[min(nt - 1, j * nt // mt), j] = True
+    mask[nt // 2, :] = False
+    mask[nt // 2, min(mt - 1, (nt // 2) * mt // nt)] = True
+    for j in range(mt):
+        if not mask[:, j].any():
+            mask[0, j] = True
+    keep = mask.cuda().repeat_interleave(128, 0).repeat_interleave(128, 1)[:n, :m]
+    stages, iters = [1.0, 0.3], 3
+    la, lb = a.log(), b.log()
+    xr, yr = (_tf32(x), _tf32(y)) if mode == "tf32" else (x, y)
+    alpha, beta = (x.double() ** 2).sum(1), (y.double() ** 2).sum(1)
+    fh, gh = -alpha, -beta
+    for eps in stages:
+        for _ in range(iters):
+            fh = _masked_lse(xr, yr, gh, lb, eps, keep)
+            gh = _masked_lse(yr, xr, fh, la, eps, keep.T)
+    lib = _lib.load()
+    previous = lib.fs_set_cta_limit(limit)
+    try:
+        f, gp = sinkhorn_flashstyle_alternating(x, y, a, b, eps_list=stages, iters_per_eps=iters, tile_mask=mask,
+                                                allow_tf32=(mode == "tf32"))
+        f2, _ = sinkhorn_flashstyle_alternating(x, y, a, b, eps_list=stages, iters_per_eps=iters, tile_mask=mask,
+                                                allow_tf32=(mode == "tf32"))
+    finally:
+        lib.fs_set_cta_limit(previous)
+    tol = 5e-3 if mode == "tf32" else 3e-4
+    assert _r(f, fh + alpha) < tol and _r(gp, gh + beta) < tol
+    assert torch.equal(f, f2)
+    assert lib.fs_device_error() == 0
+
+
+def test_row_block_without_kept_tiles_gets_the_empty_soft_min(monkeypatch):
+    """A row block whose tile list is empty is visited by no work item; its rows must still be written (with
+    the soft-min over nothing, +inf), identically on the tensor-core and the CUDA-core engine."""
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating
+    g = torch.Generator().manual_seed(5)
+    n, m = 700, 520
+    x, y = torch.randn(n, 3, generator=g).cuda(), torch.randn(m, 3, generator=g).cuda()
+    a, b = torch.full((n,), 1.0 / n).cuda(), torch.full((m,), 1.0 / m).cuda()
+    mask = torch.ones((n + 127) // 128, (m + 127) // 128, dtype=torch.bool)
+    mask[2, :] = False
+    res = {}
+    for mode in ("simt", "fp32"):
+        monkeypatch.setenv("FLASH_SINKHORN_B200_PREC", mode)
+        res[mode] = sinkhorn_flashstyle_alternating(x, y, a, b, eps=0.5, n_iters=1, tile_mask=mask, allow_tf32=False)
+    for mode in res:
+        f = res[mode][0]
+        assert torch.isinf(f[256:384]).all() and (f[256:384] > 0).all()
+        assert torch.isfinite(f[:256]).all() and torch.isfinite(f[384:]).all()
+    assert _r(res["fp32"][0][:256], res["simt"][0][:256]) < 2e-4
+
+
+def test_sharded_alternating_with_tile_lists_on_a_one_rank_group():
+    """The multi-GPU block-sparse path (fs_symmetric_step_range_tiles, rows split by kept tiles, padded gather)
+    on a one-rank NCCL group against the single-GPU solver; the two-rank loop with unequal ranges is covered
+    on CPU (tests/test_sharded_gloo.py)."""
+    import socket
+
+    import torch.distributed as dist
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.distributed import alternating_solve_sharded
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating, tile_mask_to_csr
+    own_group = not dist.is_initialized()
+    if own_group:
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+    try:
+        g = torch.Generator().manual_seed(9)
+        n, m = 1500, 1100
+        x, y = (torch.rand(n, 3, generator=g)).cuda(), (torch.rand(m, 3, generator=g)).cuda()
+        a, b = torch.full((n,), 1.0 / n).cuda(), torch.full((m,), 1.0 / m).cuda()
+        nt, mt = (n + 127) // 128, (m + 127) // 128
+        mask = torch.rand(nt, mt, generator=g) < 0.5
+        mask[:, 0] = True
+        mask[0, :] = True
+        csr = tile_mask_to_csr(mask, x.device)
+        counts = lambda t: [0] + torch.cumsum(t.sum(dim=1), dim=0).tolist()
+        for prec, allow in ((_lib.PREC_FP32, False), (_lib.PREC_TF32, True)):
+            f, gp, k = alternating_solve_sharded(
+                x, y, a.log(), b.log(), [0.5, 0.1], 4, cost_scale=1.0, rho_x=None, rho_y=None, ott_convention=False,
+                threshold=None, check_every=5, prec=prec, group=dist.group.WORLD, tile_csr=csr,
+                tile_row_counts=(counts(mask), counts(mask.t())))
+            f1, g1 = sinkhorn_flashstyle_alternating(x, y, a, b, eps_list=[0.5, 0.1], iters_per_eps=4, tile_mask=mask,
+                                                     allow_tf32=allow)
+            assert k == 8 and _r(f, f1) < 1e-5 and _r(gp, g1) < 1e-5
+    finally:
+        if own_group:
+            dist.destroy_process_group()

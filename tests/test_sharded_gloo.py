@@ -145,6 +145,11 @@ ALT_CASES = {
                          eps_list=[0.6], iters=9),
     "annealed_early_stop": dict(b="b_normalised", cs=1.0, rho_x=None, rho_y=None, ott=False, threshold=1e-3,
                                 check_every=3, eps_list=[8.0, 4.0, 2.0], iters=40),
+    # rows split by (synthetic) kept-tile counts instead of evenly: unequal ranges, padded gather
+    "uneven_ranges": dict(b="b_normalised", cs=1.0, rho_x=None, rho_y=2.0, ott=False, threshold=1e-3,
+                          check_every=3, eps_list=[4.0, 1.0], iters=15, uneven=True),
+    "uneven_ranges_ott": dict(b="b_normalised", cs=0.5, rho_x=None, rho_y=None, ott=True, threshold=None,
+                              check_every=5, eps_list=[0.6], iters=7, uneven=True),
 }
 
 
@@ -183,10 +188,18 @@ def _alt_worker(rank, world, port, case, out_dir):
         def gather_fn(buf, shard):
             dist.all_gather_into_tensor(buf, buf[rank * shard:(rank + 1) * shard].clone())
 
+        ranges = None
+        if case.get("uneven"):  # explicit, unequal row ranges as a block-sparse pass gets them (8-row blocks here)
+            nb, mb = -(-n // 8), -(-m // 8)
+            rp_f = np.concatenate([[0], np.cumsum(1 + np.arange(nb) ** 2)])
+            rp_g = np.concatenate([[0], np.cumsum(1 + (np.arange(mb)[::-1] % 7))])
+            ranges = {"f": D.balanced_tile_ranges(rp_f, n, world, tile=8),
+                      "g": D.balanced_tile_ranges(rp_g, m, world, tile=8)}
+            assert ranges["f"][0][1] - ranges["f"][0][0] != ranges["f"][1][1] - ranges["f"][1][0]
         fh, gh, used = D.run_alternating_sharded(
             n, m, torch.from_numpy(-alpha), torch.from_numpy(-beta), case["eps_list"], case["iters"],
             ott_convention=ott, threshold=case["threshold"], check_every=case["check_every"], world=world, rank=rank,
-            half_fn=half_fn, gather_fn=gather_fn)
+            half_fn=half_fn, gather_fn=gather_fn, ranges=ranges)
         assert calls[:2] == (["g", "f"] if ott else ["f", "g"]) and len(calls) == 2 * used
         np.savez(os.path.join(out_dir, f"alt_rank{rank}.npz"), f=fh.numpy() + alpha, g=gh.numpy() + beta, used=used)
     finally:
@@ -212,3 +225,21 @@ def test_two_rank_alternating_loop_equals_unsharded_oracle(tmp_path, name):
     assert np.array_equal(ranks[0]["f"], ranks[1]["f"]) and np.array_equal(ranks[0]["g"], ranks[1]["g"])
     if name == "annealed_early_stop":
         assert want["n_iters"] < 120
+
+
+def test_balanced_tile_ranges_cover_the_rows_and_balance_the_kept_tiles():
+    import flash_sinkhorn_b200.distributed as D
+    rng = np.random.default_rng(0)
+    for nblk, world in [(1, 2), (7, 4), (64, 8), (7813, 8), (100, 3)]:
+        counts = rng.integers(0, 50, size=nblk)
+        counts[rng.integers(0, nblk)] += 1  # at least one kept tile
+        rp = np.concatenate([[0], np.cumsum(counts)])
+        rows = nblk * 128 - 37
+        ranges = D.balanced_tile_ranges(rp, rows, world)
+        assert len(ranges) == world and ranges[0][0] == 0 and ranges[-1][1] == rows
+        for (lo, hi), (lo2, _) in zip(ranges, ranges[1:]):
+            assert hi == lo2 and lo % 128 == 0 and lo <= hi
+        per_rank = [int(rp[-(-hi // 128)] - rp[lo // 128]) for lo, hi in ranges]
+        assert sum(per_rank) == rp[-1]
+        # no rank exceeds the ideal share by more than one block's worth of tiles
+        assert max(per_rank) <= rp[-1] / world + counts.max()
