@@ -133,6 +133,25 @@ def config3_tile_mask(centres, lab_x, lab_y, n, m, radius=0.5):
     return cnt > 0
 
 
+def pass_ms_by_difference(run_solve, k1, k2, reps=3):
+    """Device time of ONE soft-min pass inside a symmetric solve: (T(k2 iterations) - T(k1 iterations)) divided by
+    the 2 (k2 - k1) passes the longer solve adds. Staging, norms and Python overhead are common to both and drop
+    out; the per-pass bias kernel stays in (it is part of every pass)."""
+    import torch
+    times = []
+    for k in (k1, k2):
+        run_solve(k)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run_solve(k)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / reps)
+    return (times[1] - times[0]) / (2.0 * (k2 - k1))
+
+
 def bench_extra(args):
     """Configs 3 (annealed alternating, 1e6 x 1e6 x 3, dense or block-sparse), 4 (unbalanced, early stop, gradient,
     20-iteration HVP at 100k x 80k x 128) and 5 (semi-unbalanced, 16384^2 x 2048, forward + grad_x)."""
@@ -198,6 +217,7 @@ def bench_extra(args):
                                                                  allow_tf32=tf32)
         kernel_entries, kernel_name = 4 * pass_entries, "alternating half-step (one soft-min pass), mean of 4"
         flop_per_entry = 2 * d
+        kernel_timer = None
     elif cfg == "5":
         n = m = args.n if args.n is not None else 16384
         d = args.d if args.d is not None else 2048
@@ -225,6 +245,11 @@ def bench_extra(args):
                                                          allow_tf32=tf32)
         kernel_entries, kernel_name = float(n) * m, "row soft-min pass (K-streamed tcgen05), n*m entries per launch"
         flop_per_entry = 2 * d
+        a5 = torch.full((n,), 1.0 / n, device=dev)
+        kernel_timer = lambda x, y: pass_ms_by_difference(
+            lambda k: sinkhorn_flashstyle_symmetric(x, y, a5, a5, use_epsilon_scaling=False, eps=0.0025, n_iters=k,
+                                                    cost_scale=0.5, reach_x=1.0, last_extrapolation=False,
+                                                    allow_tf32=tf32), 2, 12)
     else:  # config 4
         if world > 1:
             raise SystemExit("config 4 includes the Hessian-vector product, which is single-GPU: run it with --gpus 1")
@@ -268,6 +293,9 @@ def bench_extra(args):
         kernel_fn = lambda x, y, v=None: flashsinkhorn_lse_fused(x, y, -(y * y).sum(1), la, 0.04, allow_tf32=tf32)
         kernel_entries, kernel_name = float(n) * m, "row soft-min pass of the solve, n*m entries per launch"
         flop_per_entry = 2 * d
+        kernel_timer = lambda x, y, v=None: pass_ms_by_difference(
+            lambda k: sinkhorn_flashstyle_symmetric(x, y, a_w, b_w, use_epsilon_scaling=False, eps=0.04, n_iters=k,
+                                                    reach=1.0, last_extrapolation=False, allow_tf32=tf32), 2, 12)
 
     dev_in = [t.to(dev) for t in host_in]
     if args.kernel_only:  # small runs for profilers: only the dominant kernel, a few launches
@@ -345,6 +373,10 @@ def bench_extra(args):
     k1.record()
     torch.cuda.synchronize()
     kernel_ms = k0.elapsed_time(k1) / reps
+    kernel_how = "stand-alone call (includes staging of the operands), mean of 5"
+    if kernel_timer is not None:  # one pass inside a solve, by differencing two solve lengths
+        kernel_ms = kernel_timer(*dev_in)
+        kernel_how = "inside a solve: (T(12 iterations) - T(2 iterations)) / 20 passes, CUDA events"
     barrier()
 
     times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
@@ -369,7 +401,7 @@ def bench_extra(args):
                     "unit": "TFLOP/s", "frac": achieved * flop_per_entry * mult / tc_flops}
         else:
             roof = {"bound": "exp", "achieved": achieved, "peak": exp_peak, "unit": "entries/s", "frac": achieved / exp_peak}
-        roof.update({"traffic": None, "kernel": kernel_name, "kernel_ms": kernel_ms,
+        roof.update({"traffic": None, "kernel": kernel_name, "kernel_ms": kernel_ms, "kernel_timing": kernel_how,
                      "flop_per_entry": flop_per_entry * mult, "entries_per_s": achieved,
                      "peak_source": "of measured: tensor = bf16 sustained (MEASURED_PEAKS.json) / 2 for TF32; exp = "
                                     "ex2.approx rate from fs_micro_exp_rate(0,32) on this GPU"})
@@ -642,7 +674,10 @@ def main():
                        "ms_per_100iter_solve": ms_solve,
                        "ms_per_100iter_solve_note": "one OT(x,y) solve, debias off, last_extrapolation off "
                                                     f"({iters + 1} Jacobi steps), timed directly",
-                       "apply_plan_mat_ms": apply_ms},
+                       "apply_plan_mat_ms": apply_ms,
+                       # results of the last step, so that N-GPU and 1-GPU runs can be compared from the records
+                       "loss": loss_val, "grad_x_abs_sum": float(gx.double().abs().sum().item()),
+                       "grad_x_norm": float(gx.double().norm().item())},
             "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "entries/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": x_host.numel() * 4 + y_host.numel() * 4,
                     "d2h_bytes_per_step": gx_host.numel() * 4 + 4},

@@ -51,6 +51,7 @@ SIGNATURES = {
     "fs_micro_mma_cycles": (c_double, [c_int, c_int]),
     "fs_set_reserved_sms": (c_int, [c_int]),
     "fs_set_cta_limit": (c_int, [c_int]),
+    "fs_engine": (c_int, [c_int, c_int, c_int, c_int]),
     "fs_plan_ctas": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "fs_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "fs_workspace_bytes_labels": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
@@ -72,6 +73,7 @@ SIGNATURES = {
          c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
          c_int, _P, c_size_t, _P],
     ),
+    "fs_symmetric_step_multi": (c_int, [_P, c_int, c_int, c_int, _P]),
     "fs_grad_range": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float,
@@ -243,6 +245,18 @@ class LabelCost:
                          label_y.to(dtype=torch.int32, device=device).contiguous(),
                          label_cost_matrix.to(dtype=torch.float32, device=device).contiguous(),
                          lambda_x, lambda_y)
+
+
+class StepItem(ctypes.Structure):
+    """``fs_step_item`` of the C header (one row-sharded Jacobi step of one problem)."""
+
+    _fields_ = [("x", c_void_p), ("y", c_void_p), ("n", c_int), ("m", c_int),
+                ("f_hat", c_void_p), ("g_hat", c_void_p), ("log_a", c_void_p), ("log_b", c_void_p),
+                ("f_out", c_void_p), ("g_out", c_void_p), ("alpha_x", c_void_p), ("beta_y", c_void_p),
+                ("eps", c_float), ("w", c_float), ("damp_f", c_float), ("damp_g", c_float), ("cost_scale", c_float),
+                ("f_begin", c_int), ("f_end", c_int), ("g_begin", c_int), ("g_end", c_int), ("restage", c_int),
+                ("ws", c_void_p), ("ws_bytes", c_size_t),
+                ("f_shard", c_int), ("g_shard", c_int), ("pack_stride", c_int)]
 
 
 def stream_ptr(device: torch.device) -> int:

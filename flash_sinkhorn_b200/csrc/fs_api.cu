@@ -376,6 +376,11 @@ int fs_device_error(void) { return tc::read_error_flag(); }
 
 int fs_set_cta_limit(int k) { return tc::set_cta_limit(k); }
 
+int fs_engine(int n, int m, int d, int prec) {
+  if (prec == FS_PREC_SIMT || !tc::supported(n, m, d, prec, 0)) return 0;
+  return tc::k_streamed(d, prec, 0) ? 2 : 1;
+}
+
 int fs_plan_ctas(int n_row_blocks, int n_col_tiles, int sms, int reserved, int limit) {
   return tc::plan_ctas(n_row_blocks, n_col_tiles, sms, reserved, limit);
 }
@@ -855,6 +860,95 @@ extern "C" int fs_symmetric_step_range_tiles(const float* x, const float* y, int
   if (beta_y && damp_g < 1.f) { eg.shift = beta_y; eg.shiftcoef = w * (1.f - damp_g); }
   if (f_end > f_begin) FS_CUDA(p.lse(0, g_hat, log_b, eps, ef));
   if (g_end > g_begin) FS_CUDA(p.lse(1, f_hat, log_a, eps, eg));
+  return FS_OK;
+}
+
+extern "C" int fs_symmetric_step_multi(const fs_step_item* items, int n_items, int d, int prec, void* stream) {
+  constexpr int kMaxItems = 8;
+  if (!items || n_items <= 0 || n_items > kMaxItems)
+    return fail(FS_ERR_BAD_ARG, "fs_symmetric_step_multi takes 1..%d items", kMaxItems);
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Problem probs[kMaxItems];
+  tc::MultiPass passes[2 * kMaxItems];
+  int n_pass = 0;
+  bool all_tc = true;
+  for (int i = 0; i < n_items; ++i) {
+    const fs_step_item& it = items[i];
+    FS_TRY(check_common(it.x, it.y, it.n, it.m, d, it.eps, it.cost_scale, prec));
+    if (!it.f_hat || !it.g_hat || !it.log_a || !it.log_b || !it.f_out || !it.g_out)
+      return fail(FS_ERR_BAD_ARG, "item %d: potentials, log-weights and outputs must be non-null", i);
+    if (it.f_out == it.f_hat || it.g_out == it.g_hat)
+      return fail(FS_ERR_BAD_ARG, "item %d: outputs must not alias the inputs (Jacobi step)", i);
+    if (it.f_begin < 0 || it.f_end > it.n || it.g_begin < 0 || it.g_end > it.m || it.f_begin > it.f_end ||
+        it.g_begin > it.g_end)
+      return fail(FS_ERR_BAD_ARG, "item %d: row ranges must satisfy 0 <= begin <= end <= rows", i);
+    // Packed potentials: element j of f_hat lives at f_hat[(j / f_shard) * pack_stride + j % f_shard] (same for
+    // g_hat, f_out, g_out). The rows a pass produces lie inside ONE shard, so for them - the old values that are
+    // averaged in, the outputs - the packed vector is an ordinary contiguous one behind a shifted pointer.
+    const bool packed = it.f_shard > 0 || it.g_shard > 0;
+    if (packed && (it.f_shard <= 0 || it.g_shard <= 0 || it.pack_stride <= 0))
+      return fail(FS_ERR_BAD_ARG, "item %d: packed potentials need f_shard, g_shard and pack_stride > 0", i);
+    if (packed && ((it.f_end > it.f_begin && (it.f_end - 1) / it.f_shard != it.f_begin / it.f_shard) ||
+                   (it.g_end > it.g_begin && (it.g_end - 1) / it.g_shard != it.g_begin / it.g_shard)))
+      return fail(FS_ERR_BAD_ARG, "item %d: a row range must lie inside one shard of the packed layout", i);
+    auto rows_alias = [&](const float* base, int shard, int begin) -> const float* {
+      if (!packed || !base) return base;
+      const long long q = begin / shard;
+      return base + q * it.pack_stride - q * shard;
+    };
+    Ws ws(it.ws, it.ws_bytes);
+    Problem& p = probs[i];
+    FS_TRY(make_problem(p, ws, it.x, it.y, it.n, it.m, d, it.cost_scale, prec, st, false, 0, it.restage != 0));
+    if (packed && !p.use_tc)
+      return fail(FS_ERR_UNSUPPORTED, "item %d: packed potentials are read by the tensor-core engine only", i);
+    p.row_lo[0] = it.f_begin; p.row_hi[0] = it.f_end;
+    p.row_lo[1] = it.g_begin; p.row_hi[1] = it.g_end;
+    all_tc = all_tc && p.use_tc;
+    for (int side = 0; side < 2; ++side) {
+      const int lo = side == 0 ? it.f_begin : it.g_begin, hi = side == 0 ? it.f_end : it.g_end;
+      if (hi <= lo) continue;
+      tc::MultiPass& mp = passes[n_pass++];
+      mp.s = &p.staged;
+      mp.side = side;
+      mp.a = p.stream_args(side, side == 0 ? it.g_hat : it.f_hat, side == 0 ? it.log_b : it.log_a, it.eps);
+      LseEpilogue ep;
+      const float damp = side == 0 ? it.damp_f : it.damp_g;
+      const float* shift = side == 0 ? it.alpha_x : it.beta_y;
+      const int shard = side == 0 ? it.f_shard : it.g_shard;
+      ep.damping = damp; ep.w = it.w;
+      ep.old = rows_alias(side == 0 ? it.f_hat : it.g_hat, shard, lo);
+      ep.out = const_cast<float*>(rows_alias(side == 0 ? it.f_out : it.g_out, shard, lo));
+      if (packed) {  // the column potential of this pass is the OTHER side's packed vector
+        mp.a.pot_shard = side == 0 ? it.g_shard : it.f_shard;
+        mp.a.pot_stride = it.pack_stride;
+      }
+      if (shift && damp < 1.f) { ep.shift = shift; ep.shiftcoef = it.w * (1.f - damp); }
+      mp.e = ep;
+    }
+  }
+  // Groups of passes share a launch when the tensor-core engine takes them that way; otherwise one by one.
+  const int group = tc::multi_max();
+  for (int k0 = 0; k0 < n_pass; k0 += group) {
+    const int cnt = n_pass - k0 < group ? n_pass - k0 : group;
+    cudaError_t e = all_tc ? tc::lse_multi(passes + k0, cnt, st) : cudaErrorNotSupported;
+    if (e == cudaSuccess) {
+      g_launches.fetch_add(2, std::memory_order_relaxed);
+      continue;
+    }
+    if (e != cudaErrorNotSupported)
+      return fail(FS_ERR_CUDA, "multi-pass launch failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    for (int k = k0; k < k0 + cnt; ++k) {
+      const tc::MultiPass& mp = passes[k];
+      const Problem* owner = nullptr;
+      for (int i = 0; i < n_items; ++i)
+        if (&probs[i].staged == mp.s) owner = &probs[i];
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      // (the stream arguments carry the packed-potential addressing, so they are passed on as they are)
+      FS_CUDA(owner->use_tc ? tc::lse(*mp.s, mp.side, mp.a, mp.e, st) : simt_lse(mp.a, mp.e, st));
+    }
+  }
   return FS_OK;
 }
 

@@ -32,6 +32,10 @@ struct StreamArgs {
   int row_begin = 0;            // only rows [row_begin, nr) are produced (row sharding); nr = end of the range
   const float* pot = nullptr;   // [nc]
   const float* logw = nullptr;  // [nc] or nullptr
+  // Packed potentials (tensor-core engine only): when pot_shard > 0, element j of the potential is at
+  // pot[(j / pot_shard) * pot_stride + j % pot_shard] (slices of several vectors gathered from the ranks of a
+  // multi-GPU solve into one [ranks, pot_stride] buffer).
+  int pot_shard = 0, pot_stride = 0;
   float eps = 1.f, cost_scale = 1.f;
   // Block-sparse tile list over 128x128 (row-tile, col-tile) pairs, CSR by row tile; nullptr = dense.
   const int* tile_row_ptr = nullptr;

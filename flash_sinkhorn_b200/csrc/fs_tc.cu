@@ -40,24 +40,23 @@ __device__ int g_tc_error = 0;  // non-zero once any bounded wait gave up (read 
 
 namespace {
 
-struct KernelParams {
+// One streaming pass of a launch ("sub-pass"): rows [row_begin, nr) of one cloud against all columns of the other.
+struct SubPass {
+  CUtensorMap mapA_full, mapA_tail, mapB_full, mapB_tail;
   int nr, nc;        // end of the row range / valid columns
   int row_begin;     // first row of the range (row sharding)
   int ntiles;        // column tiles of BN
-  int nfull, ntail;  // K blocks: nfull of 32 floats (128B swizzle) + ntail of 8 floats (32B swizzle)
-  int nstage;
+  int nblk;          // row blocks of BM rows
+  int item0;         // index of this pass's first (row block, column tile) item in the launch's item list
   float scale2;      // 2*cs*log2e/eps: logit = scale2 * S
   float eps;
   LseEpilogue ep;
-  // Work split: the nblk x ntiles (row block, column tile) items are laid out row block after row block
-  // and cut into gridDim.x equal contiguous ranges, one per CTA (one CTA per SM, a single wave). A CTA's
-  // range may end one row block and begin the next; a row block shared by several CTAs gets one partial
-  // (scale2*max, sum) pair per row from each, and the last of them to finish merges the pairs.
-  int nblk;
+  // Partial (scale2*max, sum) pairs of row blocks that several CTAs share, and one arrival counter per row
+  // block (zero between launches). Passes of one launch never share these.
   float* part_m;
   float* part_s;
   int part_stride;
-  int* tickets;  // one counter per row block, zero between launches
+  int* tickets;
   int* out_idx;  // AM kernels: arg-max column per row (values go to ep.out, multiplied by scale2)
   // CSR kernels: block-sparse list of kept (128-row block, 128-column tile) pairs. csr_rp points at the entry
   // of the first row block of this launch's row range (nblk + 1 entries are read), csr_ci is the whole
@@ -65,6 +64,21 @@ struct KernelParams {
   const int* csr_rp;
   const int* csr_ci;
 };
+
+// A launch = up to NSUB passes over operands of the same shape class (same K blocks, tile shape and ring depth).
+// Work split: the (row block, column tile) items of all passes, pass after pass and row block after row block,
+// are cut into gridDim.x equal contiguous ranges, one per CTA (one CTA per SM, a single wave). A CTA's range may
+// end one row block and begin the next (also of the next pass); a row block shared by several CTAs gets one
+// partial pair per row from each, and the last of them to finish merges the pairs.
+template <int NSUB>
+struct Launch {
+  int nsub;
+  int nfull, ntail;  // K blocks: nfull of 32 floats (128B swizzle) + ntail of 8 floats (32B swizzle)
+  int nstage;
+  long long total;   // items of all passes (dense passes: sum of nblk * ntiles)
+  SubPass sub[NSUB];
+};
+constexpr int kMaxSub = 4;  // passes per multi-pass launch (keeps the kernel parameters under 4 KB)
 
 // Soft-max warpgroups per 128-row half: each takes half of every tile's 32-column chunks (more warps per
 // scheduler to hide the fixed latencies around the chunk max / rescale); their partials merge at the end.
@@ -74,18 +88,21 @@ constexpr int kParts = 2;
 // raw scores and the smallest column attaining it (hard c-transform); no exponentials at all.
 // CSR = true: the item list is the list of kept tiles (row block after row block, NHALF = 1, BN = 128) instead
 // of all nblk x ntiles pairs; everything else - contiguous ranges per CTA, segments, ticketed merge - is the same.
-template <int NHALF, int BN, bool AM, bool CSR = false>
+// NSUB > 1: several dense passes in one launch (no arg-max, no tile list, no device-side early-stop flag).
+template <int NHALF, int BN, bool AM, bool CSR = false, int NSUB = 1>
 __global__ void __launch_bounds__(128 + 128 * NHALF * kParts, 1)
-tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constant__ CUtensorMap mapA_tail,
-              const __grid_constant__ CUtensorMap mapB_full, const __grid_constant__ CUtensorMap mapB_tail,
-              const KernelParams p) {
+tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int BM = 128 * NHALF;
   // This CTA's items [w_begin, w_end) of the flattened (row block, column tile) list.
   static_assert(!CSR || (NHALF == 1 && BN == 128 && !AM), "tile lists are over 128 x 128 tiles");
+  static_assert(NSUB == 1 || (!CSR && !AM), "multi-pass launches are dense soft-min passes");
+  int sub = 0;  // pass of the segment this thread's role is working on (always 0 when NSUB == 1)
+  auto SP = [&]() -> const SubPass& { return P.sub[NSUB == 1 ? 0 : sub]; };
+  const SubPass& p = P.sub[0];  // single-pass code paths (CSR, arg-max, early-stop flag) read pass 0
   const int rp0 = CSR ? p.csr_rp[0] : 0;
-  const long long total_items = CSR ? (long long)(p.csr_rp[p.nblk] - rp0) : (long long)p.nblk * p.ntiles;
+  const long long total_items = CSR ? (long long)(p.csr_rp[p.nblk] - rp0) : P.total;
   // CTAs that share the items. A sparse list may hold few tiles per CTA; G is then lowered so that a row block
   // (at most ntiles items) is never cut into more pieces than there are partial slots (16).
   int G = (int)gridDim.x;
@@ -99,10 +116,17 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   const int w_begin = has_work ? (int)((total_items * blockIdx.x) / G) : 0;
   const int w_end = has_work ? (int)((total_items * (blockIdx.x + 1)) / G) : 0;
   // Items of row block b are [row_start(b), row_end(b)); blk_of(w) = row block holding item w.
-  auto row_start = [&](int b) { return CSR ? p.csr_rp[b] - rp0 : b * p.ntiles; };
-  auto row_end = [&](int b) { return CSR ? p.csr_rp[b + 1] - rp0 : (b + 1) * p.ntiles; };
+  // (b counts the row blocks of the current pass; blk_of and next_blk also move `sub` to the pass of the item.)
+  auto row_start = [&](int b) { return CSR ? p.csr_rp[b] - rp0 : SP().item0 + b * SP().ntiles; };
+  auto row_end = [&](int b) { return CSR ? p.csr_rp[b + 1] - rp0 : SP().item0 + (b + 1) * SP().ntiles; };
   auto blk_of = [&](int w) {
-    if (!CSR) return w / p.ntiles;
+    if (!CSR) {
+      if (NSUB > 1) {
+        sub = 0;
+        while (sub + 1 < P.nsub && P.sub[sub + 1].item0 <= w) ++sub;
+      }
+      return (w - SP().item0) / SP().ntiles;
+    }
     int lo = 0, hi = p.nblk - 1;  // smallest b with row_end(b) > w
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
@@ -110,12 +134,16 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     }
     return lo;
   };
-  auto next_blk = [&](int b, int w) {  // row block of item w, known to lie after row block b
+  auto next_blk = [&](int b, int w) {  // row block of item w, the first item after row block b
     ++b;
     if (CSR) while (row_end(b) <= w) ++b;
+    if (NSUB > 1 && b == SP().nblk) {  // dense passes have no empty row block: w opens the next pass
+      ++sub;
+      b = 0;
+    }
     return b;
   };
-  auto col_of = [&](int w, int b) { return CSR ? p.csr_ci[rp0 + w] : w - b * p.ntiles; };
+  auto col_of = [&](int w, int b) { return CSR ? p.csr_ci[rp0 + w] : w - row_start(b); };
   // First item of CTA c; CTA holding item t (largest c whose first item is <= t).
   auto cta_first = [&](int c) { return (int)((total_items * c) / G); };
   auto cta_of = [&](int t) {
@@ -125,22 +153,22 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     return c;
   };
 
-  if (p.ep.ctrl && p.ep.ctrl->converged) {  // solve already stopped: identity step
-    if (p.ep.old && p.ep.out)
-      for (int r = p.row_begin + blockIdx.x * blockDim.x + tid; r < p.nr; r += gridDim.x * blockDim.x)
-        p.ep.out[r] = p.ep.old[r];
+  if (NSUB == 1 && SP().ep.ctrl && SP().ep.ctrl->converged) {  // solve already stopped: identity step
+    if (SP().ep.old && SP().ep.out)
+      for (int r = SP().row_begin + blockIdx.x * blockDim.x + tid; r < SP().nr; r += gridDim.x * blockDim.x)
+        SP().ep.out[r] = SP().ep.old[r];
     return;
   }
 
   // ---- shared memory carve-up (all operand blocks 1024-byte aligned) ----
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t a_half_bytes = p.nfull * (128 * 128) + p.ntail * (128 * 32);
-  const uint32_t b_stage_bytes = p.nfull * (BN * 128) + p.ntail * (BN * 32);
+  const uint32_t a_half_bytes = P.nfull * (128 * 128) + P.ntail * (128 * 32);
+  const uint32_t b_stage_bytes = P.nfull * (BN * 128) + P.ntail * (BN * 32);
   uint8_t* a_smem = base;
   uint8_t* b_smem = a_smem + NHALF * a_half_bytes;
-  uint64_t* bars = (uint64_t*)(b_smem + p.nstage * b_stage_bytes);
+  uint64_t* bars = (uint64_t*)(b_smem + P.nstage * b_stage_bytes);
   // barrier indices
-  const int B_FULL = 0, B_EMPTY = p.nstage, S_FULL = 2 * p.nstage, S_EMPTY = S_FULL + 2 * NHALF,
+  const int B_FULL = 0, B_EMPTY = P.nstage, S_FULL = 2 * P.nstage, S_EMPTY = S_FULL + 2 * NHALF,
             A_FULL = S_EMPTY + 2 * NHALF, A_EMPTY = A_FULL + 1, DRAIN = A_EMPTY + 1, NBARS = DRAIN + 2;
   uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -152,7 +180,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
   constexpr uint32_t kTmemCols = (2 * NHALF * BN) < 32 ? 32 : (2 * NHALF * BN);
 
   if (tid == 0) {
-    for (int s = 0; s < p.nstage; ++s) {
+    for (int s = 0; s < P.nstage; ++s) {
       mbar_init(bar(B_FULL + s), 1);
       mbar_init(bar(B_EMPTY + s), NHALF);  // one commit per MMA-issuing lane (one lane per 128-row half)
     }
@@ -184,16 +212,16 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       bool ok = true;
       // Column tile `issued` (a CTA-wide running index) of the segment that starts at item w0.
       auto load_b = [&](int j) -> bool {
-        const int s = issued % p.nstage;
-        const uint32_t ph = (issued / p.nstage) & 1;
+        const int s = issued % P.nstage;
+        const uint32_t ph = (issued / P.nstage) & 1;
         if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 2000)) return false;
         mbar_expect_tx(bar(B_FULL + s), b_stage_bytes);
         uint32_t dst = smem_u32(b_smem + s * b_stage_bytes);
         const int col0 = j * BN;
-        for (int kb = 0; kb < p.nfull; ++kb)
-          tma_load_2d(dst + kb * (BN * 128), &mapB_full, kb * 32, col0, bar(B_FULL + s));
-        for (int t = 0; t < p.ntail; ++t)
-          tma_load_2d(dst + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, col0,
+        for (int kb = 0; kb < P.nfull; ++kb)
+          tma_load_2d(dst + kb * (BN * 128), &SP().mapB_full, kb * 32, col0, bar(B_FULL + s));
+        for (int t = 0; t < P.ntail; ++t)
+          tma_load_2d(dst + P.nfull * (BN * 128) + t * (BN * 32), &SP().mapB_tail, P.nfull * 32 + t * 8, col0,
                       bar(B_FULL + s));
         ++issued;
         return true;
@@ -204,17 +232,17 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
 #pragma unroll 1
       for (int w = w_begin; ok && w < w_end; ++seg) {
         const int seg_end = row_end(blk) < w_end ? row_end(blk) : w_end;
-        const int row0 = p.row_begin + blk * BM;
+        const int row0 = SP().row_begin + blk * BM;
         // The row operand of the previous segment must have been read by its last MMA.
         if (!mbar_wait(bar(A_EMPTY), (seg & 1) ^ 1, abort_flag, 2000)) break;
         mbar_expect_tx(bar(A_FULL), NHALF * a_half_bytes);
 #pragma unroll 1
         for (int h = 0; h < NHALF; ++h) {
           uint32_t dst = smem_u32(a_smem + h * a_half_bytes);
-          for (int kb = 0; kb < p.nfull; ++kb)
-            tma_load_2d(dst + kb * (128 * 128), &mapA_full, kb * 32, row0 + h * 128, bar(A_FULL));
-          for (int t = 0; t < p.ntail; ++t)
-            tma_load_2d(dst + p.nfull * (128 * 128) + t * (128 * 32), &mapA_tail, p.nfull * 32 + t * 8,
+          for (int kb = 0; kb < P.nfull; ++kb)
+            tma_load_2d(dst + kb * (128 * 128), &SP().mapA_full, kb * 32, row0 + h * 128, bar(A_FULL));
+          for (int t = 0; t < P.ntail; ++t)
+            tma_load_2d(dst + P.nfull * (128 * 128) + t * (128 * 32), &SP().mapA_tail, P.nfull * 32 + t * 8,
                         row0 + h * 128, bar(A_FULL));
         }
 #pragma unroll 1
@@ -227,15 +255,15 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         if (ok && w < w_end) {
           blk = next_blk(blk, w);
           const int nnext = (row_end(blk) < w_end ? row_end(blk) : w_end) - w;
-          const int npre = nnext < p.nstage ? nnext : p.nstage;
+          const int npre = nnext < P.nstage ? nnext : P.nstage;
 #pragma unroll 1
           for (; ok && pre < npre; ++pre) ok = load_b(col_of(w + pre, blk));
         }
       }
       if (*abort_flag) {  // let every copy we issued land before the CTA goes away
         if (seg > 0) mbar_wait_quiet(bar(A_FULL), (seg - 1) & 1);
-        for (int j = (issued > p.nstage ? issued - p.nstage : 0); j < issued; ++j)
-          mbar_wait_quiet(bar(B_FULL + j % p.nstage), (j / p.nstage) & 1);
+        for (int j = (issued > P.nstage ? issued - P.nstage : 0); j < issued; ++j)
+          mbar_wait_quiet(bar(B_FULL + j % P.nstage), (j / P.nstage) & 1);
       }
     }
   } else if (warp == 1 || (warp == 3 && NHALF == 2)) {
@@ -258,8 +286,8 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
         tc_fence_after();
 #pragma unroll 1
         for (int i = 0; i < nseg; ++i, ++jt) {
-          const int s = jt % p.nstage;
-          const uint32_t ph = (jt / p.nstage) & 1;
+          const int s = jt % P.nstage;
+          const uint32_t ph = (jt / P.nstage) & 1;
           if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
           const int buf = jt & 1;
           const uint32_t sph = (jt >> 1) & 1;
@@ -272,7 +300,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
           uint32_t al = a_lo0, bl = desc_lo(smem_u32(b_smem + s * b_stage_bytes));
           uint32_t acc = 0;
 #pragma unroll 1
-          for (int kb = 0; kb < p.nfull; ++kb) {
+          for (int kb = 0; kb < P.nfull; ++kb) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
               umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
@@ -282,7 +310,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
             bl += (BN * 128) >> 4;
           }
 #pragma unroll 1
-          for (int t = 0; t < p.ntail; ++t) {
+          for (int t = 0; t < P.ntail; ++t) {
             umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc, acc);
             acc = 1;
             al += (128 * 32) >> 4;
@@ -307,7 +335,9 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     const int part = wg % kParts;        // which half of each tile's chunks
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const float scale = p.scale2;
+    // (the soft-max warps set `sub` with blk_of(w_begin) below, before the first chunk is consumed)
+    if (has_work) blk_of(w_begin);
+    float scale = SP().scale2;  // logit scale of the current segment's pass
     // off_run is the fp32 exponent offset all terms of s_run are relative to: sum = s_run * 2^off_run.
     // It is carried as the ROUNDED value scale*max (not recomputed from the max), so that rescaling by
     // 2^(off_old - off_new) and the final off_run + log2(s_run) are exact identities in fp32.
@@ -386,10 +416,10 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     };
     // Epilogue of a finished row: raw log2 normaliser and / or the damped, averaged potential update.
     auto store_lse = [&](int r, float lse2) {
-      const LseEpilogue& ep = p.ep;
+      const LseEpilogue& ep = SP().ep;
       if (ep.lse2) ep.lse2[r] = lse2;
       if (ep.out) {
-        float cand = -p.eps * ep.damping * (lse2 * kLn2);
+        float cand = -SP().eps * ep.damping * (lse2 * kLn2);
         float o = ep.w * cand;
         if (ep.old) o += (1.0f - ep.w) * ep.old[r];
         if (ep.shift) o -= ep.shiftcoef * ep.shift[r];
@@ -402,8 +432,8 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     if (CSR && part == 0) {
 #pragma unroll 1
       for (int b = blockIdx.x; b < p.nblk; b += gridDim.x) {
-        const int r = p.row_begin + b * BM + h * 128 + q * 32 + lane;
-        if (row_end(b) == row_start(b) && r < p.nr) store_lse(r, -INFINITY);
+        const int r = SP().row_begin + b * BM + h * 128 + q * 32 + lane;
+        if (row_end(b) == row_start(b) && r < SP().nr) store_lse(r, -INFINITY);
       }
     }
     // End of a segment (the part of one row block this CTA covers): merge the two column parts, then either
@@ -412,7 +442,7 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     // depend on which CTA that is - and applies the epilogue. Every soft-max warp runs the same barrier
     // sequence for every segment, also after an abort (live = false), so the named barriers always match.
     auto finalize = [&](int blk, bool live) {
-      const int r = p.row_begin + blk * BM + h * 128 + q * 32 + lane;
+      const int r = SP().row_begin + blk * BM + h * 128 + q * 32 + lane;
       // AM: a partial is (maximum, column); the larger maximum wins, equal maxima keep the smaller column.
       auto better = [](float va, int ia, float vb, int ib) { return vb > va || (vb == va && ib < ia); };
       if (part == 1) {  // second column part parks its partial in shared memory
@@ -434,47 +464,47 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
       const int pieces = c_hi - c_lo + 1, piece = (int)blockIdx.x - c_lo;
       bool finish = pieces == 1;
       if (pieces > 1) {
-        if (live && part == 0 && r < p.nr) {
-          p.part_m[(size_t)piece * p.part_stride + r] = AM ? m_run : off_run;
-          p.part_s[(size_t)piece * p.part_stride + r] = AM ? __int_as_float(idx_run) : s_run;
+        if (live && part == 0 && r < SP().nr) {
+          SP().part_m[(size_t)piece * SP().part_stride + r] = AM ? m_run : off_run;
+          SP().part_s[(size_t)piece * SP().part_stride + r] = AM ? __int_as_float(idx_run) : s_run;
         }
         __threadfence();  // the pairs must be visible device-wide before the ticket is taken
         asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
-        if (warp == 4 && lane == 0) *last_flag = (atomicAdd(p.tickets + blk, 1) == pieces - 1) ? 1 : 0;
+        if (warp == 4 && lane == 0) *last_flag = (atomicAdd(SP().tickets + blk, 1) == pieces - 1) ? 1 : 0;
         asm volatile("bar.sync 1, %0;" ::"n"(128 * NHALF * kParts) : "memory");
         finish = *last_flag != 0;
         if (finish) {
           __threadfence();
-          if (part == 0 && r < p.nr) {
-            float M = __ldcg(p.part_m + r);
+          if (part == 0 && r < SP().nr) {
+            float M = __ldcg(SP().part_m + r);
             if (AM) {
-              int I = __float_as_int(__ldcg(p.part_s + r));
+              int I = __float_as_int(__ldcg(SP().part_s + r));
               for (int c = 1; c < pieces; ++c) {
-                const float vc = __ldcg(p.part_m + (size_t)c * p.part_stride + r);
-                const int ic = __float_as_int(__ldcg(p.part_s + (size_t)c * p.part_stride + r));
+                const float vc = __ldcg(SP().part_m + (size_t)c * SP().part_stride + r);
+                const int ic = __float_as_int(__ldcg(SP().part_s + (size_t)c * SP().part_stride + r));
                 if (better(M, I, vc, ic)) { M = vc; I = ic; }
               }
               m_run = M;
               idx_run = I;
             } else {
-              for (int c = 1; c < pieces; ++c) M = fmaxf(M, __ldcg(p.part_m + (size_t)c * p.part_stride + r));
+              for (int c = 1; c < pieces; ++c) M = fmaxf(M, __ldcg(SP().part_m + (size_t)c * SP().part_stride + r));
               float S = 0.f;
               for (int c = 0; c < pieces; ++c)
-                S += __ldcg(p.part_s + (size_t)c * p.part_stride + r) *
-                     ex2(__ldcg(p.part_m + (size_t)c * p.part_stride + r) - M);
+                S += __ldcg(SP().part_s + (size_t)c * SP().part_stride + r) *
+                     ex2(__ldcg(SP().part_m + (size_t)c * SP().part_stride + r) - M);
               off_run = M;
               s_run = S;
             }
           }
-          if (warp == 4 && lane == 0) p.tickets[blk] = 0;  // ready for the next launch on this stream
+          if (warp == 4 && lane == 0) SP().tickets[blk] = 0;  // ready for the next launch on this stream
         }
       }
       if (AM) {
-        if (finish && live && part == 0 && r < p.nr && !*abort_flag) {
-          p.ep.out[r] = p.scale2 * m_run;  // scale2 = -2*cost_scale turns the maximal score into the minimal cost
-          p.out_idx[r] = idx_run;
+        if (finish && live && part == 0 && r < SP().nr && !*abort_flag) {
+          SP().ep.out[r] = SP().scale2 * m_run;  // scale2 = -2*cost_scale turns the maximal score into the minimal cost
+          SP().out_idx[r] = idx_run;
         }
-      } else if (finish && live && part == 0 && r < p.nr && !*abort_flag) {
+      } else if (finish && live && part == 0 && r < SP().nr && !*abort_flag) {
         store_lse(r, off_run + log2f(fmaxf(s_run, 1e-40f)));
       }
       // merge_off / merge_sum / last_flag are re-used by the next segment
@@ -489,7 +519,13 @@ tc_lse_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_consta
     auto seg_len = [&]() { return (row_end(seg_blk) < w_end ? row_end(seg_blk) : w_end) - seg_w; };
     auto next_seg = [&]() {  // step to the segment after the current one (if any)
       seg_w += seg_len();
-      if (seg_w < w_end) seg_blk = next_blk(seg_blk, seg_w);
+      if (seg_w < w_end) {
+        seg_blk = next_blk(seg_blk, seg_w);
+        if (NSUB > 1) {  // the next segment may belong to another pass, with its own logit scale
+          scale = SP().scale2;
+          off_run = __fmul_rn(scale, kRunInit);
+        }
+      }
     };
     int seg_end_g = has_work ? seg_len() * CH : 0;
     auto consumed = [&](int g) {  // chunk g has been folded in: close the segment if it was its last chunk
@@ -947,12 +983,14 @@ __global__ void stage_kernel(const float* __restrict__ src, int rows, int rows_p
 
 // Writes the bias of a pass, divided by the logit scale and split into 3 TF32 pieces, into opB's aug columns.
 __global__ void bias_kernel(float* __restrict__ opB, int rows, int kc, int kp, const float* __restrict__ pot,
-                            const float* __restrict__ logw, float inv_eps, float inv_scale2, const Ctrl* ctrl) {
+                            const float* __restrict__ logw, float inv_eps, float inv_scale2, const Ctrl* ctrl,
+                            int pot_shard = 0, int pot_stride = 0) {
   if (ctrl && ctrl->converged) return;
   int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
+  const float pr = pot_shard > 0 ? pot[(size_t)(r / pot_shard) * pot_stride + r % pot_shard] : pot[r];
   // bias in log2 units, same association as the reference kernels, then / scale2
-  float b2 = logw ? (pot[r] * (inv_eps * kLog2e) + logw[r] * kLog2e) : pot[r] * kLog2e;
+  float b2 = logw ? (pr * (inv_eps * kLog2e) + logw[r] * kLog2e) : pr * kLog2e;
   float b = b2 * inv_scale2;
   float hi = to_tf32(b);
   float r1 = b - hi;
@@ -1032,15 +1070,41 @@ Shape plan_shape_csr(int d, int prec, int nlab) {
   return s;
 }
 
-template <int NHALF, int BN, bool AM, bool CSR = false>
-cudaError_t launch(const CUtensorMap& ma_f, const CUtensorMap& ma_t, const CUtensorMap& mb_f,
-                   const CUtensorMap& mb_t, const KernelParams& kp, dim3 grid, size_t smem, cudaStream_t st) {
-  auto kern = tc_lse_kernel<NHALF, BN, AM, CSR>;
+template <int NHALF, int BN, bool AM, bool CSR = false, int NSUB = 1>
+cudaError_t launch(const Launch<NSUB>& lp, dim3 grid, size_t smem, cudaStream_t st) {
+  auto kern = tc_lse_kernel<NHALF, BN, AM, CSR, NSUB>;
   // Per device (context) attribute; cheap enough to set on every launch.
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
   if (e != cudaSuccess) return e;
-  kern<<<grid, 128 + 128 * NHALF * kParts, smem, st>>>(ma_f, ma_t, mb_f, mb_t, kp);
+  kern<<<grid, 128 + 128 * NHALF * kParts, smem, st>>>(lp);
   return cudaGetLastError();
+}
+
+// Bias columns of up to kMaxSub column operands in one launch (blockIdx.y = job).
+struct BiasJobs {
+  struct Job {
+    float* opB;
+    int rows, kc, kp;
+    const float* pot;
+    const float* logw;
+    float inv_eps, inv_scale2;
+    int pot_shard, pot_stride;  // packed potential (see StreamArgs), 0 = contiguous
+  } job[kMaxSub];
+};
+
+__global__ void bias_multi_kernel(const BiasJobs jobs) {
+  const BiasJobs::Job& j = jobs.job[blockIdx.y];
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= j.rows) return;
+  const float pr = j.pot_shard > 0 ? j.pot[(size_t)(r / j.pot_shard) * j.pot_stride + r % j.pot_shard] : j.pot[r];
+  const float b2 = j.logw ? (pr * (j.inv_eps * kLog2e) + j.logw[r] * kLog2e) : pr * kLog2e;
+  const float b = b2 * j.inv_scale2;
+  const float hi = to_tf32(b);
+  const float r1 = b - hi;
+  const float mid = to_tf32(r1);
+  const float lo = to_tf32(r1 - mid);
+  float* row = j.opB + (size_t)r * j.kp + j.kc;
+  row[0] = hi; row[1] = mid; row[2] = lo;
 }
 
 constexpr int kMaxChunks = 16;
@@ -1111,9 +1175,9 @@ int pick_ctas_for(int nblk, int ntiles, int sms, int reserved, int limit) {
 }
 
 void launch_bias(const CloudOps& colc, int kc, int kp, const float* pot, const float* logw, float inv_eps,
-                 float inv_scale2, const Ctrl* ctrl, cudaStream_t st) {
+                 float inv_scale2, const Ctrl* ctrl, cudaStream_t st, int pot_shard, int pot_stride) {
   bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, kc, kp, pot, logw, inv_eps, inv_scale2,
-                                                       ctrl);
+                                                       ctrl, pot_shard, pot_stride);
 }
 
 int pick_ctas(int nblk, int ntiles) {
@@ -1171,8 +1235,8 @@ size_t staged_bytes(int n, int m, int d, int prec, int nlab) {
   size_t b = 0;
   b += 2 * (((size_t)pad256(n) * per_row + 1023) & ~size_t(1023));
   b += 2 * (((size_t)pad256(m) * per_row + 1023) & ~size_t(1023));
-  b += 2 * (size_t)kMaxChunks * pad256(n > m ? n : m) * sizeof(float);  // column-split partials
-  b += (size_t)(pad256(n > m ? n : m) / 128) * sizeof(int);             // row-block tickets
+  b += 2 * 2 * (size_t)kMaxChunks * pad256(n > m ? n : m) * sizeof(float);  // column-split partials, per side
+  b += 2 * (size_t)(pad256(n > m ? n : m) / 128) * sizeof(int);             // row-block tickets, per side
   return b + 1024;
 }
 
@@ -1199,17 +1263,49 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
                                                                     V ? lab->W : nullptr, V, c, w_coef);
   }
   s.part_stride = pad256(n > m ? n : m);
-  s.part_m = reinterpret_cast<float*>(p);
-  s.part_s = s.part_m + (size_t)kMaxChunks * s.part_stride;
-  s.tickets = reinterpret_cast<int*>(s.part_s + (size_t)kMaxChunks * s.part_stride);
+  // Each side has its own partial slots and tickets: the two passes of a Jacobi step may share one launch.
+  const size_t slots = (size_t)kMaxChunks * s.part_stride;
+  float* fp = reinterpret_cast<float*>(p);
+  for (int sd = 0; sd < 2; ++sd) {
+    s.part_m[sd] = fp + (2 * sd) * slots;
+    s.part_s[sd] = fp + (2 * sd + 1) * slots;
+  }
+  int* tk = reinterpret_cast<int*>(fp + 4 * slots);
+  s.tickets[0] = tk;
+  s.tickets[1] = tk + s.part_stride / 128;
   if (run_kernels) {
-    cudaError_t e = cudaMemsetAsync(s.tickets, 0, (size_t)(s.part_stride / 128) * sizeof(int), st);
+    cudaError_t e = cudaMemsetAsync(tk, 0, 2 * (size_t)(s.part_stride / 128) * sizeof(int), st);
     if (e != cudaSuccess) return e;
   }
   return cudaGetLastError();
 }
 
 namespace {
+// Tensor maps and geometry of one pass over staged operands (side 0: rows of x against y, side 1: the reverse).
+// A boxes are 128 rows, B boxes BN rows; when a K-block class is absent its map still has to be a valid object:
+// it is encoded over the first columns (never used by the kernel).
+bool fill_subpass(SubPass& kp, const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, const Shape& sh,
+                  float scale2) {
+  const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
+  const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
+  bool ok = true;
+  ok &= encode_map(&kp.mapA_full, rowc.opA, rowc.rows_pad, sh.kp, sh.nfull ? 32 : 8, 128,
+                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&kp.mapA_tail, rowc.opA, rowc.rows_pad, sh.kp, 8, 128, CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&kp.mapB_full, colc.opB, colc.rows_pad, sh.kp, sh.nfull ? 32 : 8, sh.bn,
+                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
+  ok &= encode_map(&kp.mapB_tail, colc.opB, colc.rows_pad, sh.kp, 8, sh.bn, CU_TENSOR_MAP_SWIZZLE_32B);
+  kp.nr = a.nr; kp.nc = a.nc; kp.row_begin = a.row_begin;
+  kp.ntiles = (a.nc + sh.bn - 1) / sh.bn;
+  const int bm = 128 * sh.nhalf;
+  kp.nblk = (a.nr - a.row_begin + bm - 1) / bm;
+  kp.item0 = 0;
+  kp.scale2 = scale2; kp.eps = a.eps; kp.ep = e;
+  kp.part_m = s.part_m[side]; kp.part_s = s.part_s[side]; kp.part_stride = s.part_stride; kp.tickets = s.tickets[side];
+  kp.out_idx = nullptr; kp.csr_rp = nullptr; kp.csr_ci = nullptr;
+  return ok;
+}
+
 // One streaming pass over the staged operands: LSE (out_idx == nullptr) or running arg-max of the raw scores.
 cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, int* out_idx,
                         cudaStream_t st) {
@@ -1229,46 +1325,89 @@ cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const Ls
                                                          1.0f / (scale2 * kLog2e), nullptr);
   else
     bias_kernel<<<(colc.rows + 255) / 256, 256, 0, st>>>(colc.opB, colc.rows, sh.kc, sh.kp, a.pot, a.logw,
-                                                         1.0f / a.eps, 1.0f / scale2, e.ctrl);
-  CUtensorMap ma_f, ma_t, mb_f, mb_t;
-  // A tensor map boxes are 128 rows; B boxes BN rows. When a K-block class is absent its map
-  // still has to be a valid object: encode it over the first columns (never used by the kernel).
-  bool ok = true;
-  ok &= encode_map(&ma_f, rowc.opA, rowc.rows_pad, sh.kp, sh.nfull ? 32 : 8, 128,
-                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
-  ok &= encode_map(&ma_t, rowc.opA, rowc.rows_pad, sh.kp, 8, 128, CU_TENSOR_MAP_SWIZZLE_32B);
-  ok &= encode_map(&mb_f, colc.opB, colc.rows_pad, sh.kp, sh.nfull ? 32 : 8, sh.bn,
-                   sh.nfull ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B);
-  ok &= encode_map(&mb_t, colc.opB, colc.rows_pad, sh.kp, 8, sh.bn, CU_TENSOR_MAP_SWIZZLE_32B);
-  if (!ok) return cudaErrorInvalidValue;
-  KernelParams kp;
-  kp.nr = a.nr; kp.nc = a.nc; kp.row_begin = a.row_begin;
-  kp.ntiles = (a.nc + sh.bn - 1) / sh.bn;
-  kp.nfull = sh.nfull; kp.ntail = sh.ntail; kp.nstage = sh.nstage;
-  kp.scale2 = scale2; kp.eps = a.eps; kp.ep = e;
-  const int bm = 128 * sh.nhalf;
-  const int nblk = (a.nr - a.row_begin + bm - 1) / bm;
-  if (nblk <= 0) return cudaSuccess;
-  kp.nblk = nblk;
-  kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride; kp.tickets = s.tickets;
+                                                         1.0f / a.eps, 1.0f / scale2, e.ctrl, a.pot_shard, a.pot_stride);
+  Launch<1> lp{};
+  lp.nsub = 1;
+  lp.nfull = sh.nfull; lp.ntail = sh.ntail; lp.nstage = sh.nstage;
+  SubPass& kp = lp.sub[0];
+  if (!fill_subpass(kp, s, side, a, e, sh, scale2)) return cudaErrorInvalidValue;
+  if (kp.nblk <= 0) return cudaSuccess;
+  lp.total = (long long)kp.nblk * kp.ntiles;
   kp.out_idx = out_idx;
   kp.csr_rp = csr ? a.tile_row_ptr + a.row_begin / 128 : nullptr;
   kp.csr_ci = a.tile_col_idx;
-  dim3 grid(pick_ctas(nblk, kp.ntiles));
-  if (csr) return launch<1, 128, false, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  dim3 grid(pick_ctas(kp.nblk, kp.ntiles));
+  if (csr) return launch<1, 128, false, true>(lp, grid, sh.smem, st);
   if (am) {
-    if (sh.nhalf == 2) return launch<2, 128, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-    if (sh.bn == 128) return launch<1, 128, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-    return launch<1, 64, true>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+    if (sh.nhalf == 2) return launch<2, 128, true>(lp, grid, sh.smem, st);
+    if (sh.bn == 128) return launch<1, 128, true>(lp, grid, sh.smem, st);
+    return launch<1, 64, true>(lp, grid, sh.smem, st);
   }
-  if (sh.nhalf == 2) return launch<2, 128, false>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  if (sh.bn == 128) return launch<1, 128, false>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
-  return launch<1, 64, false>(ma_f, ma_t, mb_f, mb_t, kp, grid, sh.smem, st);
+  if (sh.nhalf == 2) return launch<2, 128, false>(lp, grid, sh.smem, st);
+  if (sh.bn == 128) return launch<1, 128, false>(lp, grid, sh.smem, st);
+  return launch<1, 64, false>(lp, grid, sh.smem, st);
 }
 }  // namespace
 
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st) {
   return stream_pass(s, side, a, e, nullptr, st);
+}
+
+int multi_max() { return kMaxSub; }
+
+cudaError_t lse_multi(const MultiPass* passes, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  if (n > kMaxSub || !passes) return cudaErrorInvalidValue;
+  const Staged& s0 = *passes[0].s;
+  const Shape sh = plan_shape(s0.d, s0.prec, s0.nlab);
+  if (!sh.ok || sh.streamed) return cudaErrorNotSupported;
+  Launch<kMaxSub> lp{};
+  BiasJobs jobs{};
+  lp.nfull = sh.nfull; lp.ntail = sh.ntail; lp.nstage = sh.nstage;
+  int used = 0, max_cols = 0;
+  long long total = 0;
+  for (int i = 0; i < n; ++i) {
+    const MultiPass& mp = passes[i];
+    const Staged& s = *mp.s;
+    if (s.d != s0.d || s.prec != s0.prec || s.nlab != s0.nlab || s.kp != s0.kp) return cudaErrorNotSupported;
+    if (mp.a.tile_row_ptr || mp.e.ctrl) return cudaErrorNotSupported;
+    if (mp.a.nr <= mp.a.row_begin) continue;  // empty row range
+    const float scale2 = (2.0f * mp.a.cost_scale) * (1.0f / mp.a.eps) * kLog2e;
+    SubPass& kp = lp.sub[used];
+    if (!fill_subpass(kp, s, mp.side, mp.a, mp.e, sh, scale2)) return cudaErrorInvalidValue;
+    kp.item0 = (int)total;
+    total += (long long)kp.nblk * kp.ntiles;
+    if (total >= (1ll << 31)) return cudaErrorNotSupported;
+    const CloudOps& colc = s.cloud[mp.side == 0 ? 1 : 0];
+    BiasJobs::Job& j = jobs.job[used];
+    j.opB = colc.opB; j.rows = colc.rows; j.kc = sh.kc; j.kp = sh.kp;
+    j.pot = mp.a.pot; j.logw = mp.a.logw; j.inv_eps = 1.0f / mp.a.eps; j.inv_scale2 = 1.0f / scale2;
+    j.pot_shard = mp.a.pot_shard; j.pot_stride = mp.a.pot_stride;
+    if (colc.rows > max_cols) max_cols = colc.rows;
+    // Two passes of one launch must not write the bias columns of the same operand (nor merge in the same
+    // partial slots): that is the same side of the same staged problem twice.
+    for (int k = 0; k < used; ++k)
+      if (lp.sub[k].part_m == kp.part_m) return cudaErrorInvalidValue;
+    ++used;
+  }
+  if (used == 0) return cudaSuccess;
+  lp.nsub = used;
+  lp.total = total;
+  bias_multi_kernel<<<dim3((max_cols + 255) / 256, used), 256, 0, st>>>(jobs);
+  // CTAs: one wave, at least ~4 items each, and no row block cut into more pieces than there are slots.
+  long long g = detail::sm_count() - g_reserved_sms.load(std::memory_order_relaxed);
+  const int limit = g_cta_limit.load(std::memory_order_relaxed);
+  if (g < 1) g = 1;
+  if (limit >= 1 && limit < g) g = limit;
+  if (g > (total + 3) / 4) g = (total + 3) / 4;
+  if (g < 1) g = 1;
+  int max_tiles = 1;
+  for (int k = 0; k < used; ++k) max_tiles = lp.sub[k].ntiles > max_tiles ? lp.sub[k].ntiles : max_tiles;
+  while (g > 1 && (long long)max_tiles * g / total + 2 > kMaxChunks) --g;
+  dim3 grid((unsigned)g);
+  if (sh.nhalf == 2) return launch<2, 128, false, false, kMaxSub>(lp, grid, sh.smem, st);
+  if (sh.bn == 128) return launch<1, 128, false, false, kMaxSub>(lp, grid, sh.smem, st);
+  return launch<1, 64, false, false, kMaxSub>(lp, grid, sh.smem, st);
 }
 
 cudaError_t argmax(const Staged& s, int side, const StreamArgs& a, float* out_val, int* out_idx, cudaStream_t st) {

@@ -23,10 +23,12 @@ struct CloudOps {
 struct Staged {
   CloudOps cloud[2];  // 0 = x, 1 = y
   int d = 0, nlab = 0, kc = 0, kp = 0, prec = 0;  // nlab: label-table columns staged after the coordinates
-  float* part_m = nullptr;  // [pieces, part_stride] partial scaled maxima of row blocks shared by several CTAs
-  float* part_s = nullptr;  // [pieces, part_stride] partial sums
+  // Per side (0: rows of x, 1: rows of y): [pieces, part_stride] partial scaled maxima and sums of row blocks
+  // shared by several CTAs, and [rows_pad / 128] arrival counters of those CTAs (zero at rest).
+  float* part_m[2] = {nullptr, nullptr};
+  float* part_s[2] = {nullptr, nullptr};
   int part_stride = 0;
-  int* tickets = nullptr;   // [rows_pad / 128] per-row-block arrival counters of the CTAs sharing a row block (zero at rest)
+  int* tickets[2] = {nullptr, nullptr};
 };
 
 // Streaming passes leave `k` SMs unused from now on (process-wide; returns the previous value).
@@ -47,6 +49,20 @@ cudaError_t stage(Staged& s, char* buf, const float* x, const float* y, int n, i
                   cudaStream_t st, bool run_kernels = true, const LabelCost* lab = nullptr, float w_coef = 0.f);
 // One LSE pass: side 0 = rows of x against y, side 1 = rows of y against x.
 cudaError_t lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, cudaStream_t st);
+
+// Several dense LSE passes (of one or several staged problems with the same d, precision and label columns) as
+// ONE launch preceded by one bias launch: the (row block, column tile) items of all passes form one list that is
+// cut over the SMs, so the ramp and tail of a launch are paid once per group instead of once per pass. At most
+// multi_max() passes; cudaErrorNotSupported when a pass is K-streamed, carries a tile list or an early-stop flag
+// (the caller then runs the passes one by one).
+struct MultiPass {
+  const Staged* s;
+  int side;
+  StreamArgs a;
+  LseEpilogue e;
+};
+int multi_max();
+cudaError_t lse_multi(const MultiPass* passes, int n, cudaStream_t st);
 
 // Hard c-transform pass over the same staged operands: out_val_i = min_j(-2cs x_i.y_j + bias_j) and the
 // smallest column attaining it (a.pot = bias, a.logw ignored, a.eps unused).
@@ -90,7 +106,7 @@ int sm_count();
 // Writes the column bias of a pass (divided by the logit scale, split into three TF32 pieces) into the bias
 // columns of the column operand.
 void launch_bias(const CloudOps& colc, int kc, int kp, const float* pot, const float* logw, float inv_eps,
-                 float inv_scale2, const Ctrl* ctrl, cudaStream_t st);
+                 float inv_scale2, const Ctrl* ctrl, cudaStream_t st, int pot_shard = 0, int pot_stride = 0);
 inline int pad256(int r) { return (r + 255) & ~255; }
 }  // namespace detail
 

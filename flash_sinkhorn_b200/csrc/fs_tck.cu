@@ -603,7 +603,8 @@ cudaError_t kstream_lse(const Staged& s, int side, const StreamArgs& a, const Ls
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
   const float scale2 = (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;
-  detail::launch_bias(colc, s.kc, s.kp, a.pot, a.logw, 1.0f / a.eps, 1.0f / scale2, e.ctrl, st);
+  detail::launch_bias(colc, s.kc, s.kp, a.pot, a.logw, 1.0f / a.eps, 1.0f / scale2, e.ctrl, st, a.pot_shard,
+                      a.pot_stride);
   KParams kp{};
   set_chunks(kp, s.kp);
   const KPlan k = plan_k(kp.nk, a.nc);
@@ -616,7 +617,7 @@ cudaError_t kstream_lse(const Staged& s, int side, const StreamArgs& a, const Ls
   const int bm = 128 * k.nhalf;
   kp.nblk = (a.nr - a.row_begin + bm - 1) / bm;
   if (kp.nblk <= 0) return cudaSuccess;
-  kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride; kp.tickets = s.tickets;
+  kp.part_m = s.part_m[side]; kp.part_s = s.part_s[side]; kp.part_stride = s.part_stride; kp.tickets = s.tickets[side];
   kp.s_out = s_out; kp.ld_s = ld_s;
   return launch_plan<EPI_LSE>(k, ma, mb, kp, detail::pick_ctas(kp.nblk, kp.ntiles), st);
 }
@@ -642,7 +643,7 @@ cudaError_t kstream_vec(const Staged& s, int side, const StreamArgs& a, const Pv
   const int bm = 128 * k.nhalf;
   kp.nblk = (a.nr - a.row_begin + bm - 1) / bm;
   if (kp.nblk <= 0) return cudaSuccess;
-  kp.part_m = s.part_m; kp.part_s = s.part_s; kp.part_stride = s.part_stride; kp.tickets = s.tickets;
+  kp.part_m = s.part_m[side]; kp.part_s = s.part_s[side]; kp.part_stride = s.part_stride; kp.tickets = s.tickets[side];
   kp.R = pa.R; kp.vpad = vpad; kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.vout = pa.out; kp.skip = pa.skip;
   return launch_plan<EPI_VEC>(k, ma, mb, kp, detail::pick_ctas(kp.nblk, kp.ntiles), st);
 }

@@ -183,6 +183,128 @@ def run_symmetric_sharded(*args, **kwargs):
     return run_many([sharded_steps(*args, **kwargs)])[0]
 
 
+class PackedLayout:
+    """Where the potentials of several problems live in one buffer that a single all-gather completes.
+
+    The buffer is ``[world, width]``: row r is what rank r produces in one step - for every problem its slice of
+    f (``shard_f`` slots) and, unless the problem is a self-transport one, its slice of g. Element j of a full
+    vector therefore sits at ``row j // shard``, column ``offset + j % shard``: the "packed" addressing that
+    ``fs_symmetric_step_multi`` takes (shard size + row pitch), so that no copy sits between the kernel that
+    writes the slices, the collective and the kernel that reads the full vectors."""
+
+    def __init__(self, sizes, world: int):
+        """``sizes`` = ``[(n, m, self_problem)]`` per problem."""
+        self.world = world
+        self.slots = []
+        off = 0
+        for n, m, self_problem in sizes:
+            sf = shard_layout(n, world)
+            f_slot = (off, sf, n)
+            off += sf
+            if self_problem:
+                g_slot = f_slot
+            else:
+                sg = shard_layout(m, world)
+                g_slot = (off, sg, m)
+                off += sg
+            self.slots.append((f_slot, g_slot))
+        self.width = max(off, 1)
+
+    def new_buffer(self, like: torch.Tensor) -> torch.Tensor:
+        return torch.zeros(self.world * self.width, dtype=like.dtype, device=like.device)
+
+    def full(self, buf: torch.Tensor, k: int, side: int) -> torch.Tensor:
+        """Full vector of problem k (side 0 = f, 1 = g) gathered out of ``buf`` (a copy)."""
+        off, shard, size = self.slots[k][side]
+        return buf.view(self.world, self.width)[:, off:off + shard].reshape(-1)[:size].clone()
+
+    def store(self, buf: torch.Tensor, k: int, side: int, vec: torch.Tensor) -> None:
+        off, shard, size = self.slots[k][side]
+        padded = torch.zeros(self.world * shard, dtype=buf.dtype, device=buf.device)
+        padded[:size].copy_(vec)
+        buf.view(self.world, self.width)[:, off:off + shard].copy_(padded.view(self.world, shard))
+
+
+def run_symmetric_fused(problems, *, world: int, rank: int, step_fn: Callable, gather_fn: Callable):
+    """Several symmetric solves in lockstep, every step of all of them as ONE fused launch and ONE all-gather.
+
+    ``problems`` = list of dicts with ``n, m, f_hat0, g_hat0, eps_list, last_extrapolation, threshold,
+    check_every, self_problem``. Step t of every problem that still has a step t is handed to
+    ``step_fn(items, old_buf, new_buf, layout)`` at once; ``items`` = ``[(k, eps, w, (f_lo, f_hi, g_lo, g_hi))]``
+    and the function must write rows ``[f_lo, f_hi)`` of problem k's new f (and ``[g_lo, g_hi)`` of its new g,
+    unless the range is empty) into rank ``rank``'s row of ``new_buf`` at the layout's offsets, reading the full
+    old vectors from ``old_buf``. ``gather_fn(buf, width)`` then completes ``new_buf`` in place. A problem that
+    has finished keeps its slots unchanged (its values are carried over by a copy of its slots).
+    Returns ``[(f_hat, g_hat, f_hat_pre, g_hat_pre, steps)]`` like :func:`sharded_steps`.
+    """
+    layout = PackedLayout([(p["n"], p["m"], p["self_problem"]) for p in problems], world)
+    like = problems[0]["f_hat0"]
+    buf = [layout.new_buffer(like), layout.new_buffer(like)]
+    cur = 0
+    plans, state = [], []
+    for k, p in enumerate(problems):
+        layout.store(buf[0], k, 0, p["f_hat0"])
+        if not p["self_problem"]:
+            layout.store(buf[0], k, 1, p["g_hat0"])
+        eps = list(p["eps_list"])
+        steps = [(eps[0], 1.0, "init")] + [(e, 0.5, "loop") for e in eps]
+        if p["last_extrapolation"]:
+            steps.append((eps[-1], 1.0, "last"))
+        plans.append(steps)
+        f_lo, f_hi = shard_range(p["n"], world, rank)
+        g_lo, g_hi = shard_range(p["m"], world, rank)
+        if p["self_problem"]:
+            g_hi = g_lo  # only the f half runs; g aliases f
+        state.append(dict(pos=0, done=False, rng=(f_lo, f_hi, g_lo, g_hi), prev=None, pre=(None, None), used=0,
+                          loops=0))
+    while True:
+        items = []
+        for k, (p, st) in enumerate(zip(problems, state)):
+            if st["done"]:
+                continue
+            if st["pos"] >= len(plans[k]):
+                st["done"] = True
+                continue
+            eps, w, kind = plans[k][st["pos"]]
+            if kind == "last":  # the potentials before the final extrapolation are part of the result
+                st["pre"] = (layout.full(buf[cur], k, 0), layout.full(buf[cur], k, 1))
+            items.append((k, float(eps), float(w), st["rng"]))
+        if not items:
+            break
+        active = {k for k, *_ in items}
+        new = buf[cur ^ 1]
+        for k in range(len(problems)):  # finished problems: carry their slots over unchanged
+            if k not in active:
+                for side in ((0,) if problems[k]["self_problem"] else (0, 1)):
+                    off, shard, _ = layout.slots[k][side]
+                    new.view(world, layout.width)[:, off:off + shard].copy_(
+                        buf[cur].view(world, layout.width)[:, off:off + shard])
+        step_fn(items, buf[cur], new, layout)
+        wait = gather_fn(new, layout.width)
+        if wait is not None:
+            wait()
+        cur ^= 1
+        for k, eps, w, _ in items:
+            p, st = problems[k], state[k]
+            kind = plans[k][st["pos"]][2]
+            st["pos"] += 1
+            st["used"] += 1
+            if kind != "loop":
+                continue
+            st["loops"] += 1
+            if p["threshold"] is not None and st["loops"] % p["check_every"] == 0:
+                f_now, g_now = layout.full(buf[cur], k, 0), layout.full(buf[cur], k, 1)
+                if st["prev"] is not None:
+                    change = max(float((f_now - st["prev"][0]).abs().max()), float((g_now - st["prev"][1]).abs().max()))
+                    if change < p["threshold"]:  # identical on all ranks: the vectors are
+                        st["pos"] = len(plans[k]) - 1 if p["last_extrapolation"] else len(plans[k])
+                st["prev"] = (f_now, g_now)
+    out = []
+    for k, st in enumerate(state):
+        out.append((layout.full(buf[cur], k, 0), layout.full(buf[cur], k, 1), st["pre"][0], st["pre"][1], st["used"]))
+    return out
+
+
 def _gather_inplace(group, overlap: bool = False):
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     side = torch.cuda.Stream() if overlap else None
@@ -253,6 +375,69 @@ def _cuda_problem(x, y, log_a, log_b, eps_list, *, cost_scale, rho_x, rho_y, las
     return gen, finish
 
 
+def _fused_solve_cuda(problems, group):
+    """CUDA engine behind :func:`run_symmetric_fused`: one ``fs_symmetric_step_multi`` call and one all-gather per
+    step for all problems together. Needs the tensor-core engine (the packed addressing of the potentials is
+    read by its bias kernels); the caller checks ``fs_engine`` first."""
+    import ctypes
+    import os
+
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels._common import dampening
+
+    gather, world, rank = _gather_inplace(group)
+    lib = _lib.load()
+    dev = problems[0]["x"].device
+    d = problems[0]["x"].shape[1]
+    prec = problems[0]["prec"]
+    prepared, consts = [], []
+    for pr in problems:
+        x, y = pr["x"], pr["y"]
+        n, m = x.shape[0], y.shape[0]
+        cs = pr["cost_scale"]
+        alpha = cs * x.pow(2).sum(dim=1)
+        beta = alpha if y.data_ptr() == x.data_ptr() and n == m else cs * y.pow(2).sum(dim=1)
+        fi, gi = pr["f_init"], pr["g_init"]
+        f0 = (fi.float() - alpha) if fi is not None else -alpha
+        g0 = (gi.float() - beta) if gi is not None else -beta
+        same_init = (fi is None and gi is None) or (fi is not None and gi is not None and fi.data_ptr() == gi.data_ptr())
+        self_problem = (n == m and x.data_ptr() == y.data_ptr() and pr["log_a"].data_ptr() == pr["log_b"].data_ptr()
+                        and same_init and pr["rho_x"] == pr["rho_y"])
+        prepared.append(dict(n=n, m=m, f_hat0=f0, g_hat0=g0, eps_list=pr["eps_list"],
+                             last_extrapolation=pr["last_extrapolation"], threshold=pr["threshold"],
+                             check_every=pr["check_every"], self_problem=self_problem))
+        consts.append(dict(alpha=alpha, beta=beta, ws=_lib.workspace(_lib.OP_STEP, n, m, d, prec, dev), staged=False))
+    fsize = ctypes.sizeof(ctypes.c_float)
+
+    def step_fn(items, old, new, layout):
+        arr = (_lib.StepItem * len(items))()
+        for slot, (k, eps, w, rng) in zip(arr, items):
+            pr, c = problems[k], consts[k]
+            (f_off, f_shard, _), (g_off, g_shard, _) = layout.slots[k]
+            slot.x, slot.y, slot.n, slot.m = pr["x"].data_ptr(), pr["y"].data_ptr(), prepared[k]["n"], prepared[k]["m"]
+            slot.f_hat, slot.g_hat = old.data_ptr() + fsize * f_off, old.data_ptr() + fsize * g_off
+            slot.f_out, slot.g_out = new.data_ptr() + fsize * f_off, new.data_ptr() + fsize * g_off
+            slot.log_a, slot.log_b = pr["log_a"].data_ptr(), pr["log_b"].data_ptr()
+            slot.alpha_x, slot.beta_y = c["alpha"].data_ptr(), c["beta"].data_ptr()
+            slot.eps, slot.w = eps, w
+            slot.damp_f, slot.damp_g = dampening(eps, pr["rho_x"]), dampening(eps, pr["rho_y"])
+            slot.cost_scale = pr["cost_scale"]
+            slot.f_begin, slot.f_end, slot.g_begin, slot.g_end = rng
+            slot.restage = 0 if c["staged"] else 1
+            slot.ws, slot.ws_bytes = c["ws"].data_ptr(), c["ws"].numel()
+            slot.f_shard, slot.g_shard, slot.pack_stride = f_shard, g_shard, layout.width
+            c["staged"] = True
+        _lib.call("fs_symmetric_step_multi", dev, ctypes.cast(arr, ctypes.c_void_p), len(items), d, prec,
+                  _lib.stream_ptr(dev))
+
+    results = run_symmetric_fused(prepared, world=world, rank=rank, step_fn=step_fn, gather_fn=gather)
+    out = []
+    for (fh, gh, fp, gp, steps), c in zip(results, consts):
+        pre = (None, None) if fp is None else (fp + c["alpha"], gp + c["beta"])
+        out.append((fh + c["alpha"], gh + c["beta"], pre[0], pre[1], steps))
+    return out
+
+
 def symmetric_solve_sharded_many(problems, *, group):
     """Solve several independent problems with their steps interleaved (each ``problems[i]`` is the keyword
     set of :func:`symmetric_solve_sharded` without ``group``). While one problem's all-gather is in flight
@@ -262,6 +447,14 @@ def symmetric_solve_sharded_many(problems, *, group):
 
     from flash_sinkhorn_b200 import _lib
 
+    # Tensor-core shapes: every step of all problems as one fused launch + one all-gather (the fixed cost of a
+    # launch is then paid once per step instead of once per pass, which is what a short per-rank pass needs).
+    # FLASH_SINKHORN_B200_FUSED_STEPS=0 keeps the pass-by-pass schedule below (overlapped gathers).
+    d = problems[0]["x"].shape[1]
+    same = all(pr["x"].shape[1] == d and pr["prec"] == problems[0]["prec"] for pr in problems)
+    tc_engine = all(_lib.load().fs_engine(pr["x"].shape[0], pr["y"].shape[0], d, pr["prec"]) >= 1 for pr in problems)
+    if same and tc_engine and len(problems) <= 8 and os.environ.get("FLASH_SINKHORN_B200_FUSED_STEPS", "1") != "0":
+        return _fused_solve_cuda(problems, group)
     gather, world, rank = _gather_inplace(group, overlap=True)
     built = [_cuda_problem(gather=gather, world=world, rank=rank, **pr) for pr in problems]
     # The all-gather of one half-step runs next to the streaming pass of the next one; that pass is a single

@@ -102,6 +102,10 @@ int fs_set_reserved_sms(int k);
  * CTA covering many row blocks, many CTAs sharing one) without touching the environment. */
 int fs_set_cta_limit(int k);
 
+/* Which engine serves a problem of these sizes (no reference counterpart): 0 = CUDA-core fp32 FMA, 1 = tcgen05
+ * with the row operand resident in shared memory, 2 = tcgen05 with both operands streamed in K chunks. */
+int fs_engine(int n, int m, int d, int prec);
+
 /* Host arithmetic only (no reference counterpart): the CTA count a streaming pass over n_row_blocks x
  * n_col_tiles work items gets on a device with `sms` SMs when `reserved` of them are left free and the CTA
  * limit is `limit` (0 = none). At most 16 CTAs ever share a row block. Returns 0 on non-positive sizes. */
@@ -179,6 +183,31 @@ int fs_symmetric_step_range(const float* x, const float* y, int n, int m, int d,
                             float eps, float w, float damp_f, float damp_g, float cost_scale,
                             int f_begin, int f_end, int g_begin, int g_end, int restage,
                             int prec, void* ws, size_t ws_bytes, void* stream);
+
+/* Several row-sharded Jacobi steps - of one problem or of several independent problems with the same feature
+ * dimension - enqueued together (no reference counterpart). Each item is one fs_symmetric_step_range call
+ * with its own workspace (sized for FS_OP_STEP at its n, m); a side whose row range is empty is skipped.
+ * On the tensor-core engine up to four of the resulting soft-min passes share ONE kernel launch (their work
+ * items form one list that is cut over the SMs), so the fixed cost of a launch is paid once per group: this is
+ * what keeps short per-rank passes efficient when a debiased loss (three problems, four passes per iteration)
+ * is sharded over many GPUs. Results are those of the separate calls up to the order in which partial sums
+ * of a row are merged. At most 8 items. */
+typedef struct fs_step_item {
+  const float* x; const float* y; int n, m;
+  const float* f_hat; const float* g_hat; const float* log_a; const float* log_b;
+  float* f_out; float* g_out;
+  const float* alpha_x; const float* beta_y;   /* shift-correction vectors, NULL on balanced sides */
+  float eps, w, damp_f, damp_g, cost_scale;
+  int f_begin, f_end, g_begin, g_end;
+  int restage;                                   /* 0: operands staged by an earlier call into the same ws */
+  void* ws; size_t ws_bytes;
+  /* Packed potentials (all three 0 = plain contiguous vectors). With f_shard > 0 element j of f_hat and of
+   * f_out is at ptr[(j / f_shard) * pack_stride + j % f_shard], likewise g with g_shard: the layout of a
+   * [ranks, pack_stride] buffer that one all-gather completes when rank r owns rows [r*shard, (r+1)*shard)
+   * of every vector. A row range must then lie inside one shard. Tensor-core engine only. */
+  int f_shard, g_shard, pack_stride;
+} fs_step_item;
+int fs_symmetric_step_multi(const fs_step_item* items, int n_items, int d, int prec, void* stream);
 
 /* The same with a block-sparse list of kept 128 x 128 tiles (CSR over the 128-row blocks of x, and the
  * transposed list over the blocks of y, as fs_solve_alternating takes them; all four NULL = dense). No

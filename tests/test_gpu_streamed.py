@@ -224,3 +224,113 @@ def test_sharded_alternating_with_tile_lists_on_a_one_rank_group():
     finally:
         if own_group:
             dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("d,mode", [(64, "fp32"), (64, "tf32"), (24, "fp32"), (300, "tf32")])
+def test_fused_multi_problem_step_with_packed_potentials(monkeypatch, d, mode):
+    """fs_symmetric_step_multi on one GPU, playing both ranks of a two-rank layout in turn: three problems
+    (cross term and two self-transport terms of a debiased loss, different sizes) advance one Jacobi step as one
+    fused launch per "rank", reading and writing the packed [ranks, width] buffer. The result must equal the
+    ordinary one-problem step (up to the order in which a row's partial sums merge)."""
+    import ctypes
+
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.distributed import PackedLayout, shard_range
+    from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_symmetric_step
+    monkeypatch.setenv("FLASH_SINKHORN_B200_PREC", mode)
+    prec = _lib.precision_id(mode == "tf32")
+    g = torch.Generator().manual_seed(d)
+    n, m = 1500, 1100
+    x = (torch.randn(n, d, generator=g) / d**0.5).cuda()
+    y = (0.3 + torch.randn(m, d, generator=g) / d**0.5).cuda()
+    a = torch.softmax(torch.randn(n, generator=g), 0).cuda()
+    b = torch.softmax(torch.randn(m, generator=g), 0).cuda()
+    eps, w, world = 0.2, 0.5, 2
+    probs = [(x, y, a, b, False), (x, x, a, a, True), (y, y, b, b, True)]
+    layout = PackedLayout([(p[0].shape[0], p[1].shape[0], p[4]) for p in probs], world)
+    old, new = layout.new_buffer(x), layout.new_buffer(x)
+    pots, wss = [], []
+    for k, (px, py, pa, pb, selfp) in enumerate(probs):
+        fh = -(px**2).sum(1) + 0.1 * torch.randn(px.shape[0], generator=g).cuda()
+        gh = fh if selfp else -(py**2).sum(1) + 0.1 * torch.randn(py.shape[0], generator=g).cuda()
+        layout.store(old, k, 0, fh)
+        if not selfp:
+            layout.store(old, k, 1, gh)
+        pots.append((fh, gh))
+        wss.append(_lib.workspace(_lib.OP_STEP, px.shape[0], py.shape[0], d, prec, x.device))
+    fsz = 4
+    keep = []
+    for rank in range(world):
+        arr = (_lib.StepItem * len(probs))()
+        for k, (slot, (px, py, pa, pb, selfp)) in enumerate(zip(arr, probs)):
+            (f_off, f_shard, _), (g_off, g_shard, _) = layout.slots[k]
+            la, lb = pa.log().contiguous(), pb.log().contiguous()
+            keep += [la, lb]
+            f_lo, f_hi = shard_range(px.shape[0], world, rank)
+            g_lo, g_hi = shard_range(py.shape[0], world, rank)
+            if selfp:
+                g_hi = g_lo
+            slot.x, slot.y, slot.n, slot.m = px.data_ptr(), py.data_ptr(), px.shape[0], py.shape[0]
+            slot.f_hat, slot.g_hat = old.data_ptr() + fsz * f_off, old.data_ptr() + fsz * g_off
+            slot.f_out, slot.g_out = new.data_ptr() + fsz * f_off, new.data_ptr() + fsz * g_off
+            slot.log_a, slot.log_b = la.data_ptr(), lb.data_ptr()
+            slot.alpha_x, slot.beta_y = None, None
+            slot.eps, slot.w, slot.damp_f, slot.damp_g, slot.cost_scale = eps, w, 1.0, 1.0, 1.0
+            slot.f_begin, slot.f_end, slot.g_begin, slot.g_end = f_lo, f_hi, g_lo, g_hi
+            slot.restage = 1 if rank == 0 else 0
+            slot.ws, slot.ws_bytes = wss[k].data_ptr(), wss[k].numel()
+            slot.f_shard, slot.g_shard, slot.pack_stride = f_shard, g_shard, layout.width
+        _lib.call("fs_symmetric_step_multi", x.device, ctypes.cast(arr, ctypes.c_void_p), len(probs), d, prec,
+                  _lib.stream_ptr(x.device))
+    tol = 2e-3 if mode == "tf32" else 1e-5
+    for k, (px, py, pa, pb, selfp) in enumerate(probs):
+        fh, gh = pots[k]
+        f1, g1 = flashsinkhorn_symmetric_step(px, py, fh, gh, pa.log(), pb.log(), eps, alpha=w, allow_tf32=(mode == "tf32"))
+        assert _r(layout.full(new, k, 0), f1) < tol, (k, "f")
+        if not selfp:
+            assert _r(layout.full(new, k, 1), g1) < tol, (k, "g")
+    assert _lib.load().fs_device_error() == 0
+
+
+def test_fused_sharded_debiased_solves_on_a_one_rank_group(monkeypatch):
+    """symmetric_solve_sharded_many (the multi-GPU path of a debiased loss) on a one-rank NCCL group: the fused
+    lockstep schedule, the pass-by-pass schedule and the single-GPU solver agree."""
+    import socket
+
+    import torch.distributed as dist
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.distributed import symmetric_solve_sharded_many
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_symmetric
+    own_group = not dist.is_initialized()
+    if own_group:
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+    try:
+        g = torch.Generator().manual_seed(21)
+        n, m, d = 900, 700, 32
+        x, y = torch.randn(n, d, generator=g).cuda(), (0.5 + torch.randn(m, d, generator=g)).cuda()
+        a, b = torch.full((n,), 1.0 / n).cuda(), torch.softmax(torch.randn(m, generator=g), 0).cuda()
+        la, lb = a.log(), b.log()
+        eps_list = [2.0, 1.0, 0.5, 0.5, 0.5]
+        common = dict(cost_scale=0.5, rho_x=None, rho_y=2.0, last_extrapolation=True, threshold=None, check_every=5,
+                      f_init=None, g_init=None, prec=_lib.PREC_FP32)
+        probs = [dict(x=x, y=y, log_a=la, log_b=lb, eps_list=eps_list, **common),
+                 dict(x=x, y=x, log_a=la, log_b=la, eps_list=eps_list[:3], **dict(common, rho_y=None)),
+                 dict(x=y, y=y, log_a=lb, log_b=lb, eps_list=eps_list, **dict(common, rho_y=None))]
+        fused = symmetric_solve_sharded_many(probs, group=dist.group.WORLD)
+        monkeypatch.setenv("FLASH_SINKHORN_B200_FUSED_STEPS", "0")
+        plain = symmetric_solve_sharded_many(probs, group=dist.group.WORLD)
+        for fu, pl in zip(fused, plain):
+            assert fu[4] == pl[4]
+            for u, v in zip(fu[:4], pl[:4]):
+                assert _r(u, v) < 1e-5
+        f1, g1, fp1, gp1 = sinkhorn_flashstyle_symmetric(x, y, a, b, eps_list=eps_list, use_epsilon_scaling=False,
+                                                         cost_scale=0.5, rho_y=2.0, allow_tf32=False, return_prelast=True)
+        assert _r(fused[0][0], f1) < 1e-5 and _r(fused[0][1], g1) < 1e-5 and _r(fused[0][3], gp1) < 1e-5
+    finally:
+        if own_group:
+            dist.destroy_process_group()
