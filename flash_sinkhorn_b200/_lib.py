@@ -47,6 +47,8 @@ SIGNATURES = {
     "fs_device_arch": (c_int, []),
     "fs_launch_count": (ctypes.c_longlong, []),
     "fs_device_error": (c_int, []),
+    "fs_clear_device_error": (c_int, []),
+    "fs_apply_mat_plan_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "fs_micro_exp_rate": (c_double, [c_int, c_int]),
     "fs_micro_mma_cycles": (c_double, [c_int, c_int]),
     "fs_set_reserved_sms": (c_int, [c_int]),
@@ -261,6 +263,21 @@ class StepItem(ctypes.Structure):
 
 def stream_ptr(device: torch.device) -> int:
     return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def raise_if_device_timeout(device: torch.device) -> None:
+    """Raise ``FlashSinkhornError`` (FS_ERR_TIMEOUT) if a kernel of the library gave up one of its bounded waits.
+
+    Meant for the places where the host synchronises anyway (reading an iteration count or a CG record): the
+    outputs of the call that timed out are invalid, and its workspace has to be staged again. The word stays set
+    until ``fs_clear_device_error``."""
+    lib = load()
+    with torch.cuda.device(device):
+        flag = lib.fs_device_error()
+    if flag > 0:
+        raise FlashSinkhornError(
+            "FS_ERR_TIMEOUT: a streaming kernel gave up a bounded wait; the results of that call are invalid. "
+            "Re-stage its workspace (run the call again) and reset the word with fs_clear_device_error().")
 
 
 def call(name: str, device: torch.device, *args) -> None:

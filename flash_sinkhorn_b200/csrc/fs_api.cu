@@ -97,7 +97,6 @@ __global__ void ctrl_init_kernel(Ctrl* c, int have_prev) {
   c->converged = 0;
   c->have_prev = have_prev;
   c->iters_used = 0;
-  c->error = 0;
 }
 
 __global__ void bump_iters_kernel(Ctrl* c, int only_if_running) {
@@ -272,7 +271,7 @@ int check_device() {
 // `lse_only` is true for ops that only run LSE passes.
 int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int m, int d, float cs, int prec,
                  cudaStream_t st, bool measure_only, int pv_dv = 0, bool run_staging = true,
-                 const LabelCost* lab = nullptr) {
+                 const LabelCost* lab = nullptr, bool exact_width = false) {
   p.x = x; p.y = y; p.n = n; p.m = m; p.d = d; p.cs = cs; p.prec = prec; p.st = st;
   if (lab && lab->V > 0) p.lab = *lab;
   p.nlab = 3 * p.lab.V;
@@ -293,12 +292,16 @@ int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int 
     if (pv_dv > 0) {
       const int nm = n > m ? n : m;
       size_t need = 0;
-      if (tc::k_streamed(d, prec, p.nlab) && pv_dv > 1) {
-        if (tc::kstream_mat_supported(pv_dv)) {
+      if (tc::k_streamed(d, prec, p.nlab)) {
+        // one-column passes take a padded copy of the vector, wide matrices the score / weight scratch;
+        // widths in between run on the CUDA-core engine without scratch
+        const bool any_width = measure_only && !exact_width;
+        if (pv_dv == 1 || any_width) need = tc::pv_scratch_bytes(nm, d, prec, 1, p.nlab);
+        if (pv_dv > 1 && tc::kstream_mat_supported(pv_dv)) {
           need = tc::kstream_mat_scratch(nm, nm, pv_dv, prec);
           p.mat_streamed = true;
         }
-      } else if (measure_only) {
+      } else if (measure_only && !exact_width) {
         const int cand[5] = {32, 64, 96, 128, pv_dv};
         for (int c : cand)
           if (c <= pv_dv && tc::pv_supported(d, prec, c, p.nlab)) {
@@ -362,6 +365,8 @@ inline double dampening(double eps, double rho) {
 namespace fs {
 // Lets the other translation units of the library record an error for fs_last_error().
 int report_error(int code, const char* msg) { return fail(code, "%s", msg); }
+// Lets them add the kernels they enqueue themselves to the count behind fs_launch_count().
+void count_launches(int k) { g_launches.fetch_add(k, std::memory_order_relaxed); }
 }  // namespace fs
 
 using namespace fs;
@@ -373,6 +378,18 @@ int fs_version(void) { return 200; }  // 0.2.0
 long long fs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int fs_device_error(void) { return tc::read_error_flag(); }
+
+int fs_clear_device_error(void) { return tc::clear_error_flag(); }
+
+size_t fs_apply_mat_plan_bytes(int n, int m, int d, int dv, int prec) {
+  if (n <= 0 || m <= 0 || d <= 0 || dv <= 0) return 0;
+  // Same carving as fs_apply_mat performs, without a workspace: what a call with this matrix width takes.
+  Ws ws(nullptr, 0);
+  Problem p;
+  make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true, dv <= d ? dv : 0, true, nullptr, true);
+  ws.take<float>(n > m ? n : m);
+  return ws.off;
+}
 
 int fs_set_cta_limit(int k) { return tc::set_cta_limit(k); }
 

@@ -17,8 +17,7 @@ struct Ctrl {
   int converged;            // 1 once the early-stop test passed: loop steps become identity
   int have_prev;            // 1 once a snapshot exists
   int iters_used;           // number of executed steps
-  int error;                // non-zero if a bounded device wait gave up (tcgen05 engine)
-  int pad[3];
+  int pad[4];
 };
 
 // One streaming pass "rows against all cols":

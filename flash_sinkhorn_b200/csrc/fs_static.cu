@@ -28,6 +28,7 @@
 
 namespace fs {
 int report_error(int code, const char* msg);  // fs_api.cu: records the calling thread's error text
+void count_launches(int k);                   // fs_api.cu: adds to the count behind fs_launch_count()
 }
 
 namespace {
@@ -104,5 +105,6 @@ extern "C" int fs_apply_mat_static(const float* x, const float* y, int n, int m,
   a.rowlogw = side == 0 ? log_a : log_b;
   a.out = out;
   if (simt_pv(s, a, st) != cudaSuccess) return report_error(FS_ERR_CUDA, "second streaming pass failed to launch");
+  count_launches(2);  // the two streaming passes, as fs_apply_mat counts its own
   return FS_OK;
 }

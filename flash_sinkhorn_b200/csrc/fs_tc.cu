@@ -1629,6 +1629,13 @@ double micro_mma_cycles(int n_cols, bool a_in_tmem) {
 }
 
 int read_error_flag_k();  // fs_tck.cu: the K-streamed kernels keep their own word (no relocatable device code)
+int clear_error_flag_k();
+
+int clear_error_flag() {
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int)) != cudaSuccess) return -1;
+  return clear_error_flag_k();
+}
 
 int read_error_flag() {
   int v = 0;

@@ -112,6 +112,8 @@ inline int pad256(int r) { return (r + 255) & ~255; }
 
 // Value of the device-global error word (non-zero once a bounded wait gave up); synchronises.
 int read_error_flag();
+// Resets the word to zero (0 on success, -1 on a CUDA error); synchronises.
+int clear_error_flag();
 
 // Average SM cycles per tcgen05.mma (kind::tf32, 128 x n_cols x 8, n_cols in {64,128,256}; A from shared
 // memory or from TMEM) when one lane issues 4096 of them back to back on every SM. Allocates a small

@@ -729,6 +729,11 @@ cudaError_t kstream_mat(const Staged& s, int side, const StreamArgs& a, const Pv
   return cudaGetLastError();
 }
 
+int clear_error_flag_k() {
+  const int zero = 0;
+  return cudaMemcpyToSymbol(g_tck_error, &zero, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
+
 int read_error_flag_k() {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_tck_error, sizeof(int)) != cudaSuccess) return -1;

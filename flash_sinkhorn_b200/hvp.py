@@ -97,6 +97,7 @@ def _device_schur_cg(x, y, f_shift, g_shift, log_a, log_b, diag_x, denom, rhs, *
         prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
     )
     rec = info.tolist()
+    _lib.raise_if_device_timeout(dev)  # the record read has synchronised: surface a device-side time-out
     return z, CGInfo(bool(rec[0] != 0.0), int(rec[1]), float(rec[2]), float(rec[3]))
 
 

@@ -81,9 +81,10 @@ def sinkhorn_geomloss_online_grad_sqeuclid(
             raise ValueError("grad_scale must be on the same device as x.")
         gs = _lib.f32c(grad_scale.detach().reshape(1))
     prec = _lib.precision_id(allow_tf32)
-    if labels is not None and process_group is not None:
+    multi_gpu = process_group is not None and torch.distributed.get_world_size(process_group) > 1
+    if labels is not None and multi_gpu:
         raise NotImplementedError("The label cost is not available in the multi-GPU sharded gradient.")
-    if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
+    if multi_gpu:
         from flash_sinkhorn_b200.distributed import grad_sharded  # rows sharded over the ranks, then all-gathered
         return grad_sharded(x32, y32, a32, b32, la, lb, f32, g32, gs, float(eps), float(cost_scale), prec,
                             bool(compute_grad_x), bool(compute_grad_y), process_group)

@@ -169,7 +169,9 @@ def sinkhorn_flashstyle_alternating(
         prec, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev),
     )
     if return_n_iters:
-        return f, g, int(iters.item())
+        used = int(iters.item())
+        _lib.raise_if_device_timeout(dev)  # the host has synchronised anyway: surface a device-side time-out
+        return f, g, used
     return f, g
 
 
@@ -233,7 +235,8 @@ def sinkhorn_flashstyle_symmetric(
     labels = _lib.LabelCost.make(label_x, label_y, label_cost_matrix, lambda_x, lambda_y, n, m, x.device)
     if labels is not None and fused is False:
         raise ValueError("OTDD label cost requires fused=True (default). Set fused=True or omit label_cost_matrix.")
-    if labels is not None and process_group is not None:
+    multi_gpu = process_group is not None and torch.distributed.get_world_size(process_group) > 1
+    if labels is not None and multi_gpu:
         raise NotImplementedError("The label cost is not available in the multi-GPU sharded solver.")
     rho_x, rho_y = resolve_marginal_penalties(rho, reach, rho_x, rho_y, reach_x, reach_y)
 
@@ -264,7 +267,7 @@ def sinkhorn_flashstyle_symmetric(
     gi = None if g_init is None else (fi if _same_tensor(g_init, f_init) else _lib.f32c(g_init))
     prec = _lib.precision_id(allow_tf32)
 
-    if process_group is not None and torch.distributed.get_world_size(process_group) > 1:
+    if multi_gpu:
         from flash_sinkhorn_b200.distributed import symmetric_solve_sharded
 
         sharded_args = dict(
@@ -304,6 +307,7 @@ def sinkhorn_flashstyle_symmetric(
         out = out + (f_pre, g_pre)
     if return_n_iters:
         out = out + (int(iters.item()),)
+        _lib.raise_if_device_timeout(dev)  # the host has synchronised anyway: surface a device-side time-out
     return out
 
 

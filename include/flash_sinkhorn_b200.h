@@ -77,6 +77,15 @@ long long fs_launch_count(void);
  * while reading it. SYNCHRONISES the device; meant for tests and post-mortems. */
 int fs_device_error(void);
 
+/* Resets the health word of the current device to 0 (after the cause of a time-out has been dealt with and the
+ * workspaces of the affected calls have been re-staged). Returns 0, or a negative value on a CUDA error.
+ * SYNCHRONISES the device. */
+int fs_clear_device_error(void);
+
+/* Host arithmetic only: the workspace bytes an fs_apply_mat call with a matrix of `dv` columns carves at these
+ * sizes. Never more than fs_workspace_bytes(FS_OP_APPLY_MAT, n, m, d, prec), which is sized for any dv <= d. */
+size_t fs_apply_mat_plan_bytes(int n, int m, int d, int dv, int prec);
+
 /* Measurement aid (no reference counterpart): ex2 evaluations per second that this GPU sustains,
  * mode 0 = ex2.approx alone, mode 1 = the soft-max inner loop (max + FFMA + ex2 + FADD per entry) on
  * register data, with `warps_per_sm` resident warps per SM. Used by bench.py as the measured

@@ -89,8 +89,38 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
     assert torch.equal(got1b, got1)
 
 
+@pytest.mark.gpu
+def test_static_scratch_entry_at_its_row_limit_and_against_the_oracle():
+    """Exactly 65,536 output rows (the last 64-row block of the kernel ends at the end of the static array): the
+    static entry and the workspace entry run the same kernels in the same order, so their outputs are equal bit
+    for bit. A second, small problem is also compared with the dense fp64 oracle, and the launch counter of the
+    library must see the two streaming passes of a static call."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from oracle import dense_sinkhorn as O
+    eps, cs = 0.4, 1.0
+    x, y, fh, gh, la, lb, mat_m, mat_n, scale = _problem(303, STATIC_MAX_ROWS, 200, 8, 3)
+    lib = _lib.load()
+    before = lib.fs_launch_count()
+    got = _static(x, y, fh, gh, la, lb, mat_m, None, 1, eps, cs)
+    assert lib.fs_launch_count() - before == 2
+    want = _with_workspace(x, y, fh, gh, la, lb, mat_m, None, 1, eps, cs)
+    torch.cuda.synchronize()
+    assert got.shape == (STATIC_MAX_ROWS, 3) and torch.isfinite(got).all()
+    assert torch.equal(got, want)
+    xs, ys, fs_, gs, las, lbs, mm, mn, sc = _problem(404, 257, 190, 5, 4)
+    got_s = _static(xs, ys, fs_, gs, las, lbs, mm, sc, 1, eps, cs)
+    ref = O.apply_mat(*(t.double().cpu().numpy() for t in (xs, ys, fs_, gs, las, lbs, mm)), eps, 1, cost_scale=cs,
+                      scale=sc.double().cpu().numpy())
+    err = np.abs(got_s.double().cpu().numpy() - ref).max() / np.abs(ref).max()
+    assert err <= TOL
+
+
 def test_static_scratch_entry_rejects_sizes_beyond_its_array():
     """Runs without a GPU: the size check comes before any device work."""
+    import os
+    if not os.path.exists(_lib.library_path()):
+        pytest.skip("the CUDA library has not been built")
     lib = _lib.load()
     dummy = ctypes.c_void_p(256)  # never dereferenced: the call must fail on the size alone
     rc = lib.fs_apply_mat_static(dummy, dummy, STATIC_MAX_ROWS + 1, 10, 4, dummy, dummy, dummy, dummy, dummy, 4,
