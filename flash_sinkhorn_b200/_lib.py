@@ -113,6 +113,17 @@ SIGNATURES = {
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_float, c_float, c_int, _P, c_size_t, _P],
     ),
+    "fs_plan_session_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "fs_plan_session_begin": (
+        c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_float, c_float, c_int, _P, c_size_t, _P]),
+    "fs_plan_session_apply": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, c_int, _P, c_float, _P, c_int, c_float, c_float,
+         c_int, _P, c_size_t, _P]),
+    "fs_plan_session_cg": (
+        c_int,
+        [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float, c_int,
+         c_float, c_float, c_int, _P, c_size_t, _P]),
     "fs_schur_cg": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float, c_int,

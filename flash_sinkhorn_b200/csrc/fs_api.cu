@@ -226,9 +226,12 @@ struct Problem {
   cudaError_t pv(int side, const float* pot, const float* logw, float eps, const PvArgs& p) const {
     StreamArgs s = stream_args(side, pot, logw, eps);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (use_tc && !p.rows2 && !s.tile_row_ptr && pv_scratch && tc::pv_supported(d, prec, p.dv, nlab) &&
-        tc::pv_scratch_bytes(s.nc, d, prec, p.dv, nlab) <= pv_scratch_bytes)
-      return tc::pv(staged, side, s, p, pv_scratch, st);
+    if (use_tc && !s.tile_row_ptr && pv_scratch) {
+      const int nm = n > m ? n : m;
+      const size_t need = p.rows2 ? tc::mat5_scratch_bytes(nm, nm, d, prec, p.dv, nlab)
+                                  : (tc::pv_supported(d, prec, p.dv, nlab) ? tc::pv_scratch_bytes(nm, d, prec, p.dv, nlab) : 0);
+      if (need > 0 && need <= pv_scratch_bytes) return tc::pv(staged, side, s, p, pv_scratch, st);
+    }
     return simt_pv(s, p, st);
   }
   // Row normaliser R (written) followed by the matrix pass over the same scores: gradient, plan-times-matrix.
@@ -271,7 +274,7 @@ int check_device() {
 // `lse_only` is true for ops that only run LSE passes.
 int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int m, int d, float cs, int prec,
                  cudaStream_t st, bool measure_only, int pv_dv = 0, bool run_staging = true,
-                 const LabelCost* lab = nullptr, bool exact_width = false) {
+                 const LabelCost* lab = nullptr, bool exact_width = false, bool mat5 = false) {
   p.x = x; p.y = y; p.n = n; p.m = m; p.d = d; p.cs = cs; p.prec = prec; p.st = st;
   if (lab && lab->V > 0) p.lab = *lab;
   p.nlab = 3 * p.lab.V;
@@ -292,13 +295,21 @@ int make_problem(Problem& p, Ws& ws, const float* x, const float* y, int n, int 
     if (pv_dv > 0) {
       const int nm = n > m ? n : m;
       size_t need = 0;
-      if (tc::k_streamed(d, prec, p.nlab)) {
-        // one-column passes take a padded copy of the vector, wide matrices the score / weight scratch;
-        // widths in between run on the CUDA-core engine without scratch
+      if (mat5) {
+        need = tc::mat5_scratch_bytes(nm, nm, d, prec, pv_dv, p.nlab);
+      } else if (tc::k_streamed(d, prec, p.nlab)) {
+        // one-column passes take a padded copy of the vector, wide matrices the score / weight scratch, widths
+        // in between the transposed matrix of the TMEM-fed second GEMM; the size query covers them all
         const bool any_width = measure_only && !exact_width;
-        if (pv_dv == 1 || any_width) need = tc::pv_scratch_bytes(nm, d, prec, 1, p.nlab);
+        const int cand[6] = {1, 32, 64, 96, 128, pv_dv};
+        for (int c : cand)
+          if (c <= pv_dv && (c == pv_dv || any_width)) {
+            const size_t b = tc::pv_scratch_bytes(nm, d, prec, c, p.nlab);
+            if (b > need) need = b;
+          }
         if (pv_dv > 1 && tc::kstream_mat_supported(pv_dv)) {
-          need = tc::kstream_mat_scratch(nm, nm, pv_dv, prec);
+          const size_t b = tc::kstream_mat_scratch(nm, nm, pv_dv, prec);
+          if (b > need) need = b;
           p.mat_streamed = true;
         }
       } else if (measure_only && !exact_width) {
@@ -421,12 +432,12 @@ size_t fs_workspace_bytes_labels(int op, int n, int m, int d, int prec, int n_cl
   if (n <= 0 || m <= 0 || d <= 0) return 0;
   Ws ws(nullptr, 0);
   Problem p;
-  const bool matrix_op = (op == FS_OP_APPLY_MAT || op == FS_OP_GRAD);
+  const bool matrix_op = (op == FS_OP_APPLY_MAT || op == FS_OP_GRAD || op == FS_OP_MAT5);
   const bool vector_op = (op == FS_OP_APPLY_VEC || op == FS_OP_SCHUR);
   LabelCost lc;
   lc.V = n_classes > 0 ? n_classes : 0;  // only the class count matters for sizes
   make_problem(p, ws, nullptr, nullptr, n, m, d, 1.f, prec, nullptr, true, matrix_op ? d : (vector_op ? 1 : 0),
-               true, &lc);
+               true, &lc, false, op == FS_OP_MAT5);
   size_t nm = (size_t)(n > m ? n : m);
   switch (op) {
     case FS_OP_LSE:
@@ -805,7 +816,7 @@ int fs_mat5(const float* x, const float* y, int n, int m, int d, const float* f_
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Ws ws(wsp, ws_bytes);
   Problem p;
-  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false));
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cost_scale, prec, st, false, d, true, nullptr, false, true));
   float* fh = ws.take<float>(n);
   float* gh = ws.take<float>(m);
   float* R = ws.take<float>(n);
@@ -1012,6 +1023,123 @@ extern "C" int fs_grad_range(const float* x, const float* y, int n, int m, int d
 }
 
 // ---------------------------------------------------------------------------
+// Plan session: many applications of ONE transport plan (fixed clouds and potentials) that share the staged
+// operands and the two log-normaliser vectors. The Hessian-vector product is the user: its ~50 plan passes
+// then cost one streaming pass each.
+// ---------------------------------------------------------------------------
+namespace fs {
+namespace {
+
+struct Session {
+  Problem p;
+  float* R[2] = {nullptr, nullptr};  // log2 normalisers of the rows of x (side 0) and of y (side 1)
+  float* cg = nullptr;               // state and vectors of the Schur CG
+  float eps = 1.f;
+};
+
+// Lays the session out inside `ws` (identical for every call with the same sizes); stages when asked to.
+int open_session(Session& se, Ws& ws, const float* x, const float* y, int n, int m, int d, float eps, float cs,
+                 int prec, cudaStream_t st, bool stage, bool measure_only) {
+  se.eps = eps;
+  Problem& p = se.p;
+  FS_TRY(make_problem(p, ws, x, y, n, m, d, cs, prec, st, measure_only, 0, stage));
+  if (p.use_tc) {
+    const int nm = n > m ? n : m;
+    size_t need = tc::mat5_scratch_bytes(nm, nm, d, prec, d, 0);
+    const int widths[6] = {1, 32, 64, 96, 128, d};
+    for (int w : widths)
+      if (w <= d && tc::pv_supported(d, prec, w, 0)) {
+        const size_t b = tc::pv_scratch_bytes(nm, d, prec, w, 0);
+        if (b > need) need = b;
+      }
+    if (tc::k_streamed(d, prec, 0) && tc::kstream_mat_supported(d)) {
+      const size_t b = tc::kstream_mat_scratch(nm, nm, d, prec);
+      if (b > need) need = b;
+      p.mat_streamed = true;
+    }
+    p.pv_scratch_bytes = need;
+    p.pv_scratch = ws.take<char>(need);
+  }
+  se.R[0] = ws.take<float>(n);
+  se.R[1] = ws.take<float>(m);
+  se.cg = ws.take<float>(16 + 3 * (size_t)m + (size_t)n);
+  if (!measure_only && ws.overflow) return fail(FS_ERR_WORKSPACE, "workspace too small: need %zu bytes", ws.off);
+  return FS_OK;
+}
+
+}  // namespace
+}  // namespace fs
+
+extern "C" size_t fs_plan_session_bytes(int n, int m, int d, int prec) {
+  if (n <= 0 || m <= 0 || d <= 0) return 0;
+  Ws ws(nullptr, 0);
+  Session se;
+  open_session(se, ws, nullptr, nullptr, n, m, d, 1.f, 1.f, prec, nullptr, false, true);
+  return ws.off + 256;
+}
+
+extern "C" int fs_plan_session_begin(const float* x, const float* y, int n, int m, int d, const float* f_hat,
+                                     const float* g_hat, const float* log_a, const float* log_b, float eps,
+                                     float cost_scale, int prec, void* wsp, size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!f_hat || !g_hat || !log_a || !log_b) return fail(FS_ERR_BAD_ARG, "null argument");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Session se;
+  FS_TRY(open_session(se, ws, x, y, n, m, d, eps, cost_scale, prec, st, true, false));
+  LseEpilogue e0, e1;
+  e0.lse2 = se.R[0];
+  e1.lse2 = se.R[1];
+  FS_CUDA(se.p.lse(0, g_hat, log_b, eps, e0));
+  FS_CUDA(se.p.lse(1, f_hat, log_a, eps, e1));
+  return FS_OK;
+}
+
+// One plan application inside a session. kind 0: vector (operand [cols], out [rows]); 1: matrix with dv columns and
+// an optional per-column-point scale (axis 1 only); 2: the Mat5 term (operand A [n, d], axis 1, dv = d).
+extern "C" int fs_plan_session_apply(const float* x, const float* y, int n, int m, int d, const float* f_hat,
+                                     const float* g_hat, const float* log_a, const float* log_b, int kind,
+                                     const float* operand, int dv, const float* scale, float coef, float* out,
+                                     int axis, float eps, float cost_scale, int prec, void* wsp, size_t ws_bytes,
+                                     void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!f_hat || !g_hat || !log_a || !log_b || !operand || !out) return fail(FS_ERR_BAD_ARG, "null argument");
+  if (axis != 0 && axis != 1) return fail(FS_ERR_BAD_ARG, "axis must be 0 or 1");
+  if (kind < 0 || kind > 2) return fail(FS_ERR_BAD_ARG, "kind must be 0 (vector), 1 (matrix) or 2 (Mat5)");
+  if (kind == 2 && (axis != 1 || dv != d)) return fail(FS_ERR_BAD_ARG, "Mat5 is an axis-1 pass with dv == d");
+  if (kind == 1 && (dv <= 0 || dv > d)) return fail(FS_ERR_BAD_ARG, "matrix passes of a session take 1 <= dv <= d");
+  if (scale && (axis != 1 || kind != 1)) return fail(FS_ERR_BAD_ARG, "scale is only supported for axis-1 matrix passes");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Session se;
+  FS_TRY(open_session(se, ws, x, y, n, m, d, eps, cost_scale, prec, st, false, false));
+  const int side = axis == 1 ? 0 : 1;
+  const float* cpot = side == 0 ? g_hat : f_hat;
+  const float* clw = side == 0 ? log_b : log_a;
+  const float* rpot = side == 0 ? f_hat : g_hat;
+  const float* rlw = side == 0 ? log_a : log_b;
+  if (kind == 0) {
+    VecArgs v;
+    v.v = operand; v.out = out; v.rowpot = rpot; v.rowlogw = rlw;
+    FS_CUDA(se.p.vec(side, cpot, clw, eps, v, se.p.vec_on_tc() ? se.R[side] : nullptr));
+    return FS_OK;
+  }
+  PvArgs a;
+  a.R = se.R[side]; a.V = kind == 2 ? y : operand; a.dv = dv; a.colscale = scale;
+  a.epilogue = kind == 2 ? PV_MAT5 : PV_APPLY;
+  a.rows2 = kind == 2 ? operand : nullptr;
+  a.rowpot = rpot; a.rowlogw = rlw; a.coef = kind == 2 ? coef : 1.f; a.out = out;
+  if (kind == 1 && se.p.mat_streamed) {  // wide matrix of a K-streamed problem: scores are kept, R recomputed
+    FS_CUDA(se.p.lse_pv(side, cpot, clw, eps, se.R[side], a));
+    return FS_OK;
+  }
+  FS_CUDA(se.p.pv(side, cpot, clw, eps, a));
+  return FS_OK;
+}
+
+// ---------------------------------------------------------------------------
 // Device-resident conjugate gradient on the Schur complement
 // ---------------------------------------------------------------------------
 namespace fs {
@@ -1156,6 +1284,45 @@ extern "C" int fs_schur_cg(const float* x, const float* y, int n, int m, int d, 
     VecArgs v0;
     v0.v = t; v0.rowpot = g_hat; v0.rowlogw = log_b; v0.out = q; v0.skip = &s->done;
     FS_CUDA(p.vec(1, f_hat, log_a, eps, v0, on_tc ? R_col : nullptr));
+    cg_update_kernel<<<1, 1024, 0, st>>>(m, denom, q, z, r, pv, s, it);
+  }
+  cg_finish_kernel<<<1, 1, 0, st>>>(s, info, max_iter);
+  FS_CUDA(cudaGetLastError());
+  return FS_OK;
+}
+
+// The Schur-complement CG of the Hessian-vector product inside a plan session: the same device-resident loop as
+// fs_schur_cg, without staging and without the two normaliser passes (the session holds both).
+extern "C" int fs_plan_session_cg(const float* x, const float* y, int n, int m, int d, const float* f_hat,
+                                  const float* g_hat, const float* log_a, const float* log_b, const float* diag_x,
+                                  const float* denom, const float* rhs, float* z, float* info, float eps,
+                                  float cost_scale, int max_iter, float rtol, float atol, int prec, void* wsp,
+                                  size_t ws_bytes, void* stream) {
+  FS_TRY(check_common(x, y, n, m, d, eps, cost_scale, prec));
+  if (!f_hat || !g_hat || !log_a || !log_b || !diag_x || !denom || !rhs || !z || !info)
+    return fail(FS_ERR_BAD_ARG, "null argument");
+  if (max_iter < 0) return fail(FS_ERR_BAD_ARG, "max_iter must be >= 0");
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Ws ws(wsp, ws_bytes);
+  Session se;
+  FS_TRY(open_session(se, ws, x, y, n, m, d, eps, cost_scale, prec, st, false, false));
+  const Problem& p = se.p;
+  CgState* s = reinterpret_cast<CgState*>(se.cg);
+  float* r = se.cg + 16;
+  float* pv = r + m;
+  float* q = pv + m;
+  float* t = q + m;
+  const bool on_tc = p.vec_on_tc();
+  cg_init_kernel<<<1, 1024, 0, st>>>(m, rhs, z, r, pv, s, rtol, atol);
+  for (int it = 0; it < max_iter; ++it) {
+    VecArgs v1;
+    v1.v = pv; v1.rowpot = f_hat; v1.rowlogw = log_a; v1.out = t; v1.skip = &s->done;
+    FS_CUDA(p.vec(0, g_hat, log_b, eps, v1, on_tc ? se.R[0] : nullptr));
+    cg_div_kernel<<<g1(n), 256, 0, st>>>(n, t, diag_x, t, s);
+    VecArgs v0;
+    v0.v = t; v0.rowpot = g_hat; v0.rowlogw = log_b; v0.out = q; v0.skip = &s->done;
+    FS_CUDA(p.vec(1, f_hat, log_a, eps, v0, on_tc ? se.R[1] : nullptr));
     cg_update_kernel<<<1, 1024, 0, st>>>(m, denom, q, z, r, pv, s, it);
   }
   cg_finish_kernel<<<1, 1, 0, st>>>(s, info, max_iter);

@@ -1118,11 +1118,11 @@ namespace detail {
 
 // 2-D fp32 tensor [rows, kp] (kp contiguous), box = [box_k floats, box_rows rows].
 bool encode_map(CUtensorMap* map, const float* base, long long rows, long long kp, int box_k, int box_rows,
-                CUtensorMapSwizzle swz) {
+                CUtensorMapSwizzle swz, long long row_pitch) {
   auto enc = get_encode();
   if (!enc) return false;
   cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)kp * sizeof(float)};
+  cuuint64_t strides[1] = {(cuuint64_t)(row_pitch > 0 ? row_pitch : kp) * sizeof(float)};
   cuuint32_t box[2] = {(cuuint32_t)box_k, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
@@ -1209,6 +1209,13 @@ int plan_ctas(int nblk, int ntiles, int sms, int reserved, int limit) {
 }
 
 bool k_streamed(int d, int prec, int nlab) { return plan_shape(d, prec, nlab).streamed; }
+
+size_t mat5_scratch_bytes(int nr, int nc, int d, int prec, int dv, int nlab) {
+  const Shape sh = plan_shape(d, prec, nlab);
+  if (!sh.ok || (prec != 0 && prec != 1)) return 0;
+  const int nm = nr > nc ? nr : nc;
+  return kstream_pv_scratch(nm, nm, sh.kp, dv, prec, true);
+}
 
 bool csr_supported(int d, int prec, int nlab) {
   return (prec == 0 || prec == 1) && plan_shape_csr(d, prec, nlab).ok;
@@ -1468,12 +1475,14 @@ cudaError_t launch_pv(const CUtensorMap* maps, const PvKernelParams& kp, int gri
 
 bool pv_supported(int d, int prec, int dv, int nlab) {
   if (prec != 0 && prec != 1) return false;
-  if (plan_shape(d, prec, nlab).streamed) return dv == 1;  // wide V: kstream_mat, asked for separately
+  if (plan_shape(d, prec, nlab).streamed) return dv >= 1;  // one column, or V in slices through kstream_pv
   return plan_pv(d, prec, dv, nlab).ok;
 }
 
 size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab) {
-  if (plan_shape(d, prec, nlab).streamed) return dv == 1 ? (size_t)pad256(nc) * sizeof(float) + 1024 : 0;
+  const Shape shs = plan_shape(d, prec, nlab);
+  if (shs.streamed)
+    return dv == 1 ? (size_t)pad256(nc) * sizeof(float) + 1024 : kstream_pv_scratch(nc, nc, shs.kp, dv, prec, false);
   PvShape s = plan_pv(d, prec, dv, nlab);
   if (!s.ok) return 0;
   size_t one = (size_t)s.nslices * s.dv_pad * pad256(nc) * sizeof(float);
@@ -1482,10 +1491,15 @@ size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab) {
 
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa, char* scratch, cudaStream_t st) {
   Shape sh = plan_shape(s.d, s.prec, s.nlab);
-  if (sh.ok && sh.streamed)
-    return (pa.dv == 1 && !pa.rows2) ? kstream_vec(s, side, a, pa, scratch, st) : cudaErrorNotSupported;
+  if (sh.ok && (sh.streamed || pa.rows2)) {
+    if (pa.dv == 1 && !pa.rows2) return kstream_vec(s, side, a, pa, scratch, st);
+    // the caller sized the scratch with pv_scratch_bytes / mat5_scratch_bytes for these sizes
+    const size_t have = kstream_pv_scratch(a.nr > a.nc ? a.nr : a.nc, a.nr > a.nc ? a.nr : a.nc, s.kp, pa.dv, s.prec,
+                                           pa.rows2 != nullptr);
+    return kstream_pv(s, side, a, pa, scratch, have, st);
+  }
   PvShape ps = plan_pv(s.d, s.prec, pa.dv, s.nlab);
-  if (!sh.ok || !ps.ok || pa.rows2) return cudaErrorNotSupported;
+  if (!sh.ok || !ps.ok) return cudaErrorNotSupported;
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
   const float scale2 = (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;

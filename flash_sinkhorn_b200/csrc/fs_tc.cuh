@@ -70,6 +70,9 @@ cudaError_t argmax(const Staged& s, int side, const StreamArgs& a, float* out_va
 
 // Plan-times-matrix pass on the tensor cores (same staged operands, hence bit-identical scores
 // to the LSE passes). `scratch` holds the transposed, TF32-split copy of V (pv_scratch_bytes).
+// Scratch of a Mat5 pass (PvArgs::rows2 set: weights multiplied by rows2_i . cols_j), which pv() runs on the
+// K-streamed kernel at every shape; 0 when the tensor-core engine does not take the problem.
+size_t mat5_scratch_bytes(int nr, int nc, int d, int prec, int dv, int nlab = 0);
 bool pv_supported(int d, int prec, int dv, int nlab = 0);
 size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab = 0);
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, char* scratch, cudaStream_t st);
@@ -92,6 +95,11 @@ cudaError_t kstream_vec(const Staged& s, int side, const StreamArgs& a, const Pv
 // Whole matrix pass for wide V: per chunk of rows one soft-min pass that keeps its scores, an elementwise
 // pass that turns them into TF32 weights, and a K-streamed GEMM against the transposed V. Writes the row
 // normalisers to R_out ([nr] floats) on the way. `scratch` must hold kstream_mat_scratch() bytes.
+// Matrix pass with the second GEMM fed from TMEM (any contraction length, V in slices of 128 columns): narrow V
+// of K-streamed problems, and the Mat5 term of the Hessian (weights multiplied by rows2_i . cols_j) at any shape.
+size_t kstream_pv_scratch(int nr, int nc, int kp, int dv, int prec, bool mat5);
+cudaError_t kstream_pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, char* scratch,
+                       size_t scratch_bytes, cudaStream_t st);
 bool kstream_mat_supported(int dv);
 size_t kstream_mat_scratch(int nr, int nc, int dv, int prec);
 cudaError_t kstream_mat(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, float* R_out,
@@ -99,8 +107,9 @@ cudaError_t kstream_mat(const Staged& s, int side, const StreamArgs& a, const Pv
 
 // Shared host helpers of the two translation units.
 namespace detail {
+// 2-D fp32 tensor [rows, kp] whose rows are row_pitch floats apart (0 = kp: densely packed).
 bool encode_map(CUtensorMap* map, const float* base, long long rows, long long kp, int box_k, int box_rows,
-                CUtensorMapSwizzle swz);
+                CUtensorMapSwizzle swz, long long row_pitch = 0);
 int pick_ctas(int nblk, int ntiles);
 int sm_count();
 // Writes the column bias of a pass (divided by the logit scale, split into three TF32 pieces) into the bias

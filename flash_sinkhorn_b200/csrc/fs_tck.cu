@@ -474,6 +474,329 @@ tck_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUt
   if (tid == 0 && *abort_flag) atomicExch(&g_tck_error, 1);
 }
 
+// ------------------------------------------------------------------ K-streamed plan-times-matrix kernel
+// out = epilogue( sum_j 2^(logit_ij - R_i) [* (rows2_i . cols_j)] * V_j ) for narrow V (at most 128 columns per
+// launch) when the row operand does not fit in shared memory: the score GEMM streams both operands in K chunks
+// (as tck_kernel does), the weights go back to TMEM and feed the second GEMM O += W x V^T with A from TMEM, O
+// stays in TMEM for the whole pass (FlashAttention-style). R is the exact log2 normaliser from a soft-min pass
+// over the same staged operands, so no running maximum and no rescaling of O are needed.
+//   warp 0 : TMA producer of the K-chunk ring (row chunk, optional second row operand chunk, column chunk)
+//   warp 2 : TMA producer of the V^T tiles (own ring)
+//   warp 1 : score MMAs (S, and E = rows2 x cols^T in MAT5 mode), warp 3 : second GEMM
+//   warps 4..11 : two warpgroups turning scores into weights (each half of a tile's 32-column chunks)
+// One CTA = 128 rows, column tiles of 64. TMEM: NSW buffers of [S -> Wh | Wl (split) | E (MAT5)], then O.
+struct KPvParams {
+  int nr, nc, ntiles, row_begin;
+  int nk, klast, nstage, nv;   // K chunks, K steps of the last one, ring depths (K chunks / V tiles)
+  int dv, dv_pad, dv0, ld_out;
+  float scale2, eps;
+  const float* R;
+  int epilogue;
+  const float* rowpot; const float* rowlogw; const float* roww; const float* gs; float coef;
+  const float* rows_raw; int ld_rows;
+  float* out;
+  const int* skip;
+};
+
+template <bool SPLIT, bool MAT5>
+__global__ void __launch_bounds__(128 + 128 * kPartsK, 1)
+tck_pv_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapA2,
+              const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapV_hi,
+              const __grid_constant__ CUtensorMap mapV_lo, const KPvParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = p.row_begin + blockIdx.x * 128;
+  if (p.skip && *p.skip) return;  // uniform across the grid
+  constexpr int BN = 64;
+  constexpr int WCOLS = SPLIT ? 2 * BN : BN;          // S, overwritten by Wh (and Wl right after it)
+  constexpr int BUFCOLS = WCOLS + (MAT5 ? BN : 0);    // + E
+  constexpr int NSW = MAT5 ? 2 : 3;                   // score / weight buffers
+  constexpr int NVP = SPLIT ? 2 : 1;
+  static_assert(NSW * BUFCOLS + 128 <= 512, "TMEM budget");
+
+  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr uint32_t kAChunk = 128 * 128, kBChunk = BN * 128;
+  constexpr uint32_t kStage = kAChunk * (MAT5 ? 2 : 1) + kBChunk;
+  const uint32_t v_blk = (uint32_t)p.dv_pad * 128;   // one 32-column K block of V^T: dv_pad rows x 128 B
+  const uint32_t v_bytes = (BN / 32) * v_blk;        // per hi/lo part
+  const uint32_t v_stage = NVP * v_bytes;
+  uint8_t* ring = base;
+  uint8_t* v_smem = ring + (size_t)p.nstage * kStage;
+  uint64_t* bars = (uint64_t*)(v_smem + (size_t)p.nv * v_stage);
+  const int FULL = 0, EMPTY = p.nstage, V_FULL = 2 * p.nstage, V_EMPTY = V_FULL + p.nv, S_FULL = V_EMPTY + p.nv,
+            W_FULL = S_FULL + NSW, W_FREE = W_FULL + NSW, O_FULL = W_FREE + NSW, DRAIN = O_FULL + 1, NBARS = DRAIN + 1;
+  uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+  constexpr uint32_t kTmemCols = 512;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.nstage; ++s) {
+      mbar_init(bar(FULL + s), 1);
+      mbar_init(bar(EMPTY + s), 1);
+    }
+    for (int s = 0; s < p.nv; ++s) {
+      mbar_init(bar(V_FULL + s), 1);
+      mbar_init(bar(V_EMPTY + s), 1);
+    }
+    for (int i = 0; i < NSW; ++i) {
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(W_FULL + i), 4 * kPartsK);
+      mbar_init(bar(W_FREE + i), 1);
+    }
+    mbar_init(bar(O_FULL), 1);
+    mbar_init(bar(DRAIN), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t o_tmem = tmem_base + NSW * BUFCOLS;
+
+  if (warp == 0) {
+    if (lane == 0) {  // K-chunk ring: for every column tile all chunks of the row block and of the tile
+      int issued = 0;
+      bool ok = true;
+#pragma unroll 1
+      for (int j = 0; ok && j < p.ntiles; ++j) {
+#pragma unroll 1
+        for (int kc = 0; kc < p.nk; ++kc) {
+          const int s = issued % p.nstage;
+          const uint32_t ph = (issued / p.nstage) & 1;
+          if (!mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, 2000)) { ok = false; break; }
+          mbar_expect_tx(bar(FULL + s), kStage);
+          const uint32_t dst = smem_u32(ring + (size_t)s * kStage);
+          tma_load_2d(dst, &mapA, kc * 32, row0, bar(FULL + s));
+          if (MAT5) tma_load_2d(dst + kAChunk, &mapA2, kc * 32, row0, bar(FULL + s));
+          tma_load_2d(dst + kAChunk * (MAT5 ? 2 : 1), &mapB, kc * 32, j * BN, bar(FULL + s));
+          ++issued;
+        }
+      }
+      if (*abort_flag) {
+        for (int j = (issued > p.nstage ? issued - p.nstage : 0); j < issued; ++j)
+          mbar_wait_quiet(bar(FULL + j % p.nstage), (j / p.nstage) & 1);
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {  // V^T tiles (hi and, in split mode, lo) on their own ring
+      int issued = 0;
+#pragma unroll 1
+      for (int j = 0; j < p.ntiles; ++j) {
+        const int s = j % p.nv;
+        const uint32_t ph = (j / p.nv) & 1;
+        if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
+        mbar_expect_tx(bar(V_FULL + s), v_stage);
+        const uint32_t dv_dst = smem_u32(v_smem + (size_t)s * v_stage);
+        for (int kb = 0; kb < BN / 32; ++kb) {
+          tma_load_2d(dv_dst + kb * v_blk, &mapV_hi, j * BN + kb * 32, p.dv0, bar(V_FULL + s));
+          if (SPLIT) tma_load_2d(dv_dst + v_bytes + kb * v_blk, &mapV_lo, j * BN + kb * 32, p.dv0, bar(V_FULL + s));
+        }
+        issued = j + 1;
+      }
+      if (*abort_flag) {
+        for (int j = (issued > p.nv ? issued - p.nv : 0); j < issued; ++j)
+          mbar_wait_quiet(bar(V_FULL + j % p.nv), (j / p.nv) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // score GEMM(s) of tile j into buffer j % NSW, accumulated over the K chunks
+      constexpr uint32_t idesc1 = make_idesc(BN);
+      bool ok = true;
+      int s = 0;
+      uint32_t ph = 0;
+#pragma unroll 1
+      for (int j = 0; ok && j < p.ntiles; ++j) {
+        const int buf = j % NSW;
+        if (!mbar_wait(bar(W_FREE + buf), ((j / NSW) & 1) ^ 1, abort_flag, 2000)) break;
+        tc_fence_after();
+        const uint32_t s_tmem = tmem_base + buf * BUFCOLS;
+        uint32_t acc = 0;
+#pragma unroll 1
+        for (int kc = 0; kc < p.nk; ++kc) {
+          if (!mbar_wait(bar(FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t stage_addr = smem_u32(ring + (size_t)s * kStage);
+          const uint32_t al = desc_lo(stage_addr), a2l = desc_lo(stage_addr + kAChunk),
+                         bl = desc_lo(stage_addr + kAChunk * (MAT5 ? 2 : 1));
+          const int nks = (kc + 1 < p.nk) ? 4 : p.klast;
+#pragma unroll 1
+          for (int ks = 0; ks < nks; ++ks) {
+            umma_tf32(s_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1, acc);
+            if (MAT5)
+              umma_tf32(s_tmem + WCOLS, pack_desc(a2l + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1,
+                        acc);
+            acc = 1;
+          }
+          umma_commit(bar(EMPTY + s));
+          if (++s == p.nstage) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(bar(S_FULL + buf));
+      }
+      if (*abort_flag) {
+        umma_commit(bar(DRAIN));
+        mbar_wait_quiet(bar(DRAIN), 0);
+      }
+    }
+  } else if (warp == 3) {
+    if (lane == 0) {  // second GEMM O += W_j . V_j (W read from TMEM) once the weights of tile j are written
+      const uint32_t idesc2 = make_idesc(p.dv_pad);
+      const uint32_t v_blk_units = v_blk >> 4;
+      uint32_t o_acc = 0;
+#pragma unroll 1
+      for (int j = 0; j < p.ntiles; ++j) {
+        const int sv = j % p.nv, buf = j % NSW;
+        if (!mbar_wait(bar(V_FULL + sv), (j / p.nv) & 1, abort_flag, 2000)) break;
+        if (!mbar_wait(bar(W_FULL + buf), (j / NSW) & 1, abort_flag, 2000)) break;
+        tc_fence_after();
+        const uint32_t w_tmem = tmem_base + buf * BUFCOLS;
+        const uint32_t v_lo0 = desc_lo(smem_u32(v_smem + (size_t)sv * v_stage));
+#pragma unroll 1
+        for (int part = 0; part < (SPLIT ? 3 : 1); ++part) {  // Wh.Vh, Wl.Vh, Wh.Vl
+          uint32_t wa = w_tmem + ((part == 1) ? BN : 0);
+          uint32_t vl = v_lo0 + ((part == 2) ? (v_bytes >> 4) : 0);
+#pragma unroll 1
+          for (int kb = 0; kb < BN / 32; ++kb) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_tf32_ts(o_tmem, wa + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
+              o_acc = 1;
+            }
+            wa += 32;
+            vl += v_blk_units;
+          }
+        }
+        umma_commit(bar(V_EMPTY + sv));
+        umma_commit(bar(W_FREE + buf));
+      }
+      umma_commit(bar(O_FULL));
+      if (*abort_flag) mbar_wait_quiet(bar(O_FULL), 0);
+    }
+  } else if (warp >= 4) {
+    // Two warpgroups share the 128 rows: each takes half of every tile's 32-column chunks.
+    const int part = (warp - 4) >> 2;
+    const int q = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int r = row0 + q * 32 + lane;
+    const float scale = p.scale2;
+    const float negR = (r < p.nr) ? -p.R[r] : 0.f;
+    bool ok = true;
+    constexpr int CH = BN / 32 / kPartsK;
+    const int total = p.ntiles * CH;
+    const int c_base = part * CH;
+    auto issue = [&](int g, uint32_t (&rg)[32]) -> bool {
+      const int j = g / CH, c = g % CH, buf = j % NSW;
+      if (c == 0) {
+        if (!mbar_wait(bar(S_FULL + buf), (j / NSW) & 1, abort_flag)) return false;
+        __syncwarp();
+        tc_fence_after();
+      }
+      tmem_ld32_nowait(lane_addr + buf * BUFCOLS + (c_base + c) * 32, rg);
+      return true;
+    };
+    // Scores of chunk g have landed in rg: turn them into weights, store them back over the scores.
+    auto weigh = [&](int g, uint32_t (&rg)[32]) {
+      const int j = g / CH, c = g % CH, buf = j % NSW;
+      const uint32_t taddr = lane_addr + buf * BUFCOLS + (c_base + c) * 32;
+      float e[32];
+      if (MAT5) tmem_ld32(taddr + WCOLS, e);  // E = rows2 . cols of the same entries
+      float v[32];
+      if (SPLIT) {
+        float lo[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float w = ex2(fmaf(__uint_as_float(rg[i]), scale, negR));
+          if (MAT5) w *= e[i];
+          const float hi = round_tf32_pos(w);
+          lo[i] = round_tf32_pos(w - hi);
+          v[i] = hi;
+        }
+        tmem_st32(taddr + BN, lo);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float w = ex2(fmaf(__uint_as_float(rg[i]), scale, negR));
+          if (MAT5) w *= e[i];
+          v[i] = round_tf32_pos(w);
+        }
+      }
+      tmem_st32(taddr, v);
+      if (c == CH - 1) {  // this warp's share of the tile is written: tell the MMA lane
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(W_FULL + buf));
+      }
+    };
+    auto pipe = [&](int g, uint32_t (&cur)[32], uint32_t (&nxt)[32]) -> bool {
+      tmem_ld_wait(cur);
+      const bool last = (g % CH) == CH - 1;
+      const bool more = g + 1 < total;
+      if (!last && more && !issue(g + 1, nxt)) return false;
+      weigh(g, cur);
+      if (last && more && !issue(g + 1, nxt)) return false;
+      return true;
+    };
+    uint32_t ra[32], rb[32];
+    ok = total > 0 && issue(0, ra);
+#pragma unroll 1
+    for (int g = 0; ok && g < total; g += 2) {
+      ok = pipe(g, ra, rb);
+      if (!ok || g + 1 >= total) break;
+      ok = pipe(g + 1, rb, ra);
+    }
+    if (ok) ok = mbar_wait(bar(O_FULL), 0, abort_flag);
+    __syncwarp();
+    tc_fence_after();
+    // `ok` is warp-uniform. tcgen05.ld is .sync.aligned: rows beyond nr load too, only their stores are masked.
+    if (ok) {
+      const bool valid = r < p.nr;
+      const int rr = valid ? r : 0;
+      const float inv_eps = 1.0f / p.eps;
+      float fac;
+      if (p.epilogue == PV_GRAD) {
+        fac = p.coef * (p.gs ? __ldg(p.gs) : 1.f) * __ldg(p.roww + rr);
+      } else {
+        const float rt = (__ldg(p.rowpot + rr) * inv_eps + (p.rowlogw ? __ldg(p.rowlogw + rr) : 0.f)) * kLog2e;
+        fac = p.coef * ex2(rt - negR);
+      }
+      float* orow = p.out + (size_t)rr * p.ld_out + p.dv0;
+#pragma unroll 1
+      for (int c = part; c < p.dv_pad / 32; c += kPartsK) {  // the warpgroups split the output chunks
+        float o[32];
+        tmem_ld32(lane_addr + NSW * BUFCOLS + c * 32, o);
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            if (p.dv0 + col < p.dv) {
+              float val = o[i];
+              if (p.epilogue == PV_GRAD) val = __ldg(p.rows_raw + (size_t)rr * p.ld_rows + p.dv0 + col) - val;
+              orow[col] = fac * val;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (tid == 0 && *abort_flag) atomicExch(&g_tck_error, 1);
+}
+
 // W = 2^(scale2 * S - R_row), rounded to TF32, written over the scores (pitch ld). In split mode the row holds
 // [Wh | Wl | Wh] in three blocks of cols_pad columns, which the GEMM pairs with [Vh | Vh | Vl]. Columns beyond
 // nc get zero weight without looking at the stored value.
@@ -646,6 +969,129 @@ cudaError_t kstream_vec(const Staged& s, int side, const StreamArgs& a, const Pv
   kp.part_m = s.part_m[side]; kp.part_s = s.part_s[side]; kp.part_stride = s.part_stride; kp.tickets = s.tickets[side];
   kp.R = pa.R; kp.vpad = vpad; kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.vout = pa.out; kp.skip = pa.skip;
   return launch_plan<EPI_VEC>(k, ma, mb, kp, detail::pick_ctas(kp.nblk, kp.ntiles), st);
+}
+
+// ---- narrow plan-times-matrix pass (second GEMM from TMEM) -------------------------------------------
+namespace {
+
+// Second row operand of the Mat5 term in the row-role layout of the staged clouds: [Ah | Ah | Al | 0 ...] in the
+// split mode, [Ah | 0 ...] in TF32 mode, so that its contraction with the staged column operand is A_i . y_j
+// (the bias and label columns of the column operand meet zeros).
+__global__ void stage_rows2_kernel(const float* __restrict__ A, int rows, int rows_pad, int d, int kp, int split,
+                                   float* __restrict__ out) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)rows_pad * kp) return;
+  const int r = (int)(idx / kp), k = (int)(idx % kp);
+  float v = 0.f;
+  if (r < rows && k < (split ? 3 * d : d)) {
+    const float a = A[(size_t)r * d + k % d];
+    const float hi = to_tf32(a);
+    v = (split && k / d == 2) ? to_tf32(a - hi) : hi;
+  }
+  out[idx] = v;
+}
+
+struct KPvPlan {
+  int dv_pad, nslices, vrows, cols_pad, parts, nstage, nv;
+  long long ld_v;
+  size_t vt_bytes, a2_bytes, smem;
+  bool ok;
+};
+
+KPvPlan plan_kpv(int nr, int nc, int kp, int dv, int prec, bool mat5) {
+  KPvPlan k{};
+  const bool split = prec == 1;
+  const int w = dv < 128 ? dv : 128;
+  k.dv_pad = (w + 31) & ~31;
+  k.nslices = (dv + 127) / 128;
+  k.vrows = k.nslices * k.dv_pad;
+  k.cols_pad = detail::pad256(nc);
+  k.parts = split ? 3 : 1;
+  k.ld_v = (long long)k.cols_pad * k.parts;
+  k.vt_bytes = (((size_t)k.vrows * k.ld_v * sizeof(float)) + 1023) & ~size_t(1023);
+  k.a2_bytes = mat5 ? ((((size_t)detail::pad256(nr) * kp * sizeof(float)) + 1023) & ~size_t(1023)) : 0;
+  const size_t stage = (size_t)(mat5 ? 2 : 1) * 128 * 128 + 64 * 128;
+  const size_t v_stage = (size_t)(split ? 2 : 1) * 2 * k.dv_pad * 128;
+  const size_t budget = kSmemMax - 2048;
+  k.nv = (2 * v_stage + 2 * stage <= budget) ? 2 : 1;
+  const size_t rest = budget - k.nv * v_stage;
+  k.nstage = (int)(rest / stage);
+  if (k.nstage > 4) k.nstage = 4;
+  k.ok = k.nstage >= 2;
+  k.smem = k.nv * v_stage + k.nstage * stage + 2048;
+  if (k.smem < (size_t)kSmemMin) k.smem = kSmemMin;
+  return k;
+}
+
+template <bool SPLIT, bool MAT5>
+cudaError_t launch_kpv(const CUtensorMap* maps, const KPvParams& kp, int grid, size_t smem, cudaStream_t st) {
+  auto kern = tck_pv_kernel<SPLIT, MAT5>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, 128 + 128 * kPartsK, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t kstream_pv_scratch(int nr, int nc, int kp, int dv, int prec, bool mat5) {
+  const KPvPlan k = plan_kpv(nr, nc, kp, dv, prec, mat5);
+  return k.ok ? k.vt_bytes + k.a2_bytes + 2048 : 0;
+}
+
+cudaError_t kstream_pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa, char* scratch,
+                       size_t scratch_bytes, cudaStream_t st) {
+  if (!scratch || !pa.R || !pa.V || !pa.out) return cudaErrorInvalidValue;
+  const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
+  const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
+  const bool mat5 = pa.rows2 != nullptr, split = s.prec == 1;
+  const KPvPlan k = plan_kpv(rowc.rows, a.nc, s.kp, pa.dv, s.prec, mat5);
+  if (!k.ok) return cudaErrorNotSupported;
+  if (k.vt_bytes + k.a2_bytes + 2048 > scratch_bytes) return cudaErrorInvalidValue;
+  const float scale2 = (2.0f * a.cost_scale) * (1.0f / a.eps) * kLog2e;
+  detail::launch_bias(colc, s.kc, s.kp, a.pot, a.logw, 1.0f / a.eps, 1.0f / scale2, nullptr, st, a.pot_shard,
+                      a.pot_stride);
+  char* p0 = (char*)(((uintptr_t)scratch + 1023) & ~(uintptr_t)1023);
+  float* vt = reinterpret_cast<float*>(p0);
+  float* a2 = mat5 ? reinterpret_cast<float*>(p0 + k.vt_bytes) : nullptr;
+  {
+    dim3 grid((k.cols_pad + 31) / 32, (k.vrows + 31) / 32), block(32, 8);
+    stage_vt_cat_kernel<<<grid, block, 0, st>>>(pa.V, a.nc, pa.dv, pa.colscale, k.vrows, k.cols_pad, split, vt);
+  }
+  if (mat5) {
+    const size_t total = (size_t)rowc.rows_pad * s.kp;
+    stage_rows2_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(pa.rows2, rowc.rows, rowc.rows_pad, s.d, s.kp,
+                                                                        split, a2);
+  }
+  CUtensorMap maps[5];
+  bool ok = true;
+  ok &= detail::encode_map(&maps[0], rowc.opA, rowc.rows_pad, s.kp, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok &= detail::encode_map(&maps[1], mat5 ? a2 : rowc.opA, rowc.rows_pad, s.kp, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok &= detail::encode_map(&maps[2], colc.opB, colc.rows_pad, s.kp, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok &= detail::encode_map(&maps[3], vt, k.vrows, k.cols_pad, 32, k.dv_pad, CU_TENSOR_MAP_SWIZZLE_128B, k.ld_v);
+  ok &= detail::encode_map(&maps[4], split ? vt + 2 * (size_t)k.cols_pad : vt, k.vrows, k.cols_pad, 32, k.dv_pad,
+                           CU_TENSOR_MAP_SWIZZLE_128B, k.ld_v);
+  if (!ok) return cudaErrorInvalidValue;
+  KPvParams kp{};
+  kp.nr = a.nr; kp.nc = a.nc; kp.row_begin = a.row_begin;
+  kp.ntiles = (a.nc + 63) / 64;
+  KParams chunks{};
+  set_chunks(chunks, s.kp);
+  kp.nk = chunks.nk; kp.klast = chunks.klast; kp.nstage = k.nstage; kp.nv = k.nv;
+  kp.dv = pa.dv; kp.dv_pad = k.dv_pad; kp.ld_out = pa.dv;
+  kp.scale2 = scale2; kp.eps = a.eps; kp.R = pa.R; kp.epilogue = pa.epilogue;
+  kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.roww = pa.roww; kp.gs = pa.gs; kp.coef = pa.coef;
+  kp.rows_raw = a.rows; kp.ld_rows = a.d; kp.out = pa.out; kp.skip = pa.skip;
+  const int grid = (a.nr - a.row_begin + 127) / 128;
+  if (grid <= 0) return cudaSuccess;
+  for (int sl = 0; sl < k.nslices; ++sl) {
+    kp.dv0 = sl * k.dv_pad;
+    cudaError_t e;
+    if (mat5) e = split ? launch_kpv<true, true>(maps, kp, grid, k.smem, st) : launch_kpv<false, true>(maps, kp, grid, k.smem, st);
+    else e = split ? launch_kpv<true, false>(maps, kp, grid, k.smem, st) : launch_kpv<false, false>(maps, kp, grid, k.smem, st);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 // ---- wide plan-times-matrix pass -------------------------------------------------------------------

@@ -77,6 +77,65 @@ def sinkhorn_prelast_potentials_sqeuclid(
     return f_pre, g_pre
 
 
+class _PlanSession:
+    """Applications of one fixed transport plan through ``fs_plan_session_*``: the clouds are staged and the two
+    log-normaliser vectors computed once (two soft-min passes), after which every ``P v``, ``P^T u``, ``P V``,
+    ``P^T V``, Mat5 term and CG matvec is a single streaming pass. The reference launches its kernels one call
+    at a time (hvp.py:322-594); the pass count per Hessian-vector product is the same (10 + 2K there, 11 + 2K
+    here for K CG iterations)."""
+
+    def __init__(self, x, y, f_shift, g_shift, log_a, log_b, *, eps, cost_scale, allow_tf32):
+        self.x, self.y = _lib.f32c(x), _lib.f32c(y)
+        self.n, self.d = self.x.shape
+        self.m = self.y.shape[0]
+        self.dev = self.x.device
+        self.fh, self.gh = _lib.f32c(f_shift), _lib.f32c(g_shift)
+        self.la, self.lb = _lib.f32c(log_a), _lib.f32c(log_b)
+        self.eps, self.cs = float(eps), float(cost_scale)
+        self.prec = _lib.precision_id(allow_tf32)
+        nbytes = int(_lib.load().fs_plan_session_bytes(self.n, self.m, self.d, self.prec))
+        self.ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=self.dev)
+        _lib.call("fs_plan_session_begin", self.dev, *self._head(), self.eps, self.cs, self.prec, *self._tail())
+
+    def _head(self):
+        return (_lib.ptr(self.x), _lib.ptr(self.y), self.n, self.m, self.d, _lib.ptr(self.fh), _lib.ptr(self.gh),
+                _lib.ptr(self.la), _lib.ptr(self.lb))
+
+    def _tail(self):
+        return (_lib.ptr(self.ws), self.ws.numel(), _lib.stream_ptr(self.dev))
+
+    def _apply(self, kind, operand, dv, scale, coef, out, axis):
+        operand = _lib.f32c(operand)
+        scale = None if scale is None else _lib.f32c(scale)
+        _lib.call("fs_plan_session_apply", self.dev, *self._head(), kind, _lib.ptr(operand), dv, _lib.ptr(scale),
+                  float(coef), _lib.ptr(out), axis, self.eps, self.cs, self.prec, *self._tail())
+        return out
+
+    def vec(self, v, axis):
+        rows = self.n if axis == 1 else self.m
+        return self._apply(0, v, 1, None, 1.0, torch.empty((rows,), device=self.dev, dtype=torch.float32), axis)
+
+    def mat(self, V, axis, scale=None):
+        rows = self.n if axis == 1 else self.m
+        out = torch.empty((rows, V.shape[1]), device=self.dev, dtype=torch.float32)
+        return self._apply(1, V, V.shape[1], scale, 1.0, out, axis)
+
+    def mat5(self, A, coef):
+        out = torch.empty((self.n, self.d), device=self.dev, dtype=torch.float32)
+        return self._apply(2, A, self.d, None, coef, out, 1)
+
+    def schur_cg(self, diag_x, denom, rhs, *, max_iter, rtol, atol):
+        z = torch.empty((self.m,), device=self.dev, dtype=torch.float32)
+        info = torch.zeros((4,), device=self.dev, dtype=torch.float32)
+        dx, dn, rh = _lib.f32c(diag_x), _lib.f32c(denom), _lib.f32c(rhs)
+        _lib.call("fs_plan_session_cg", self.dev, *self._head(), _lib.ptr(dx), _lib.ptr(dn), _lib.ptr(rh),
+                  _lib.ptr(z), _lib.ptr(info), self.eps, self.cs, int(max_iter), float(rtol), float(atol),
+                  self.prec, *self._tail())
+        rec = info.tolist()
+        _lib.raise_if_device_timeout(self.dev)  # the record read has synchronised: surface a device-side time-out
+        return z, CGInfo(bool(rec[0] != 0.0), int(rec[1]), float(rec[2]), float(rec[3]))
+
+
 def _device_schur_cg(x, y, f_shift, g_shift, log_a, log_b, diag_x, denom, rhs, *, eps, cost_scale,
                      max_iter, rtol, atol, allow_tf32):
     n, d = x.shape
@@ -168,16 +227,17 @@ def hvp_x_sqeuclid_from_potentials(
     log_b = torch.full((m,), -math.log(m), device=dev, dtype=torch.float32)
     f_shift = (f_hat.float() - e * log_a - cost_scale * xf.pow(2).sum(dim=1)).contiguous()
     g_shift = (g_hat.float() - e * log_b - cost_scale * yf.pow(2).sum(dim=1)).contiguous()
-    kw = dict(eps=e, cost_scale=cost_scale, allow_tf32=allow_tf32)
+    # One session for all plan applications below: operands staged once, both normalisers computed once.
+    plan = _PlanSession(xf, yf, f_shift, g_shift, log_a, log_b, eps=e, cost_scale=cost_scale, allow_tf32=allow_tf32)
 
     def P(v):   # [m] -> [n]
-        return apply_plan_vec_flashstyle(x, y, f_shift, g_shift, log_a, log_b, v, axis=1, **kw)
+        return plan.vec(v, 1)
 
     def Pt(u):  # [n] -> [m]
-        return apply_plan_vec_flashstyle(x, y, f_shift, g_shift, log_a, log_b, u, axis=0, **kw)
+        return plan.vec(u, 0)
 
     def Pmat(V, axis, scale=None):
-        return apply_plan_mat_flashstyle(x, y, f_shift, g_shift, log_a, log_b, V, axis=axis, scale=scale, **kw)
+        return plan.mat(V, axis, scale)
 
     row_mass = P(torch.ones((m,), device=dev, dtype=torch.float32))
     col_mass = Pt(torch.ones((n,), device=dev, dtype=torch.float32))
@@ -203,10 +263,7 @@ def hvp_x_sqeuclid_from_potentials(
     if mode == "none":
         rhs = rhs_raw
         if cg_x0 is None and int(cg_stabilise_every) == 0:
-            z, cg = _device_schur_cg(
-                x, y, f_shift, g_shift, log_a, log_b, D_x, denom, rhs.contiguous(), eps=e,
-                cost_scale=cost_scale, max_iter=max_cg_iter, rtol=cg_rtol, atol=cg_atol, allow_tf32=allow_tf32,
-            )
+            z, cg = plan.schur_cg(D_x, denom, rhs.contiguous(), max_iter=max_cg_iter, rtol=cg_rtol, atol=cg_atol)
         else:
             z, cg = conjugate_gradient(schur, rhs, x0=cg_x0, max_iter=max_cg_iter, rtol=cg_rtol,
                                        atol=cg_atol, stabilise_every=cg_stabilise_every)
@@ -237,7 +294,7 @@ def hvp_x_sqeuclid_from_potentials(
     term2 = -k2 * x * (xa * row_mass)[:, None]
     term3 = k2 * Py * xa[:, None]
     term4 = k2 * x * (Py * A).sum(dim=1)[:, None]
-    term5 = mat5_sqeuclid(x, y, f_hat, g_hat, A, eps=e, cost_scale=cost_scale, allow_tf32=allow_tf32)
+    term5 = plan.mat5(Af, -2.0 * c / e)  # (-4 cs / eps) sum_j P_ij (A_i . y_j) y_j, reference kernels/apply_ott.py:453-566
 
     psd = RTz / e + term1
     indef = term2 + term3 + term4 + term5

@@ -358,6 +358,34 @@ int fs_schur_cg(const float* x, const float* y, int n, int m, int d,
                 float eps, float cost_scale, int max_iter, float rtol, float atol,
                 int prec, void* ws, size_t ws_bytes, void* stream);
 
+/* ---- Plan session (no reference counterpart as an API; replaces the repeated launches inside the
+ * reference's hvp.py:282-623) ------------------------------------------------------------------------------
+ * Many applications of ONE transport plan P = diag(a) exp((f_hat + g_hat + 2cs x.y)/eps) diag(b): the operands
+ * are staged and the two log-normaliser vectors computed ONCE (fs_plan_session_begin: two soft-min passes); every
+ * later application then costs a single streaming pass. All calls of a session take the same x, y, sizes,
+ * potentials, eps, cost_scale, prec and the same workspace of fs_plan_session_bytes() bytes; nothing else may
+ * write that workspace in between. The Hessian-vector product uses it: 11 + 2K passes for K CG iterations
+ * (the reference launches 10 + 2K kernels, hvp.py:164-623). */
+size_t fs_plan_session_bytes(int n, int m, int d, int prec);
+int fs_plan_session_begin(const float* x, const float* y, int n, int m, int d,
+                          const float* f_hat, const float* g_hat, const float* log_a, const float* log_b,
+                          float eps, float cost_scale, int prec, void* ws, size_t ws_bytes, void* stream);
+/* kind 0: out = P v (axis 1, operand [m]) or P^T u (axis 0, operand [n]); reference
+ * kernels/apply_flash.py:835-951. kind 1: out = P V / P^T V with dv <= d columns and an optional per-point
+ * `scale` of V's rows (axis 1 only); kernels/apply_flash.py:360-579. kind 2: the Mat5 term
+ * out_i = coef * sum_j P_ij (A_i . y_j) y_j with operand = A [n, d], axis 1, dv = d; kernels/apply_ott.py:453-566
+ * (coef = -4 cs / eps there). */
+int fs_plan_session_apply(const float* x, const float* y, int n, int m, int d,
+                          const float* f_hat, const float* g_hat, const float* log_a, const float* log_b,
+                          int kind, const float* operand, int dv, const float* scale, float coef, float* out,
+                          int axis, float eps, float cost_scale, int prec, void* ws, size_t ws_bytes, void* stream);
+/* fs_schur_cg inside a session (no staging, no normaliser passes): reference hvp.py:505-520, cg.py:27-121. */
+int fs_plan_session_cg(const float* x, const float* y, int n, int m, int d,
+                       const float* f_hat, const float* g_hat, const float* log_a, const float* log_b,
+                       const float* diag_x, const float* denom, const float* rhs, float* z, float* info,
+                       float eps, float cost_scale, int max_iter, float rtol, float atol, int prec,
+                       void* ws, size_t ws_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,7 +79,7 @@ def check(name, got, want, tol, log):
 
 
 def run_symmetric_checks(x, y, a, b, *, eps, n_iters, cs, tf32, rho_x=None, rho_y=None, tol_pot, tol_grad, tol_mat,
-                         threshold=None, tag=""):
+                         threshold=None, tag="", check_mat=True):
     """Solve on the GPU, then check on sampled rows / columns: the last (extrapolation) step of the solver as a
     soft-min of the pre-extrapolation potentials, the gradient rows at those potentials, and plan-times-matrix rows."""
     from flash_sinkhorn_b200.kernels._common import dampening, log_weights
@@ -118,6 +118,11 @@ def run_symmetric_checks(x, y, a, b, *, eps, n_iters, cs, tf32, rho_x=None, rho_
     ok &= check(f"{tag} grad_x rows", gx[ri], want_gx, tol_grad, log)
     ok &= check(f"{tag} grad_y rows", gy[cj], want_gy, tol_grad, log)
     # 3. plan-times-matrix rows (dv = d, as the reference API requires) at the final potentials
+    if not check_mat:
+        if VERBOSE:
+            print("\n".join(log))
+        assert ok, "\n".join(log)
+        return
     gen = torch.Generator().manual_seed(7)
     V = torch.randn(m, d, generator=gen).cuda()
     fh, gh = (f.double() - alpha).float(), (g.double() - beta).float()
@@ -173,8 +178,11 @@ def test_config4_sampled_rows():
     y = (1.5 * torch.randn(m, d, generator=gen)).cuda()
     a = torch.softmax(torch.randn(n, generator=gen), 0).cuda()
     b = (1.3 * torch.softmax(torch.randn(m, generator=gen), 0)).cuda()
+    # The plan itself is not compared here: with |x - y|^2 ~ 400 against reach^2 = 1 the relaxed plan destroys
+    # the mass instead of moving it, and its entries exp(-C/eps) underflow fp32 (the property test of this
+    # configuration checks exactly that); soft-mins and gradient rows are scale-free and are compared.
     run_symmetric_checks(x, y, a, b, eps=0.04, n_iters=500, cs=1.0, tf32=True, rho_x=1.0, rho_y=1.0, threshold=1e-3,
-                         tol_pot=2e-5, tol_grad=1e-3, tol_mat=2e-2, tag="C4 tf32")
+                         tol_pot=2e-5, tol_grad=1e-3, tol_mat=2e-2, tag="C4 tf32", check_mat=False)
 
 
 @pytest.mark.parametrize("tf32", [True, False])
@@ -210,11 +218,16 @@ def test_config3_sampled_rows(tf32):
             return -eps * torch.logsumexp(t, dim=1)
 
         tag = f"C3 {'tiles' if tiles is not None else 'dense'} tf32={tf32}"
-        # f from g = 0: shifted g_hat = -beta (unrounded norms) against rounded points, as the engine stages them
+        # f from g = 0: shifted g_hat = -beta (unrounded norms) against rounded points, as the engine stages them.
+        # The clouds overlap, so f = f_hat + |x|^2 is a small difference (~1e-3) of two numbers of size |x|^2 ~ 1-3
+        # that the engine holds in fp32: the error is measured against that size (2e-6 = a few fp32 ulps).
+        scale_f, scale_g = float(alpha.max()), float(beta.max())
         want_f = masked(ri, xr[ri], yr, -beta + br, False) - ar[ri] + alpha[ri]
-        ok &= check(f"{tag} f rows", f[ri], want_f, 5e-5, log)
+        err_f = float((f[ri].double() - want_f).abs().max() / scale_f)
         want_g = masked(cj, yr[cj], xr, f.double() - alpha + ar, True) - br[cj] + beta[cj]
-        ok &= check(f"{tag} g cols", g[cj], want_g, 5e-5, log)
+        err_g = float((g[cj].double() - want_g).abs().max() / scale_g)
+        log.append(f"{tag} f rows / |x|^2: {err_f:.2e}, g cols / |y|^2: {err_g:.2e} (tol 2e-06)")
+        ok &= err_f <= 2e-6 and err_g <= 2e-6
     if VERBOSE or not ok:
         print("\n".join(log))
     assert ok, "\n".join(log)

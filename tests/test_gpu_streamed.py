@@ -34,7 +34,8 @@ def _r(got, want):
     return float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp_min(1e-30))
 
 
-SHAPES = [(700, 900, 300), (700, 900, 128), (600, 1100, 2048), (257, 130, 515), (1, 300, 1025), (300, 1, 260)]
+SHAPES = [(700, 900, 300), (700, 900, 128), (600, 1100, 2048), (257, 130, 515), (1, 300, 1025), (300, 1, 260),
+          (400, 500, 230), (130, 3000, 90)]
 
 
 @pytest.mark.parametrize("tf32", [False, True])
