@@ -429,12 +429,74 @@ def bench_extra(args):
         dist.destroy_process_group()
     return 0
 
+def bench_reference_triton(args):
+    """The UNMODIFIED reference package (its Triton kernels, JIT-compiled for this GPU) on the same workload, when an
+    install of it is present under baseline/_ref. Context for the numbers of this library: the kernel to beat. Not
+    part of the product; `--impl reference` (the reference's CPU path) is the arm the contract asks for."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    try:
+        sys.path.insert(0, ref_dir)
+        import torch
+        from flash_sinkhorn import SamplesLoss as RefLoss  # noqa: the reference's own public API
+    except Exception as exc:  # pragma: no cover
+        print(json.dumps({"impl": "reference_triton", "unavailable": f"{type(exc).__name__}: {exc}"[:200]}))
+        return 0
+    dev = torch.device("cuda", 0)
+    cfg = args.config
+    if cfg == "5":
+        n = m = args.n or 16384
+        d, iters, eps = args.d or 2048, 50, 0.0025
+        gen = torch.Generator().manual_seed(4)
+        x = torch.nn.functional.normalize(torch.randn(n, d, generator=gen), dim=1).to(dev)
+        y = torch.nn.functional.normalize(torch.randn(m, d, generator=gen), dim=1).to(dev)
+        loss_fn = RefLoss("sinkhorn", blur=0.05, reach_x=1.0, reach_y=None, half_cost=True, use_epsilon_scaling=False,
+                          eps=eps, n_iters=iters, allow_tf32=not args.fp32)
+        per_step = 2.0 * (iters + 2) * n * m + float(n) * m
+        entries_ref = per_step
+    else:
+        n = m = args.n or 50000
+        d, iters, eps = args.d or 64, args.iters, 0.01
+        gen = torch.Generator().manual_seed(1)
+        x = torch.randn(n, d, generator=gen).to(dev)
+        y = (0.5 + torch.randn(m, d, generator=gen)).to(dev)
+        loss_fn = RefLoss("sinkhorn", blur=0.1, use_epsilon_scaling=False, eps=eps, n_iters=iters, half_cost=False,
+                          debias=True, allow_tf32=not args.fp32)
+        per_step = entries_per_step(n, m, iters, True)
+        # the reference evaluates both soft-mins of the self terms: what it actually computes per step
+        entries_ref = 2 * (iters + 2) * (n * m + n * n + m * m) + n * m + 2 * n * n
+
+    def step():
+        xs = x.detach().requires_grad_(True)
+        val = loss_fn(xs, y)
+        (gx,) = torch.autograd.grad(val, xs)
+        return val
+
+    for _ in range(max(1, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        val = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"impl": "reference_triton", "metric": "cost_entries_per_sec", "value": per_step / (ms * 1e-3),
+                      "unit": "entries/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                      "config": {"workload": f"config{cfg}: n=m={n} d={d} eps={eps} n_iters={iters}, stock SamplesLoss "
+                                             "of the reference package (Triton JIT on this GPU), forward + grad_x",
+                                 "entries_counted": per_step, "entries_the_reference_evaluates": entries_ref,
+                                 "loss": float(val)},
+                      "dtype": "fp32 (allow_tf32=False)" if args.fp32 else "tf32 (reference default)"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_triton"])
     ap.add_argument("--config", default="2", choices=["2", "3", "3csr", "4", "5"],
                     help="benchmark configuration (default 2, the one the headline metric is quoted on)")
     ap.add_argument("--n", type=int, default=None)
@@ -448,6 +510,8 @@ def main():
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"2": 3, "3": 1, "3csr": 1, "4": 1, "5": 3}[args.config]
+    if args.impl == "reference_triton":
+        return bench_reference_triton(args)
     if args.config != "2" and args.impl == "b200":
         return bench_extra(args)
     if args.n is None:
