@@ -36,8 +36,39 @@ def _worker(rank, world, port, out_dir):
             (gx,) = torch.autograd.grad(val, x)
             torch.cuda.synchronize()
             np.savez(os.path.join(out_dir, f"r{rank}_{int(tf32)}.npz"), loss=val.item(), gx=gx.cpu().numpy())
+        # large feature dimension (K-streamed kernels, gradient through the weight matrix), semi-unbalanced
+        xl, yl = _large_d_clouds()
+        xl = xl.cuda().requires_grad_(True)
+        loss = SamplesLoss("sinkhorn", blur=0.3, reach_x=1.0, half_cost=True, use_epsilon_scaling=False, eps=0.09,
+                           n_iters=8, process_group=dist.group.WORLD)
+        val = loss(xl, yl.cuda())
+        (gx,) = torch.autograd.grad(val, xl)
+        np.savez(os.path.join(out_dir, f"r{rank}_large_d.npz"), loss=val.item(), gx=gx.cpu().numpy())
+        # block-sparse annealed alternating solve, rows split over the ranks by kept tiles
+        from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating
+        xs, ys, a, b, mask = _sparse_problem()
+        f, g = sinkhorn_flashstyle_alternating(xs.cuda(), ys.cuda(), a.cuda(), b.cuda(), eps_list=[0.5, 0.1],
+                                               iters_per_eps=3, tile_mask=mask, process_group=dist.group.WORLD)
+        np.savez(os.path.join(out_dir, f"r{rank}_tiles.npz"), f=f.cpu().numpy(), g=g.cpu().numpy())
     finally:
         dist.destroy_process_group()
+
+
+def _large_d_clouds():
+    gen = torch.Generator().manual_seed(8)
+    return (torch.nn.functional.normalize(torch.randn(900, 700, generator=gen), dim=1),
+            torch.nn.functional.normalize(torch.randn(1100, 700, generator=gen), dim=1))
+
+
+def _sparse_problem():
+    gen = torch.Generator().manual_seed(9)
+    n, m = 2000, 1700
+    x, y = torch.rand(n, 3, generator=gen), torch.rand(m, 3, generator=gen)
+    mask = torch.rand((n + 127) // 128, (m + 127) // 128, generator=gen) < 0.4
+    mask[:, 0] = True
+    mask[0, :] = True
+    mask[3:6, 1:] = False  # few tiles in these row blocks: the kept-tile split is far from the row split
+    return x, y, torch.full((n,), 1.0 / n), torch.full((m,), 1.0 / m), mask
 
 
 def test_sharded_two_gpu_equals_single_gpu(tmp_path):
@@ -65,3 +96,24 @@ def test_sharded_two_gpu_equals_single_gpu(tmp_path):
             assert np.abs(z["gx"] - want).max() <= (2e-3 if tf32 else 2e-4) * np.abs(want).max()
         z0, z1 = (np.load(tmp_path / f"r{r}_{int(tf32)}.npz") for r in range(2))
         assert np.array_equal(z0["gx"], z1["gx"])  # all ranks hold identical results
+    # large d: K-streamed passes and the weight-matrix gradient, sharded vs single GPU
+    xl, yl = _large_d_clouds()
+    xl = xl.cuda().requires_grad_(True)
+    loss = SamplesLoss("sinkhorn", blur=0.3, reach_x=1.0, half_cost=True, use_epsilon_scaling=False, eps=0.09, n_iters=8)
+    val = loss(xl, yl.cuda())
+    (gx,) = torch.autograd.grad(val, xl)
+    for r in range(world):
+        z = np.load(tmp_path / f"r{r}_large_d.npz")
+        assert abs(float(z["loss"]) - val.item()) <= 1e-5 * abs(val.item())
+        assert np.abs(z["gx"] - gx.cpu().numpy()).max() <= 2e-3 * np.abs(gx.cpu().numpy()).max()
+    # block-sparse alternating solve: split by kept tiles vs single GPU
+    from flash_sinkhorn_b200.sinkhorn_solvers import sinkhorn_flashstyle_alternating
+    xs, ys, a, b, mask = _sparse_problem()
+    f, g = sinkhorn_flashstyle_alternating(xs.cuda(), ys.cuda(), a.cuda(), b.cuda(), eps_list=[0.5, 0.1], iters_per_eps=3,
+                                           tile_mask=mask)
+    for r in range(world):
+        z = np.load(tmp_path / f"r{r}_tiles.npz")
+        assert np.abs(z["f"] - f.cpu().numpy()).max() <= 2e-3 * np.abs(f.cpu().numpy()).max()
+        assert np.abs(z["g"] - g.cpu().numpy()).max() <= 2e-3 * np.abs(g.cpu().numpy()).max()
+    z0, z1 = (np.load(tmp_path / f"r{r}_tiles.npz") for r in range(2))
+    assert np.array_equal(z0["f"], z1["f"]) and np.array_equal(z0["g"], z1["g"])
