@@ -404,6 +404,8 @@ size_t fs_apply_mat_plan_bytes(int n, int m, int d, int dv, int prec) {
 
 int fs_set_cta_limit(int k) { return tc::set_cta_limit(k); }
 
+int fs_set_wide_tile_min_chunks(int k) { return tc::set_wide_tile_min_chunks(k); }
+
 int fs_engine(int n, int m, int d, int prec) {
   if (prec == FS_PREC_SIMT || !tc::supported(n, m, d, prec, 0)) return 0;
   return tc::k_streamed(d, prec, 0) ? 2 : 1;

@@ -82,6 +82,9 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& p, 
 // mode) both operands stream through shared memory in 32-float K chunks and the score tile accumulates in
 // TMEM over the chunks. lse() and pv() route there by themselves; the functions below are their back ends.
 bool k_streamed(int d, int prec, int nlab = 0);
+// Tuning knob of the K-streamed kernels: contractions of at least k 32-float chunks take 256 x 256 tiles with
+// one accumulator per half, shorter ones 256 x 128 tiles with two (returns the previous value).
+int set_wide_tile_min_chunks(int k);
 // lse() takes a block-sparse list of kept 128 x 128 tiles (StreamArgs::tile_row_ptr / tile_col_idx) for these
 // shapes; the row range must then start on a multiple of 128.
 bool csr_supported(int d, int prec, int nlab = 0);

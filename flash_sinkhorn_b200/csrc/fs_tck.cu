@@ -28,6 +28,8 @@
 
 #include <cudaTypedefs.h>
 
+#include <atomic>
+
 namespace fs {
 namespace tc {
 
@@ -875,10 +877,12 @@ struct KPlan {
 // (the epilogue of a tile is a few per cent of its MMA time there), shorter ones 256 x 128 tiles with two
 // accumulators per half so that the epilogue of one tile overlaps the MMAs of the next. `ncols` caps the tile
 // width for narrow outputs.
+std::atomic<int> g_wide_min_chunks{24};
+
 KPlan plan_k(int nk, int ncols) {
   KPlan k{};
   k.nhalf = 2;
-  const bool wide = nk >= 24 && ncols > 128;
+  const bool wide = nk >= g_wide_min_chunks.load(std::memory_order_relaxed) && ncols > 128;
   k.bn = wide ? 256 : 128;
   k.nbuf = wide ? 1 : 2;
   const size_t stage = (size_t)(k.nhalf * 128 + k.bn) * 128;
@@ -920,6 +924,11 @@ void set_chunks(KParams& kp, long long k_floats) {
 }
 
 }  // namespace
+
+int set_wide_tile_min_chunks(int k) {
+  if (k < 1) k = 1;
+  return g_wide_min_chunks.exchange(k, std::memory_order_relaxed);
+}
 
 cudaError_t kstream_lse(const Staged& s, int side, const StreamArgs& a, const LseEpilogue& e, float* s_out,
                         long long ld_s, cudaStream_t st) {

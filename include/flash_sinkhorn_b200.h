@@ -111,6 +111,11 @@ int fs_set_reserved_sms(int k);
  * CTA covering many row blocks, many CTAs sharing one) without touching the environment. */
 int fs_set_cta_limit(int k);
 
+/* Tuning knob (no reference counterpart): K-streamed passes whose contraction has at least k chunks of 32
+ * floats use 256 x 256 score tiles with one TMEM accumulator per 128-row half, shorter ones 256 x 128 tiles
+ * with two accumulators per half. Returns the previous value. */
+int fs_set_wide_tile_min_chunks(int k);
+
 /* Which engine serves a problem of these sizes (no reference counterpart): 0 = CUDA-core fp32 FMA, 1 = tcgen05
  * with the row operand resident in shared memory, 2 = tcgen05 with both operands streamed in K chunks. */
 int fs_engine(int n, int m, int d, int prec);
