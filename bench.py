@@ -700,6 +700,13 @@ def main():
     s1.record()
     barrier()
     ms_solve = s0.elapsed_time(s1) / 3
+    # Host time to ENQUEUE one such solve (nothing inside it synchronises): Python loop, ctypes calls, tensor-map
+    # encodes and NCCL launches. Next to the device time above it shows whether the host or the GPU binds.
+    torch.cuda.synchronize()
+    h0 = time.perf_counter()
+    solve_once()
+    host_enqueue_ms = (time.perf_counter() - h0) * 1e3
+    barrier()
 
     times = torch.tensor([ms, ms_e2e, ms_solve], device=dev, dtype=torch.float64)
     if world > 1:
@@ -738,6 +745,7 @@ def main():
                        "ms_per_100iter_solve": ms_solve,
                        "ms_per_100iter_solve_note": "one OT(x,y) solve, debias off, last_extrapolation off "
                                                     f"({iters + 1} Jacobi steps), timed directly",
+                       "host_enqueue_ms_per_100iter_solve": host_enqueue_ms,
                        "apply_plan_mat_ms": apply_ms,
                        # results of the last step, so that N-GPU and 1-GPU runs can be compared from the records
                        "loss": loss_val, "grad_x_abs_sum": float(gx.double().abs().sum().item()),
