@@ -1111,6 +1111,7 @@ constexpr int kMaxChunks = 16;
 
 std::atomic<int> g_reserved_sms{0};
 std::atomic<int> g_cta_limit{0};
+std::atomic<int> g_prefer_streamed{1};
 
 }  // namespace
 
@@ -1202,6 +1203,8 @@ int set_cta_limit(int k) {
   if (k < 0) k = 0;
   return g_cta_limit.exchange(k, std::memory_order_relaxed);
 }
+
+int set_prefer_streamed(int on) { return g_prefer_streamed.exchange(on ? 1 : 0, std::memory_order_relaxed); }
 
 int plan_ctas(int nblk, int ntiles, int sms, int reserved, int limit) {
   if (nblk <= 0 || ntiles <= 0 || sms <= 0) return 0;
@@ -1322,6 +1325,10 @@ cudaError_t stream_pass(const Staged& s, int side, const StreamArgs& a, const Ls
   const bool am = out_idx != nullptr;
   if (csr && (am || !a.tile_col_idx || (a.row_begin & 127))) return cudaErrorNotSupported;
   if (sh.streamed) return am ? cudaErrorNotSupported : kstream_lse(s, side, a, e, nullptr, 0, st);
+  // A resident plan that only fits 64-column tiles issues half-efficient MMAs (N = 64); the K-streamed kernel
+  // with its 256 x 128 tiles is faster there (d = 64 in the exact mode: K = 195), unless a knob says otherwise.
+  if (sh.bn == 64 && !am && !csr && g_prefer_streamed.load(std::memory_order_relaxed))
+    return kstream_lse(s, side, a, e, nullptr, 0, st);
   const CloudOps& rowc = s.cloud[side == 0 ? 0 : 1];
   const CloudOps& colc = s.cloud[side == 0 ? 1 : 0];
   // LSE: logit = scale2 * (x.y + bias/scale2). Arg-max: cost = -2cs * (x.y - bias/(2cs)), so the column
@@ -1491,6 +1498,8 @@ size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab) {
 
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa, char* scratch, cudaStream_t st) {
   Shape sh = plan_shape(s.d, s.prec, s.nlab);
+  if (sh.ok && pa.dv == 1 && !pa.rows2 && sh.bn == 64 && !sh.streamed && g_prefer_streamed.load(std::memory_order_relaxed))
+    return kstream_vec(s, side, a, pa, scratch, st);
   if (sh.ok && (sh.streamed || pa.rows2)) {
     if (pa.dv == 1 && !pa.rows2) return kstream_vec(s, side, a, pa, scratch, st);
     // the caller sized the scratch with pv_scratch_bytes / mat5_scratch_bytes for these sizes

@@ -33,6 +33,9 @@ struct Staged {
 
 // Streaming passes leave `k` SMs unused from now on (process-wide; returns the previous value).
 int set_reserved_sms(int k);
+// Shapes whose resident-operand plan only fits 64-column score tiles run their soft-min and plan-times-vector
+// passes on the K-streamed kernels (on = 1, the default) or on the resident ones (0). Returns the previous value.
+int set_prefer_streamed(int on);
 // Streaming passes use at most `k` CTAs from now on (0 = no limit; returns the previous value). Test knob.
 int set_cta_limit(int k);
 // CTA count a streaming pass over nblk row blocks x ntiles column tiles would get on a device with `sms`

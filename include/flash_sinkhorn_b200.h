@@ -116,6 +116,12 @@ int fs_set_cta_limit(int k);
  * with two accumulators per half. Returns the previous value. */
 int fs_set_wide_tile_min_chunks(int k);
 
+/* Tuning knob (no reference counterpart): shapes whose row operand fits in shared memory only next to
+ * 64-column score tiles (e.g. d = 64 in the exact mode) run their soft-min and plan-times-vector passes on the
+ * K-streamed kernels (on != 0, the default: larger, MMA-efficient tiles) or on the resident-operand kernels
+ * (on = 0). Returns the previous value. */
+int fs_set_prefer_streamed(int on);
+
 /* Which engine serves a problem of these sizes (no reference counterpart): 0 = CUDA-core fp32 FMA, 1 = tcgen05
  * with the row operand resident in shared memory, 2 = tcgen05 with both operands streamed in K chunks. */
 int fs_engine(int n, int m, int d, int prec);
