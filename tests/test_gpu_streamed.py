@@ -8,6 +8,7 @@ mode the engine solves the exact problem for the TF32-rounded points, so it is c
 rounded the same way (round-to-nearest onto 10 mantissa bits) - 2e-3 on soft-mins, plan-times-vector and
 gradients, 1e-2 on plan-times-matrix (weights and matrix are rounded to TF32 once more for the second product).
 """
+import math
 import os
 
 import numpy as np
@@ -335,3 +336,36 @@ def test_fused_sharded_debiased_solves_on_a_one_rank_group(monkeypatch):
     finally:
         if own_group:
             dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("d,tf32", [(64, False), (160, True), (100, True)])
+def test_resident_and_streamed_kernels_agree_on_shapes_both_can_serve(d, tf32):
+    """Shapes whose resident-operand plan only fits 64-column tiles run on the K-streamed kernels by default; the
+    resident kernels stay selectable (`fs_set_prefer_streamed(0)`) and are what multi-pass launches use. Both
+    contract the same staged operands in the same K order, so soft-mins and plan-times-vector agree to rounding."""
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_vec_flashstyle
+    from flash_sinkhorn_b200.kernels.sinkhorn_flashstyle_sqeuclid import flashsinkhorn_lse
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(d)
+    n, m = 1900, 2300
+    x = (torch.randn(n, d, generator=g) / d**0.5).cuda()
+    y = (torch.randn(m, d, generator=g) / d**0.5).cuda()
+    bias = torch.randn(m, generator=g).cuda()
+    la, lb = torch.full((n,), -math.log(n)).cuda(), torch.full((m,), -math.log(m)).cuda()
+    gh = -(y**2).sum(1)
+    v = torch.randn(m, generator=g).cuda()
+    out = {}
+    previous = lib.fs_set_prefer_streamed(1)
+    try:
+        for on in (1, 0):
+            lib.fs_set_prefer_streamed(on)
+            f = flashsinkhorn_lse(x, y, bias, 0.1, allow_tf32=tf32)
+            fh = flashsinkhorn_lse(x, y, gh / 0.1 + lb, 0.1, allow_tf32=tf32)
+            pv = apply_plan_vec_flashstyle(x, y, fh, gh, la, lb, v, eps=0.1, axis=1, allow_tf32=tf32)
+            out[on] = (f, pv)
+    finally:
+        lib.fs_set_prefer_streamed(previous)
+    assert _r(out[1][0], out[0][0]) < 2e-6
+    assert _r(out[1][1], out[0][1]) < 2e-5
+    assert lib.fs_device_error() == 0
