@@ -78,6 +78,7 @@ SIGNATURES = {
          c_int, _P, c_size_t, _P],
     ),
     "fs_symmetric_step_multi": (c_int, [_P, c_int, c_int, c_int, _P]),
+    "fs_solve_symmetric_batched": (c_int, [_P, c_int, c_int, c_int, c_float, c_double, c_double, c_int, _P]),
     "fs_grad_range": (
         c_int,
         [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_float,
@@ -272,6 +273,14 @@ class StepItem(ctypes.Structure):
                 ("f_begin", c_int), ("f_end", c_int), ("g_begin", c_int), ("g_end", c_int), ("restage", c_int),
                 ("ws", c_void_p), ("ws_bytes", c_size_t),
                 ("f_shard", c_int), ("g_shard", c_int), ("pack_stride", c_int)]
+
+
+class BatchItem(ctypes.Structure):
+    """``fs_batch_item`` of the C header (one problem of a batched symmetric solve)."""
+
+    _fields_ = [("x", c_void_p), ("y", c_void_p), ("n", c_int), ("m", c_int), ("log_a", c_void_p), ("log_b", c_void_p),
+                ("eps_list_host", c_void_p), ("n_eps", c_int), ("f", c_void_p), ("g", c_void_p),
+                ("f_pre", c_void_p), ("g_pre", c_void_p), ("ws", c_void_p), ("ws_bytes", c_size_t)]
 
 
 def stream_ptr(device: torch.device) -> int:

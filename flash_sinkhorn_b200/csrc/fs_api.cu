@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 namespace fs {
 namespace {
@@ -981,6 +982,122 @@ extern "C" int fs_symmetric_step_multi(const fs_step_item* items, int n_items, i
       FS_CUDA(owner->use_tc ? tc::lse(*mp.s, mp.side, mp.a, mp.e, st) : simt_lse(mp.a, mp.e, st));
     }
   }
+  return FS_OK;
+}
+
+// Several symmetric solves in lockstep (batched inputs, or the three problems of a debiased loss): every step of
+// all problems that still have one goes out as fused multi-pass launches, so B small problems cost about one
+// solve's worth of launches instead of B. Schedules may differ in length; a finished problem drops out.
+extern "C" int fs_solve_symmetric_batched(const fs_batch_item* items, int n_items, int d, int last_extrapolation,
+                                          float cost_scale, double rho_x, double rho_y, int prec, void* stream) {
+  constexpr int kMaxBatch = 256;
+  if (!items || n_items <= 0 || n_items > kMaxBatch)
+    return fail(FS_ERR_BAD_ARG, "fs_solve_symmetric_batched takes 1..%d items", kMaxBatch);
+  FS_TRY(check_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  struct Item {
+    Problem p;
+    SolveBufs b;
+    int cur = 0, steps = 0;
+    bool self_problem = false;
+  };
+  std::vector<Item> its(n_items);
+  int max_steps = 0;
+  for (int i = 0; i < n_items; ++i) {
+    const fs_batch_item& in = items[i];
+    if (!in.eps_list_host || in.n_eps <= 0) return fail(FS_ERR_BAD_ARG, "item %d: eps_list must be non-empty", i);
+    FS_TRY(check_common(in.x, in.y, in.n, in.m, d, (float)in.eps_list_host[0], cost_scale, prec));
+    for (int k = 0; k < in.n_eps; ++k)
+      if (!(in.eps_list_host[k] > 0.0)) return fail(FS_ERR_BAD_ARG, "item %d: eps_list[%d] must be > 0", i, k);
+    if (!in.log_a || !in.log_b || !in.f || !in.g) return fail(FS_ERR_BAD_ARG, "item %d: log_a, log_b, f, g must be non-null", i);
+    Item& it = its[i];
+    Ws ws(in.ws, in.ws_bytes);
+    FS_TRY(make_problem(it.p, ws, in.x, in.y, in.n, in.m, d, cost_scale, prec, st, false));
+    carve_solve(ws, it.b, in.n, in.m);
+    if (ws.overflow) return fail(FS_ERR_WORKSPACE, "item %d: workspace too small: need %zu bytes", i, ws.off);
+    it.steps = in.n_eps + 1 + (last_extrapolation ? 1 : 0);
+    if (it.steps > max_steps) max_steps = it.steps;
+    it.self_problem = in.x == in.y && in.n == in.m && in.log_a == in.log_b && rho_x == rho_y;
+    sqnorm_kernel<<<g1(in.n * 32), 256, 0, st>>>(in.x, in.n, d, cost_scale, it.b.alpha);
+    sqnorm_kernel<<<g1(in.m * 32), 256, 0, st>>>(in.y, in.m, d, cost_scale, it.b.beta);
+    axpby_kernel<<<g1(in.n), 256, 0, st>>>(in.n, 0.f, nullptr, -1.f, it.b.alpha, it.b.fh[0]);
+    axpby_kernel<<<g1(in.m), 256, 0, st>>>(in.m, 0.f, nullptr, -1.f, it.b.beta, it.b.gh[0]);
+  }
+  FS_CUDA(cudaGetLastError());
+  std::vector<tc::MultiPass> passes;
+  std::vector<int> owner;
+  const int group = tc::multi_max();
+  for (int t = 0; t < max_steps; ++t) {
+    passes.clear();
+    owner.clear();
+    for (int i = 0; i < n_items; ++i) {
+      Item& it = its[i];
+      if (t >= it.steps) continue;
+      const fs_batch_item& in = items[i];
+      const bool first = t == 0, last = last_extrapolation && t == it.steps - 1;
+      const double eps = first ? in.eps_list_host[0] : (last ? in.eps_list_host[in.n_eps - 1] : in.eps_list_host[t - 1]);
+      const float w = (first || last) ? 1.0f : 0.5f;
+      if (last) {  // the potentials before the final extrapolation are part of the result
+        if (in.f_pre) axpby_kernel<<<g1(in.n), 256, 0, st>>>(in.n, 1.f, it.b.fh[it.cur], 1.f, it.b.alpha, in.f_pre);
+        if (in.g_pre) axpby_kernel<<<g1(in.m), 256, 0, st>>>(in.m, 1.f, it.b.gh[it.cur], 1.f, it.b.beta, in.g_pre);
+      }
+      const float df = (float)dampening(eps, rho_x), dg = (float)dampening(eps, rho_y);
+      for (int side = 0; side < (it.self_problem ? 1 : 2); ++side) {
+        tc::MultiPass mp;
+        mp.s = &it.p.staged;
+        mp.side = side;
+        mp.a = it.p.stream_args(side, side == 0 ? it.b.gh[it.cur] : it.b.fh[it.cur], side == 0 ? in.log_b : in.log_a,
+                                (float)eps);
+        LseEpilogue ep;
+        const float damp = side == 0 ? df : dg;
+        ep.damping = damp; ep.w = w;
+        ep.old = side == 0 ? it.b.fh[it.cur] : it.b.gh[it.cur];
+        ep.out = side == 0 ? it.b.fh[it.cur ^ 1] : it.b.gh[it.cur ^ 1];
+        if (damp < 1.f) { ep.shift = side == 0 ? it.b.alpha : it.b.beta; ep.shiftcoef = w * (1.f - damp); }
+        mp.e = ep;
+        passes.push_back(mp);
+        owner.push_back(i);
+      }
+    }
+    const int n_pass = (int)passes.size();
+    for (int k0 = 0; k0 < n_pass; k0 += group) {
+      const int cnt = n_pass - k0 < group ? n_pass - k0 : group;
+      bool all_tc = true;
+      for (int k = k0; k < k0 + cnt; ++k) all_tc = all_tc && its[owner[k]].p.use_tc;
+      cudaError_t e = all_tc ? tc::lse_multi(passes.data() + k0, cnt, st) : cudaErrorNotSupported;
+      if (e == cudaSuccess) {
+        g_launches.fetch_add(2, std::memory_order_relaxed);
+        continue;
+      }
+      if (e != cudaErrorNotSupported) return fail(FS_ERR_CUDA, "multi-pass launch failed: %s", cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      for (int k = k0; k < k0 + cnt; ++k) {
+        const tc::MultiPass& mp = passes[k];
+        const Problem& pr = its[owner[k]].p;
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        FS_CUDA(pr.use_tc ? tc::lse(*mp.s, mp.side, mp.a, mp.e, st) : simt_lse(mp.a, mp.e, st));
+      }
+    }
+    for (int i = 0; i < n_items; ++i) {
+      Item& it = its[i];
+      if (t >= it.steps) continue;
+      if (it.self_problem)  // g equals f bit for bit: one soft-min per step, copied
+        FS_CUDA(cudaMemcpyAsync(it.b.gh[it.cur ^ 1], it.b.fh[it.cur ^ 1], sizeof(float) * (size_t)items[i].n,
+                                cudaMemcpyDeviceToDevice, st));
+      it.cur ^= 1;
+    }
+  }
+  for (int i = 0; i < n_items; ++i) {
+    const fs_batch_item& in = items[i];
+    Item& it = its[i];
+    axpby_kernel<<<g1(in.n), 256, 0, st>>>(in.n, 1.f, it.b.fh[it.cur], 1.f, it.b.alpha, in.f);
+    axpby_kernel<<<g1(in.m), 256, 0, st>>>(in.m, 1.f, it.b.gh[it.cur], 1.f, it.b.beta, in.g);
+    if (!last_extrapolation) {
+      if (in.f_pre) axpby_kernel<<<g1(in.n), 256, 0, st>>>(in.n, 1.f, it.b.fh[it.cur], 1.f, it.b.alpha, in.f_pre);
+      if (in.g_pre) axpby_kernel<<<g1(in.m), 256, 0, st>>>(in.m, 1.f, it.b.gh[it.cur], 1.f, it.b.beta, in.g_pre);
+    }
+  }
+  FS_CUDA(cudaGetLastError());
   return FS_OK;
 }
 

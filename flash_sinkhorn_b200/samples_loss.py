@@ -20,6 +20,7 @@ import torch
 from flash_sinkhorn_b200._autograd import _SinkhornConfig, _SinkhornCostFn
 from flash_sinkhorn_b200.kernels._common import epsilon_schedule, max_diameter
 from flash_sinkhorn_b200.sinkhorn_solvers import (
+    sinkhorn_flashstyle_symmetric_batched,
     sinkhorn_flashstyle_alternating,
     sinkhorn_flashstyle_symmetric,
     sinkhorn_flashstyle_symmetric_many,
@@ -324,6 +325,39 @@ class SamplesLoss(torch.nn.Module):
                 pre = [(f, g, f, g) if fp is None else (f, g, fp, gp) for (f, g, fp, gp, _) in sols]
             cross, self_x, self_y = (ot(*t, presolved=p) for t, p in zip(terms, pre))
             return cross - 0.5 * self_x - 0.5 * self_y
+
+        # Batched inputs: the reference loops over the items (samples_loss.py:515-552). Here all symmetric solves of
+        # the batch - three per item for the debiased loss - go to the library in ONE call and advance in lockstep,
+        # several soft-min passes per launch; the cost / gradient nodes then receive the finished potentials. Early
+        # stopping, the label cost, the alternating backend and sharded runs keep the per-item loop.
+        labels_on = (self.label_cost_matrix is not None and label_x is not None and label_y is not None
+                     and self.lambda_y != 0.0)
+        if (parsed.batched and self.backend != "alternating" and self.threshold is None and not labels_on
+                and not multi_gpu):
+            items = list(zip(parsed.x, parsed.y, parsed.a, parsed.b))
+            groups = []
+            for xs, ys, wa, wb in items:
+                if self.debias and not self.potentials:
+                    groups.append([(xs, ys, wa, wb), (xs, xs, wa, wa), (ys, ys, wb, wb)])
+                else:
+                    groups.append([(xs, ys, wa, wb)])
+            # detached views keep their storage, which is how the solver recognises a self-transport problem
+            flat = [tuple(t.detach() for t in prob) for grp in groups for prob in grp]
+            with torch.no_grad():
+                sols = sinkhorn_flashstyle_symmetric_batched(
+                    flat, blur=self.blur, scaling=self.scaling, use_epsilon_scaling=self.use_epsilon_scaling,
+                    eps=self.eps, n_iters=self.n_iters, allow_tf32=self.allow_tf32, cost_scale=self.cost_scale,
+                    rho_x=self.rho_x, rho_y=self.rho_y, last_extrapolation=self.last_extrapolation)
+            if self.potentials:
+                f = torch.stack([sol[0] for sol in sols], dim=0).view(parsed.a_view_shape)
+                g = torch.stack([sol[1] for sol in sols], dim=0).view(parsed.b_view_shape)
+                return f, g
+            vals, k = [], 0
+            for grp in groups:
+                terms = [ot(*prob, label_x, label_y, presolved=sols[k + j][:4]) for j, prob in enumerate(grp)]
+                k += len(grp)
+                vals.append(terms[0] - 0.5 * terms[1] - 0.5 * terms[2] if len(terms) == 3 else terms[0])
+            return torch.stack(vals, dim=0)
 
         if parsed.batched:
             items = zip(parsed.x, parsed.y, parsed.a, parsed.b)

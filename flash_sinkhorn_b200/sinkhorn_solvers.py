@@ -23,7 +23,8 @@ from flash_sinkhorn_b200.kernels._common import (
     resolve_marginal_penalties,
 )
 
-__all__ = ["sinkhorn_flashstyle_alternating", "sinkhorn_flashstyle_symmetric", "tile_mask_to_csr"]
+__all__ = ["sinkhorn_flashstyle_alternating", "sinkhorn_flashstyle_symmetric", "sinkhorn_flashstyle_symmetric_batched",
+           "tile_mask_to_csr"]
 
 
 def _same_tensor(u: Optional[torch.Tensor], v: Optional[torch.Tensor]) -> bool:
@@ -309,6 +310,86 @@ def sinkhorn_flashstyle_symmetric(
         out = out + (int(iters.item()),)
         _lib.raise_if_device_timeout(dev)  # the host has synchronised anyway: surface a device-side time-out
     return out
+
+
+def sinkhorn_flashstyle_symmetric_batched(
+    problems,
+    *,
+    blur: float = 0.05,
+    scaling: float = 0.5,
+    use_epsilon_scaling: bool = True,
+    last_extrapolation: bool = True,
+    cost_scale: float = 1.0,
+    eps: Optional[float] = None,
+    n_iters: Optional[int] = None,
+    rho: Optional[float] = None,
+    reach: Optional[float] = None,
+    rho_x: Optional[float] = None,
+    rho_y: Optional[float] = None,
+    reach_x: Optional[float] = None,
+    reach_y: Optional[float] = None,
+    allow_tf32: bool = True,
+):
+    """Several independent symmetric solves in ONE library call (``fs_solve_symmetric_batched``).
+
+    Extension without a reference counterpart (the reference loops over batch items in Python,
+    samples_loss.py:515-552). ``problems`` is a sequence of ``(x, y, a, b)`` with one feature dimension; every
+    problem gets the schedule :func:`sinkhorn_flashstyle_symmetric` would give it (its own diameter with
+    ``use_epsilon_scaling``), and all of them advance in lockstep, up to four soft-min passes per kernel launch.
+    No early stopping, warm start or label cost. Returns one ``(f, g, f_prelast, g_prelast, n_steps)`` per problem
+    (the pre-extrapolation pair equals ``(f, g)`` without ``last_extrapolation``); results equal the one-at-a-time
+    solves up to the merge order of partial sums (rounding level). A problem given as ``(x, x, a, a)`` - the same
+    tensors twice - is solved as a self-transport problem with one soft-min per step.
+    """
+    rho_x, rho_y = resolve_marginal_penalties(rho, reach, rho_x, rho_y, reach_x, reach_y)
+    problems = list(problems)
+    if not problems:
+        return []
+    d = problems[0][0].shape[1]
+    prec = _lib.precision_id(allow_tf32)
+    arr = (_lib.BatchItem * len(problems))()
+    keep, outs = [], []
+    dev = None
+    for slot, (x, y, a, b) in zip(arr, problems):
+        if x.shape[1] != d or y.shape[1] != d:
+            raise ValueError("all problems of a batched solve must share the feature dimension")
+        pdev = _lib.require_cuda(x=x, y=y, a=a, b=b)
+        if dev is None:
+            dev = pdev
+        elif pdev != dev:
+            raise ValueError("all problems of a batched solve must be on the same device")
+        n, m = x.shape[0], y.shape[0]
+        if use_epsilon_scaling:
+            sched = epsilon_schedule(max_diameter(x, y), blur, scaling, p=2.0)
+        else:
+            if eps is None or n_iters is None:
+                raise ValueError("When use_epsilon_scaling=False, provide eps and n_iters")
+            sched = [float(eps)] * int(n_iters)
+        if n_iters is not None:
+            sched = list(sched)[: int(n_iters)]
+        if len(sched) == 0:
+            raise ValueError("eps_list must be non-empty")
+        x32 = _lib.f32c(x)
+        y32 = x32 if _same_tensor(y, x) else _lib.f32c(y)
+        la = log_weights(a).contiguous()
+        lb = la if _same_tensor(b, a) else log_weights(b).contiguous()
+        f = torch.empty((n,), device=dev, dtype=torch.float32)
+        g = torch.empty((m,), device=dev, dtype=torch.float32)
+        fp = torch.empty((n,), device=dev, dtype=torch.float32)
+        gp = torch.empty((m,), device=dev, dtype=torch.float32)
+        ws = _lib.workspace(_lib.OP_SOLVE_SYMMETRIC, n, m, d, prec, dev)
+        eps_arr = _eps_array(sched)
+        keep += [x32, y32, la, lb, ws, eps_arr]
+        slot.x, slot.y, slot.n, slot.m = x32.data_ptr(), y32.data_ptr(), n, m
+        slot.log_a, slot.log_b = la.data_ptr(), lb.data_ptr()
+        slot.eps_list_host, slot.n_eps = ctypes.cast(eps_arr, ctypes.c_void_p), len(sched)
+        slot.f, slot.g, slot.f_pre, slot.g_pre = f.data_ptr(), g.data_ptr(), fp.data_ptr(), gp.data_ptr()
+        slot.ws, slot.ws_bytes = ws.data_ptr(), ws.numel()
+        outs.append((f, g, fp, gp, len(sched) + 1 + (1 if last_extrapolation else 0)))
+    _lib.call("fs_solve_symmetric_batched", dev, ctypes.cast(arr, ctypes.c_void_p), len(problems), d,
+              1 if last_extrapolation else 0, float(cost_scale), _neg_if_none(rho_x), _neg_if_none(rho_y), prec,
+              _lib.stream_ptr(dev))
+    return outs
 
 
 def sinkhorn_flashstyle_symmetric_many(problems, *, process_group, **kwargs):

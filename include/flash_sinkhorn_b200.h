@@ -229,6 +229,24 @@ typedef struct fs_step_item {
 } fs_step_item;
 int fs_symmetric_step_multi(const fs_step_item* items, int n_items, int d, int prec, void* stream);
 
+/* Several symmetric solves at once (replaces the Python loop over batch items of the reference,
+ * samples_loss.py:515-552, and serves the three solves of a debiased loss): same step sequence per item as
+ * fs_solve_symmetric (own eps schedule, lengths may differ), no early stopping, no warm start, no label cost.
+ * Every step of all unfinished items goes out as fused multi-pass launches (up to four soft-min passes per
+ * launch), so B small problems cost about a quarter of B solves' worth of launches. Results equal the
+ * one-at-a-time solves up to the order in which a row's partial sums are merged (rounding level, not bit for
+ * bit). Each item brings its own workspace of fs_workspace_bytes(FS_OP_SOLVE_SYMMETRIC, n, m, d, prec) bytes.
+ * An item with y == x, log_b == log_a (and rho_x == rho_y) is a self-transport problem: one soft-min per step. */
+typedef struct fs_batch_item {
+  const float* x; const float* y; int n, m;
+  const float* log_a; const float* log_b;
+  const double* eps_list_host; int n_eps;
+  float* f; float* g; float* f_pre; float* g_pre;   /* outputs [n], [m]; the *_pre pair may be NULL */
+  void* ws; size_t ws_bytes;
+} fs_batch_item;
+int fs_solve_symmetric_batched(const fs_batch_item* items, int n_items, int d, int last_extrapolation,
+                               float cost_scale, double rho_x, double rho_y, int prec, void* stream);
+
 /* The same with a block-sparse list of kept 128 x 128 tiles (CSR over the 128-row blocks of x, and the
  * transposed list over the blocks of y, as fs_solve_alternating takes them; all four NULL = dense). No
  * reference counterpart. Row ranges must start on multiples of 128; a multi-GPU caller cuts them so that

@@ -369,3 +369,48 @@ def test_resident_and_streamed_kernels_agree_on_shapes_both_can_serve(d, tf32):
     assert _r(out[1][0], out[0][0]) < 2e-6
     assert _r(out[1][1], out[0][1]) < 2e-5
     assert lib.fs_device_error() == 0
+
+
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
+def test_batched_inputs_go_out_as_one_lockstep_solve(monkeypatch, mode):
+    """(B, N, D) inputs: all solves of the batch (three per item with debiasing) run in one library call, several
+    soft-min passes per launch. Loss and gradients equal the per-item loop up to the merge order of partial sums,
+    with fewer launches; `potentials=True` returns the per-item potentials."""
+    from flash_sinkhorn_b200 import SamplesLoss, _lib
+    monkeypatch.setenv("FLASH_SINKHORN_B200_PREC", mode)
+    tf32 = mode == "tf32"
+    g = torch.Generator().manual_seed(17)
+    B, n, m, d = 3, 600, 500, 24
+    x = torch.randn(B, n, d, generator=g).cuda()
+    y = (0.4 + torch.randn(B, m, d, generator=g) * torch.tensor([1.0, 1.5, 0.7]).view(B, 1, 1)).cuda()
+    a = torch.softmax(torch.randn(B, n, generator=g), 1).cuda()
+    b = torch.softmax(torch.randn(B, m, generator=g), 1).cuda()
+    lib = _lib.load()
+    for kw in (dict(blur=0.3, scaling=0.6, debias=True, half_cost=True),
+               dict(blur=0.5, use_epsilon_scaling=False, eps=0.25, n_iters=12, reach=2.0, last_extrapolation=False)):
+        loss = SamplesLoss("sinkhorn", allow_tf32=tf32, **kw)
+        xs = x.clone().requires_grad_(True)
+        c0 = lib.fs_launch_count()
+        vals = loss(a, xs, b, y)
+        batched_launches = lib.fs_launch_count() - c0
+        (gx,) = torch.autograd.grad(vals.sum(), xs)
+        assert vals.shape == (B,)
+        c0 = lib.fs_launch_count()
+        singles = []
+        for i in range(B):
+            xi = x[i].clone().requires_grad_(True)
+            vi = loss(a[i], xi, b[i], y[i])
+            (gi,) = torch.autograd.grad(vi, xi)
+            singles.append((vi, gi))
+        loop_launches = lib.fs_launch_count() - c0
+        tol_l, tol_g = (1e-4, 3e-2) if tf32 else (1e-5, 2e-4)
+        for i, (vi, gi) in enumerate(singles):
+            assert abs(float(vals[i]) - float(vi)) <= tol_l * abs(float(vi)), (kw, i)
+            assert _r(gx[i], gi) < tol_g, (kw, i)
+        assert batched_launches < loop_launches
+    pot = SamplesLoss("sinkhorn", blur=0.3, scaling=0.6, potentials=True, allow_tf32=tf32)
+    f, gpot = pot(a, x, b, y)
+    assert f.shape == (B, n) and gpot.shape == (B, m)
+    f0, g0 = pot(a[1], x[1], b[1], y[1])
+    assert _r(f[1], f0) < (2e-3 if tf32 else 1e-5) and _r(gpot[1], g0) < (2e-3 if tf32 else 1e-5)
+    assert lib.fs_device_error() == 0
