@@ -367,7 +367,9 @@ def test_resident_and_streamed_kernels_agree_on_shapes_both_can_serve(d, tf32):
     finally:
         lib.fs_set_prefer_streamed(previous)
     assert _r(out[1][0], out[0][0]) < 2e-6
-    assert _r(out[1][1], out[0][1]) < 2e-5
+    # plan-times-vector: the resident kernel rounds weights and vector to TF32 for its second GEMM in TF32 mode,
+    # the K-streamed one multiplies them in fp32
+    assert _r(out[1][1], out[0][1]) < (2e-3 if tf32 else 2e-5)
     assert lib.fs_device_error() == 0
 
 
