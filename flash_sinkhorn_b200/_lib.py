@@ -55,6 +55,7 @@ SIGNATURES = {
     "fs_set_cta_limit": (c_int, [c_int]),
     "fs_set_wide_tile_min_chunks": (c_int, [c_int]),
     "fs_set_prefer_streamed": (c_int, [c_int]),
+    "fs_set_pv_split": (c_int, [c_int]),
     "fs_engine": (c_int, [c_int, c_int, c_int, c_int]),
     "fs_plan_ctas": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "fs_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),

@@ -409,6 +409,8 @@ int fs_set_wide_tile_min_chunks(int k) { return tc::set_wide_tile_min_chunks(k);
 
 int fs_set_prefer_streamed(int on) { return tc::set_prefer_streamed(on); }
 
+int fs_set_pv_split(int split) { return tc::set_pv_split(split); }
+
 int fs_engine(int n, int m, int d, int prec) {
   if (prec == FS_PREC_SIMT || !tc::supported(n, m, d, prec, 0)) return 0;
   return tc::k_streamed(d, prec, 0) ? 2 : 1;

@@ -600,6 +600,12 @@ struct PvKernelParams {
   const float* rows_raw; int ld_rows;   // original row cloud (GRAD epilogue: x_i - O_i)
   float* out;
   const int* skip;       // device flag: non-zero => whole launch is a no-op
+  // Column split: CTA b serves row block b / nsplit and the column tiles of share b % nsplit; with nsplit > 1
+  // every CTA parks its raw O tile in `partial` ([row block][share][128][dv_pad]) and the one that takes
+  // the last ticket of the row block adds the shares in share order and applies the epilogue.
+  int nsplit;
+  float* partial;
+  int* tickets;
 };
 
 
@@ -613,10 +619,13 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
              const PvKernelParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = p.row_begin + blockIdx.x * 128;
+  const int blk = (int)blockIdx.x / p.nsplit, share = (int)blockIdx.x % p.nsplit;
+  const int row0 = p.row_begin + blk * 128;
   if (p.skip && *p.skip) return;  // uniform across the grid (set by an earlier kernel of the stream)
   constexpr int WCOLS = SPLIT ? 2 * BN : BN;  // TMEM columns per S/W buffer (Wl lives right after Wh)
   constexpr int NV = SPLIT ? 2 : 1;
+  const int j0 = (int)((long long)share * p.ntiles / p.nsplit);
+  const int ntl = (int)((long long)(share + 1) * p.ntiles / p.nsplit) - j0;  // column tiles of this CTA
 
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t a_bytes = p.nfull * (128 * 128) + p.ntail * (128 * 32);
@@ -636,6 +645,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
             DRAIN = O_FULL + 1, NBARS = DRAIN + 1;
   uint32_t* tmem_slot = (uint32_t*)(bars + NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* last_flag = (volatile int*)(tmem_slot + 2);
   auto bar = [&](int i) { return smem_u32(bars + i); };
   constexpr uint32_t kTmemCols = 512;
 
@@ -679,16 +689,16 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
         tma_load_2d(dst + p.nfull * (128 * 128) + t * (128 * 32), &mapA_tail, p.nfull * 32 + t * 8, row0, bar(A_FULL));
       int issued = 0;
 #pragma unroll 1
-      for (int j = 0; j < p.ntiles; ++j) {
+      for (int j = 0; j < ntl; ++j) {
         const int s = j % p.nb;
         const uint32_t ph = (j / p.nb) & 1;
         if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
         mbar_expect_tx(bar(B_FULL + s), b_bytes);
         uint32_t d0 = smem_u32(b_smem + s * b_bytes);
         for (int kb = 0; kb < p.nfull; ++kb)
-          tma_load_2d(d0 + kb * (BN * 128), &mapB_full, kb * 32, j * BN, bar(B_FULL + s));
+          tma_load_2d(d0 + kb * (BN * 128), &mapB_full, kb * 32, (j0 + j) * BN, bar(B_FULL + s));
         for (int t = 0; t < p.ntail; ++t)
-          tma_load_2d(d0 + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, j * BN,
+          tma_load_2d(d0 + p.nfull * (BN * 128) + t * (BN * 32), &mapB_tail, p.nfull * 32 + t * 8, (j0 + j) * BN,
                       bar(B_FULL + s));
         issued = j + 1;
       }
@@ -702,15 +712,16 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
     if (lane == 0) {  // V^T tiles (hi and, in split mode, lo) on their own ring
       int issued = 0;
 #pragma unroll 1
-      for (int j = 0; j < p.ntiles; ++j) {
+      for (int j = 0; j < ntl; ++j) {
         const int s = j % p.nv;
         const uint32_t ph = (j / p.nv) & 1;
         if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1, abort_flag, 2000)) break;
         mbar_expect_tx(bar(V_FULL + s), v_stage);
         uint32_t dv_dst = smem_u32(v_smem + s * v_stage);
         for (int kb = 0; kb < BN / 32; ++kb) {
-          tma_load_2d(dv_dst + kb * v_blk, &mapV_hi, j * BN + kb * 32, p.dv0, bar(V_FULL + s));
-          if (SPLIT) tma_load_2d(dv_dst + v_bytes + kb * v_blk, &mapV_lo, j * BN + kb * 32, p.dv0, bar(V_FULL + s));
+          tma_load_2d(dv_dst + kb * v_blk, &mapV_hi, (j0 + j) * BN + kb * 32, p.dv0, bar(V_FULL + s));
+          if (SPLIT)
+            tma_load_2d(dv_dst + v_bytes + kb * v_blk, &mapV_lo, (j0 + j) * BN + kb * 32, p.dv0, bar(V_FULL + s));
         }
         issued = j + 1;
       }
@@ -729,7 +740,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       tc_fence_after();
       const uint32_t a_lo0 = desc_lo(smem_u32(a_smem));
 #pragma unroll 1
-      for (int j = 0; ok && j < p.ntiles; ++j) {
+      for (int j = 0; ok && j < ntl; ++j) {
         const int s = j % p.nb, buf = j % kNSW;
         if (!mbar_wait(bar(W_FREE + buf), ((j / kNSW) & 1) ^ 1, abort_flag, 2000)) break;
         if (!mbar_wait(bar(B_FULL + s), (j / p.nb) & 1, abort_flag, 2000)) break;
@@ -770,7 +781,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       uint32_t o_acc = 0;
       bool ok = true;
 #pragma unroll 1
-      for (int j = 0; j < p.ntiles; ++j) {
+      for (int j = 0; j < ntl; ++j) {
         const int sv = j % p.nv, buf = j % kNSW;
         if (!mbar_wait(bar(V_FULL + sv), (j / p.nv) & 1, abort_flag, 2000)) { ok = false; break; }
         if (!mbar_wait(bar(W_FULL + buf), (j / kNSW) & 1, abort_flag, 2000)) { ok = false; break; }
@@ -805,12 +816,13 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
     const int part = (warp - 4) >> 2;
     const int q = warp & 3;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int r = row0 + q * 32 + lane;
+    const int r_in = q * 32 + lane;  // row within the block
+    const int r = row0 + r_in;
     const float scale = p.scale2;
     const float negR = (r < p.nr) ? -p.R[r] : 0.f;
     bool ok = true;
     constexpr int CH = BN / 32 / kParts;
-    const int total = p.ntiles * CH;
+    const int total = ntl * CH;
     const int c_base = part * CH;
     auto issue = [&](int g, uint32_t (&rg)[32]) -> bool {
       const int j = g / CH, c = g % CH, buf = j % kNSW;
@@ -862,7 +874,7 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       return true;
     };
     uint32_t ra[32], rb[32];
-    ok = issue(0, ra);
+    ok = total > 0 && issue(0, ra);
 #pragma unroll 1
     for (int g = 0; ok && g < total; g += 2) {
       ok = pipe(g, ra, rb);
@@ -874,33 +886,77 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
     tc_fence_after();
     // `ok` is warp-uniform (every lane polls the same barrier). tcgen05.ld is .sync.aligned: all 32
     // lanes must execute it together, so rows beyond nr load too and only their stores are masked.
-    if (ok) {
-      const bool valid = r < p.nr;
-      const int rr = valid ? r : 0;
-      const float inv_eps = 1.0f / p.eps;
-      float fac;
-      if (p.epilogue == PV_GRAD) {
-        fac = p.coef * (p.gs ? __ldg(p.gs) : 1.f) * __ldg(p.roww + rr);
-      } else {
-        float rt = (__ldg(p.rowpot + rr) * inv_eps + (p.rowlogw ? __ldg(p.rowlogw + rr) : 0.f)) * kLog2e;
-        fac = p.coef * ex2(rt - negR);
-      }
+    const float inv_eps = 1.0f / p.eps;
+    // Epilogue of one output row: o = sum_j w_ij V_j over ALL columns.
+    auto finish_row = [&](int rr, int c, const float (&o)[32], float fac) {
       float* orow = p.out + (size_t)rr * p.ld_out + p.dv0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        int col = c * 32 + i;
+        if (p.dv0 + col < p.dv) {
+          float val = o[i];
+          if (p.epilogue == PV_GRAD) val = __ldg(p.rows_raw + (size_t)rr * p.ld_rows + p.dv0 + col) - val;
+          orow[col] = fac * val;
+        }
+      }
+    };
+    auto row_factor = [&](int rr) {
+      if (p.epilogue == PV_GRAD) return p.coef * (p.gs ? __ldg(p.gs) : 1.f) * __ldg(p.roww + rr);
+      // Rounding written out (the compiler's choice of fused multiply-adds here moved a CG-bound result by 1e-3).
+      const float pot = __ldg(p.rowpot + rr), lw = (p.rowlogw ? __ldg(p.rowlogw + rr) : 0.f);
+      const float t = __fadd_rn(__fmul_rn(pot, inv_eps), lw);
+      return __fmul_rn(p.coef, ex2(__fmaf_rn(t, kLog2e, -negR)));
+    };
+    const size_t tile_elems = (size_t)128 * p.dv_pad;
+    const bool valid = r < p.nr;
+    const int rr = valid ? r : 0;
+    if (ok) {
+      const float fac = (p.nsplit == 1) ? row_factor(rr) : 0.f;
+      float* my_partial = p.nsplit > 1 ? p.partial + ((size_t)blk * p.nsplit + share) * tile_elems : nullptr;
 #pragma unroll 1
       for (int c = part; c < p.dv_pad / 32; c += kParts) {  // the warpgroups split the output chunks
         float o[32];
         tmem_ld32(lane_addr + kNSW * WCOLS + c * 32, o);
-        if (valid) {
+        if (p.nsplit == 1) {
+          if (valid) finish_row(rr, c, o, fac);
+        } else {  // raw share of the row, merged below
+          float4* dst = reinterpret_cast<float4*>(my_partial + (size_t)r_in * p.dv_pad + c * 32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            int col = c * 32 + i;
-            if (p.dv0 + col < p.dv) {
-              float val = o[i];
-              if (p.epilogue == PV_GRAD) val = __ldg(p.rows_raw + (size_t)rr * p.ld_rows + p.dv0 + col) - val;
-              orow[col] = fac * val;
+          for (int i = 0; i < 8; ++i) dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+      }
+    }
+    if (p.nsplit > 1) {
+      // Every soft-max warp runs this barrier sequence, also after an abort; what happens between the barriers
+      // is decided by one thread and read back from shared memory, so it is the same for all of them.
+      __threadfence();  // the shares must be visible device-wide before the ticket is taken
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * kParts) : "memory");
+      if (warp == 4 && lane == 0)
+        *last_flag = (!*abort_flag && atomicAdd(p.tickets + blk, 1) == p.nsplit - 1) ? 1 : 0;
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * kParts) : "memory");
+      if (*last_flag) {
+        __threadfence();
+        if (valid) {
+          const float* blk_partial = p.partial + (size_t)blk * p.nsplit * tile_elems;
+          const float fac = row_factor(r);
+#pragma unroll 1
+          for (int c = part; c < p.dv_pad / 32; c += kParts) {
+            float o[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0.f;
+            for (int sh = 0; sh < p.nsplit; ++sh) {  // fixed order: the sum does not depend on who merges
+              const float4* src =
+                  reinterpret_cast<const float4*>(blk_partial + (size_t)sh * tile_elems + (size_t)r_in * p.dv_pad + c * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 t = __ldcg(src + i);
+                o[4 * i] += t.x; o[4 * i + 1] += t.y; o[4 * i + 2] += t.z; o[4 * i + 3] += t.w;
+              }
             }
+            finish_row(r, c, o, fac);
           }
         }
+        if (warp == 4 && lane == 0) p.tickets[blk] = 0;  // ready for the next launch on this stream
       }
     }
   }
@@ -1112,6 +1168,7 @@ constexpr int kMaxChunks = 16;
 std::atomic<int> g_reserved_sms{0};
 std::atomic<int> g_cta_limit{0};
 std::atomic<int> g_prefer_streamed{1};
+std::atomic<int> g_pv_split{0};  // column shares per row block of the matrix pass. 0: chosen by SM fill, 1..8: forced
 
 }  // namespace
 
@@ -1205,6 +1262,10 @@ int set_cta_limit(int k) {
 }
 
 int set_prefer_streamed(int on) { return g_prefer_streamed.exchange(on ? 1 : 0, std::memory_order_relaxed); }
+
+int set_pv_split(int split) {
+  return g_pv_split.exchange(split >= 1 && split <= 8 ? split : 0, std::memory_order_relaxed);
+}
 
 int plan_ctas(int nblk, int ntiles, int sms, int reserved, int limit) {
   if (nblk <= 0 || ntiles <= 0 || sms <= 0) return 0;
@@ -1440,6 +1501,35 @@ struct PvShape {
   bool split, ok;
 };
 
+// Share slots (one raw O tile of a row block each) that the scratch of a matrix pass holds for the column
+// split: a function of the larger cloud only, so that sizing and launching agree. No split below 16 column
+// tiles; otherwise up to 8 shares per row block, capped at eight 128-row tiles per SM of a 148-SM device.
+int pv_share_slots(int nm, int bn) {
+  const int ntiles = (nm + bn - 1) / bn;
+  const int smax = ntiles / 8 < 8 ? ntiles / 8 : 8;
+  if (smax < 2) return 0;
+  const long long nblk = (nm + 127) / 128;
+  const long long cap = nblk > 1184 ? nblk : 1184;
+  const long long want = nblk * smax;
+  return (int)(want < cap ? want : cap);
+}
+
+// Shares per row block: the smallest count within 2 % of the best SM fill (CTAs / (waves * SMs)).
+int pick_pv_split(int nblk, int ntiles, int slots, int sms) {
+  if (sms < 1) sms = 1;
+  auto fill = [&](int s) {
+    const long long ctas = (long long)nblk * s;
+    return (double)ctas / (double)(((ctas + sms - 1) / sms) * sms);
+  };
+  int best = 1;
+  double best_fill = fill(1);
+  for (int s = 2; s <= 8 && s <= ntiles / 8 && (long long)nblk * s <= slots; ++s)
+    if (fill(s) > best_fill + 0.02) { best = s; best_fill = fill(s); }
+  const int forced = g_pv_split.load(std::memory_order_relaxed);
+  if (forced >= 1 && forced <= 8 && forced <= ntiles && (forced == 1 || (long long)nblk * forced <= slots)) return forced;
+  return best;
+}
+
 PvShape plan_pv(int d, int prec, int dv, int nlab = 0) {
   PvShape s{};
   Shape sh = plan_shape(d, prec, nlab);
@@ -1493,7 +1583,8 @@ size_t pv_scratch_bytes(int nc, int d, int prec, int dv, int nlab) {
   PvShape s = plan_pv(d, prec, dv, nlab);
   if (!s.ok) return 0;
   size_t one = (size_t)s.nslices * s.dv_pad * pad256(nc) * sizeof(float);
-  return (s.split ? 2 : 1) * ((one + 1023) & ~size_t(1023)) + 1024;
+  return (s.split ? 2 : 1) * ((one + 1023) & ~size_t(1023)) + 1024 +
+         (size_t)pv_share_slots(nc, s.bn) * 128 * s.dv_pad * sizeof(float);
 }
 
 cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa, char* scratch, cudaStream_t st) {
@@ -1542,8 +1633,15 @@ cudaError_t pv(const Staged& s, int side, const StreamArgs& a, const PvArgs& pa,
   kp.scale2 = scale2; kp.eps = a.eps; kp.R = pa.R; kp.epilogue = pa.epilogue;
   kp.rowpot = pa.rowpot; kp.rowlogw = pa.rowlogw; kp.roww = pa.roww; kp.gs = pa.gs; kp.coef = pa.coef;
   kp.rows_raw = a.rows; kp.ld_rows = a.d; kp.out = pa.out; kp.skip = pa.skip;
-  const int grid = (a.nr - a.row_begin + 127) / 128;
-  if (grid <= 0) return cudaSuccess;
+  const int nblk = (a.nr - a.row_begin + 127) / 128;
+  if (nblk <= 0) return cudaSuccess;
+  // Column shares per row block: as many as fill the SMs best, within the share slots the scratch was sized for.
+  const int nm = a.nr > a.nc ? a.nr : a.nc;
+  kp.nsplit = pick_pv_split(nblk, kp.ntiles, pv_share_slots(nm, ps.bn),
+                            detail::sm_count() - g_reserved_sms.load(std::memory_order_relaxed));
+  kp.partial = reinterpret_cast<float*>(p + (ps.split ? 2 : 1) * one);
+  kp.tickets = s.tickets[side];
+  const int grid = nblk * kp.nsplit;
   for (int sl = 0; sl < ps.nslices; ++sl) {
     kp.dv0 = sl * ps.dv_pad;
     cudaError_t e = ps.split ? launch_pv<64, true>(maps, kp, grid, ps.smem, st)

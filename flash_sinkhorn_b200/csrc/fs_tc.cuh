@@ -36,6 +36,9 @@ int set_reserved_sms(int k);
 // Shapes whose resident-operand plan only fits 64-column score tiles run their soft-min and plan-times-vector
 // passes on the K-streamed kernels (on = 1, the default) or on the resident ones (0). Returns the previous value.
 int set_prefer_streamed(int on);
+// Column shares per row block of the plan-times-matrix kernel with the row operand resident: 0 = as many as fill
+// the SMs best (the default), 1..8 = forced where the scratch has room. Test knob; returns the previous value.
+int set_pv_split(int split);
 // Streaming passes use at most `k` CTAs from now on (0 = no limit; returns the previous value). Test knob.
 int set_cta_limit(int k);
 // CTA count a streaming pass over nblk row blocks x ntiles column tiles would get on a device with `sms`

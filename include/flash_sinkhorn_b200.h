@@ -122,6 +122,13 @@ int fs_set_wide_tile_min_chunks(int k);
  * (on = 0). Returns the previous value. */
 int fs_set_prefer_streamed(int on);
 
+/* Test knob (no reference counterpart): the plan-times-matrix kernel with the row operand resident in shared
+ * memory cuts the column range of a 128-row block into shares, one CTA each; every CTA parks its raw output
+ * tile in the scratch and the last to finish adds the shares in share order (run-to-run identical bits).
+ * split = 0: as many shares as fill the SMs best (the default); 1..8: that many where the scratch has room.
+ * Process-wide; returns the previous value. */
+int fs_set_pv_split(int split);
+
 /* Which engine serves a problem of these sizes (no reference counterpart): 0 = CUDA-core fp32 FMA, 1 = tcgen05
  * with the row operand resident in shared memory, 2 = tcgen05 with both operands streamed in K chunks. */
 int fs_engine(int n, int m, int d, int prec);

@@ -245,3 +245,41 @@ def test_c_transform_shapes_and_ties(monkeypatch, mode, n, m, d):
     else:
         picked = ((x.double() - y[idx].double()) ** 2).sum(1) - psi[idx].double()
         assert (picked - c.double()).abs().max() < (5e-2 if mode == "tf32" else 2e-4)
+
+
+@pytest.mark.parametrize("tf32", [True, False])
+@pytest.mark.parametrize("n,m,d,vec", [(2100, 4200, 16, False), (4200, 2100, 40, False), (2305, 5000, 8, True),
+                                       (300, 9000, 24, False), (1300, 4100, 100, False)])
+@pytest.mark.parametrize("split", [0, 1, 2, 3, 4])
+def test_plan_times_matrix_work_split(n, m, d, vec, split, tf32):
+    """The plan-times-matrix kernel with the row operand resident cuts the column range of a row block into
+    shares, one CTA each, that the last CTA to finish adds in share order: every share count (forced through
+    the test knob) must give the dense fp64 answer, ragged last row block included, and identical bits from
+    run to run."""
+    from flash_sinkhorn_b200 import _lib
+    from flash_sinkhorn_b200.kernels.apply_flash import apply_plan_mat_flashstyle, apply_plan_vec_flashstyle
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(n + 7 * m + d)
+    eps, cs = 0.3, 0.5
+    x = (torch.randn(n, d, generator=g) / d ** 0.5).cuda()
+    y = (0.2 + torch.randn(m, d, generator=g) / d ** 0.5).cuda()
+    fh = -cs * (x ** 2).sum(1) + 0.05 * torch.randn(n, generator=g).cuda()
+    gh = -cs * (y ** 2).sum(1) + 0.05 * torch.randn(m, generator=g).cuda()
+    la = torch.log_softmax(torch.randn(n, generator=g), 0).cuda()
+    lb = torch.log_softmax(torch.randn(m, generator=g), 0).cuda()
+    xd, yd = x.double(), y.double()
+    logit = (fh.double()[:, None] + gh.double()[None] + 2 * cs * xd @ yd.T) / eps + la.double()[:, None] + lb.double()[None]
+    P = torch.exp(logit)
+    v = torch.randn(m, generator=g).cuda() if vec else torch.randn(m, d, generator=g).cuda()
+    apply = apply_plan_vec_flashstyle if vec else apply_plan_mat_flashstyle
+    previous = lib.fs_set_pv_split(split)
+    try:
+        got = apply(x, y, fh, gh, la, lb, v, eps=eps, axis=1, cost_scale=cs, allow_tf32=tf32)
+        again = apply(x, y, fh, gh, la, lb, v, eps=eps, axis=1, cost_scale=cs, allow_tf32=tf32)
+    finally:
+        lib.fs_set_pv_split(previous)
+    want = P @ v.double()
+    err = float((got.double() - want).abs().max() / want.abs().max())
+    assert err < (2e-2 if tf32 else 2e-4), err
+    assert torch.equal(got, again)
+    assert lib.fs_device_error() == 0

@@ -154,7 +154,7 @@ def test_hvp(name, rx, ry, cs):
 
 def test_config1_golden_is_recorded():
     z = load_golden("config1")
-    # Values measured independently during the survey of the reference (fp32 dense path).
+    # Values measured independently on the fp32 dense path of the reference.
     assert float(z["loss"]) == pytest.approx(36.8802109, rel=2e-6)
     assert float(z["grad_x_norm"]) == pytest.approx(0.128287598, rel=2e-4)
 
