@@ -267,35 +267,39 @@ tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
       }
     }
   } else if (warp == 1 || (warp == 3 && NHALF == 2)) {
-    // ===================== MMA issuers: one lane per 128-row half =====================
-    // A lane that shares its scheduler with soft-max warps sustains one MMA per ~90 cycles, the tensor pipe
-    // one per 64: with one lane per half (warps 1 and 3) the score tiles of the next column tile are ready
-    // well before the soft-max warps ask for them, instead of just in time.
-    if (lane == 0) {
+    // ===================== MMA issuers: one warp per 128-row half =====================
+    // A stream that shares its scheduler with soft-max warps sustains one MMA per ~90 cycles, the tensor pipe
+    // one per 64: with one issuer per half (warps 1 and 3) the score tiles of the next column tile are ready
+    // well before the soft-max warps ask for them, instead of just in time. All 32 lanes run the loop and one
+    // elected lane issues: descriptor arithmetic is then warp-uniform (uniform registers, which is where
+    // tcgen05 instructions take their operands) instead of per-thread values moved over for every MMA. Every
+    // exit decision is a warp vote, since elect.sync needs all 32 lanes at the same instruction.
+    {
       const int h = (warp == 1) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc(BN);
       const uint32_t a_lo0 = desc_lo(smem_u32(a_smem + h * a_half_bytes));
       bool ok = true;
       int jt = 0, seg = 0;  // column tiles processed so far by this CTA (ring / buffer position), segment count
-#pragma unroll 1
       int blk = has_work ? blk_of(w_begin) : 0;
 #pragma unroll 1
       for (int w = w_begin; ok && w < w_end; ++seg) {
         const int nseg = (row_end(blk) < w_end ? row_end(blk) : w_end) - w;
-        if (!mbar_wait(bar(A_FULL), seg & 1, abort_flag, 2000)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(A_FULL), seg & 1, abort_flag, 2000))) break;
         tc_fence_after();
 #pragma unroll 1
         for (int i = 0; i < nseg; ++i, ++jt) {
           const int s = jt % P.nstage;
           const uint32_t ph = (jt / P.nstage) & 1;
-          if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000))) { ok = false; break; }
           const int buf = jt & 1;
           const uint32_t sph = (jt >> 1) & 1;
-          if (!mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000))) {
+            ok = false;
+            break;
+          }
           tc_fence_after();
-          // The issuing thread is a single lane: every integer instruction it spends per MMA is exposed
-          // latency (~5 cycles each). Descriptors are therefore advanced incrementally: the low word holds
-          // (address >> 4), the high word (stride, version, swizzle) is a constant per block class.
+          // Descriptors are advanced incrementally: the low word holds (address >> 4), the high word (stride,
+          // version, swizzle) is a constant per block class.
           const uint32_t d_tmem = tmem_base + (uint32_t)((h * 2 + buf) * BN);
           uint32_t al = a_lo0, bl = desc_lo(smem_u32(b_smem + s * b_stage_bytes));
           uint32_t acc = 0;
@@ -303,7 +307,8 @@ tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
           for (int kb = 0; kb < P.nfull; ++kb) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
+              if (elect_one())
+                umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
               acc = 1;
             }
             al += (128 * 128) >> 4;
@@ -311,19 +316,25 @@ tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
           }
 #pragma unroll 1
           for (int t = 0; t < P.ntail; ++t) {
-            umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc, acc);
+            if (elect_one()) umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc, acc);
             acc = 1;
             al += (128 * 32) >> 4;
             bl += (BN * 32) >> 4;
           }
-          umma_commit(bar(S_FULL + h * 2 + buf));
-          umma_commit(bar(B_EMPTY + s));
+          if (elect_one()) {
+            umma_commit(bar(S_FULL + h * 2 + buf));
+            umma_commit(bar(B_EMPTY + s));
+          }
+          __syncwarp();
         }
-        umma_commit(bar(A_EMPTY));  // the row operand may be replaced once every MMA issued so far retired
+        // the row operand may be replaced once every MMA issued so far retired
+        if (elect_one()) umma_commit(bar(A_EMPTY));
+        __syncwarp();
         w += nseg;
         if (w < w_end) blk = next_blk(blk, w);
       }
-      if (*abort_flag) {  // wait (bounded) for every MMA issued by this lane before TMEM is freed
+      __syncwarp();
+      if (*abort_flag && lane == 0) {  // wait (bounded) for every MMA issued by this warp before TMEM is freed
         umma_commit(bar(DRAIN + h));
         mbar_wait_quiet(bar(DRAIN + h), 0);
       }
@@ -731,19 +742,21 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    // Score GEMM S_j = A . B_j^T into S/W buffer j%3. Issued by its own lane, the second GEMM by another
-    // warp's lane: a lane sharing its scheduler with soft-max warps sustains one MMA per ~90 cycles, and
-    // the 9 + 16 instructions of a tile would otherwise queue behind each other.
-    if (lane == 0) {
+    // Score GEMM S_j = A . B_j^T into S/W buffer j%3, issued from this warp, the second GEMM from another:
+    // one stream sharing its scheduler with soft-max warps sustains one MMA per ~90 cycles, and the 9 + 16
+    // instructions of a tile would otherwise queue behind each other. All 32 lanes run the loop (uniform
+    // descriptor arithmetic), one elected lane issues.
+    {
       constexpr uint32_t idesc1 = make_idesc(BN);
-      bool ok = mbar_wait(bar(A_FULL), 0, abort_flag, 2000);
+      // every exit decision is a warp vote: elect.sync needs all 32 lanes at the same instruction
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(A_FULL), 0, abort_flag, 2000));
       tc_fence_after();
       const uint32_t a_lo0 = desc_lo(smem_u32(a_smem));
 #pragma unroll 1
       for (int j = 0; ok && j < ntl; ++j) {
         const int s = j % p.nb, buf = j % kNSW;
-        if (!mbar_wait(bar(W_FREE + buf), ((j / kNSW) & 1) ^ 1, abort_flag, 2000)) break;
-        if (!mbar_wait(bar(B_FULL + s), (j / p.nb) & 1, abort_flag, 2000)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(W_FREE + buf), ((j / kNSW) & 1) ^ 1, abort_flag, 2000))) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_FULL + s), (j / p.nb) & 1, abort_flag, 2000))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * WCOLS;
         uint32_t al = a_lo0, bl = desc_lo(smem_u32(b_smem + s * b_bytes));
@@ -752,7 +765,8 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
         for (int kb = 0; kb < p.nfull; ++kb) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1, acc);
+            if (elect_one())
+              umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1, acc);
             acc = 1;
           }
           al += (128 * 128) >> 4;
@@ -760,31 +774,34 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
         }
 #pragma unroll 1
         for (int t = 0; t < p.ntail; ++t) {
-          umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc1, acc);
+          if (elect_one()) umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc1, acc);
           acc = 1;
           al += (128 * 32) >> 4;
           bl += (BN * 32) >> 4;
         }
-        umma_commit(bar(S_FULL + buf));
-        umma_commit(bar(B_EMPTY + s));
+        if (elect_one()) {
+          umma_commit(bar(S_FULL + buf));
+          umma_commit(bar(B_EMPTY + s));
+        }
+        __syncwarp();
       }
-      if (*abort_flag) {  // let every MMA issued by this thread retire before TMEM is freed
+      __syncwarp();
+      if (*abort_flag && lane == 0) {  // let every MMA issued by this warp retire before TMEM is freed
         umma_commit(bar(DRAIN));
         mbar_wait_quiet(bar(DRAIN), 0);
       }
     }
   } else if (warp == 3) {
     // Second GEMM O += W_j . V_j (W read from TMEM), once the soft-max warps have written W_j.
-    if (lane == 0) {
+    {
       const uint32_t idesc2 = make_idesc(p.dv_pad);
       const uint32_t v_blk_units = v_blk >> 4;
       uint32_t o_acc = 0;
-      bool ok = true;
 #pragma unroll 1
       for (int j = 0; j < ntl; ++j) {
         const int sv = j % p.nv, buf = j % kNSW;
-        if (!mbar_wait(bar(V_FULL + sv), (j / p.nv) & 1, abort_flag, 2000)) { ok = false; break; }
-        if (!mbar_wait(bar(W_FULL + buf), (j / kNSW) & 1, abort_flag, 2000)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(V_FULL + sv), (j / p.nv) & 1, abort_flag, 2000))) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(W_FULL + buf), (j / kNSW) & 1, abort_flag, 2000))) break;
         tc_fence_after();
         const uint32_t w_tmem = tmem_base + buf * WCOLS;
         const uint32_t v_lo0 = desc_lo(smem_u32(v_smem + sv * v_stage));
@@ -797,19 +814,24 @@ tc_pv_kernel(const __grid_constant__ CUtensorMap mapA_full, const __grid_constan
           for (int kb = 0; kb < BN / 32; ++kb) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_tf32_ts(o_tmem, wa + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
+              if (elect_one()) umma_tf32_ts(o_tmem, wa + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
               o_acc = 1;
             }
             wa += 32;
             vl += v_blk_units;
           }
         }
-        umma_commit(bar(V_EMPTY + sv));
-        umma_commit(bar(W_FREE + buf));
+        if (elect_one()) {
+          umma_commit(bar(V_EMPTY + sv));
+          umma_commit(bar(W_FREE + buf));
+        }
+        __syncwarp();
       }
-      (void)ok;
-      umma_commit(bar(O_FULL));
-      if (*abort_flag) mbar_wait_quiet(bar(O_FULL), 0);
+      __syncwarp();
+      if (lane == 0) {
+        umma_commit(bar(O_FULL));
+        if (*abort_flag) mbar_wait_quiet(bar(O_FULL), 0);
+      }
     }
   } else if (warp >= 4) {
     // Two warpgroups share the 128 rows: each takes half of every tile's 32-column chunks.
