@@ -160,8 +160,10 @@ tck_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUt
       }
     }
   } else if (warp == 1 || (warp == 3 && NHALF == 2)) {
-    // ===================== MMA issuers: one lane per 128-row half =====================
-    if (lane == 0) {
+    // ===================== MMA issuers: one warp per 128-row half =====================
+    // All 32 lanes run the loop (warp-uniform descriptor arithmetic), one elected lane issues; every exit
+    // decision is a warp vote, since elect.sync needs all lanes at the same instruction.
+    {
       const int h = (warp == 1) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc(BN);
       bool ok = true;
@@ -172,36 +174,44 @@ tck_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUt
       for (int w = w_begin; ok && w < w_end; ++w, ++jt) {
         const int buf = jt % NBUF;
         const uint32_t sph = (jt / NBUF) & 1;
-        if (!mbar_wait(bar(S_EMPTY + h * NBUF + buf), sph ^ 1, abort_flag, 2000)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(S_EMPTY + h * NBUF + buf), sph ^ 1, abort_flag, 2000))) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)((h * NBUF + buf) * BN);
         uint32_t acc = 0;
 #pragma unroll 1
         for (int kc = 0; kc < p.nk; ++kc) {
-          if (!mbar_wait(bar(FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(FULL + s), ph, abort_flag, 2000))) { ok = false; break; }
           tc_fence_after();
           const uint32_t stage_addr = smem_u32(ring + (size_t)s * kStage);
           const uint32_t al = desc_lo(stage_addr + h * kAHalf), bl = desc_lo(stage_addr + NHALF * kAHalf);
           if (kc + 1 < p.nk) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
+              if (elect_one())
+                umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
               acc = 1;
             }
           } else {
 #pragma unroll 1
             for (int ks = 0; ks < p.klast; ++ks) {
-              umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
+              if (elect_one())
+                umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
               acc = 1;
             }
           }
-          umma_commit(bar(EMPTY + s));
+          if (elect_one()) umma_commit(bar(EMPTY + s));
+          __syncwarp();
           if (++s == p.nstage) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(bar(S_FULL + h * NBUF + buf));
+        if (elect_one()) umma_commit(bar(S_FULL + h * NBUF + buf));
+        __syncwarp();
       }
-      if (*abort_flag) {  // wait (bounded) for every MMA issued by this lane before TMEM is freed
+      __syncwarp();
+      if (*abort_flag && lane == 0) {  // wait (bounded) for every MMA issued by this warp before TMEM is freed
         umma_commit(bar(DRAIN + h));
         mbar_wait_quiet(bar(DRAIN + h), 0);
       }
@@ -608,7 +618,8 @@ tck_pv_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {  // score GEMM(s) of tile j into buffer j % NSW, accumulated over the K chunks
+    {  // score GEMM(s) of tile j into buffer j % NSW, accumulated over the K chunks. All 32 lanes run the loop
+       // (warp-uniform descriptor arithmetic), one elected lane issues; exits are warp votes.
       constexpr uint32_t idesc1 = make_idesc(BN);
       bool ok = true;
       int s = 0;
@@ -616,13 +627,13 @@ tck_pv_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ 
 #pragma unroll 1
       for (int j = 0; ok && j < p.ntiles; ++j) {
         const int buf = j % NSW;
-        if (!mbar_wait(bar(W_FREE + buf), ((j / NSW) & 1) ^ 1, abort_flag, 2000)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(W_FREE + buf), ((j / NSW) & 1) ^ 1, abort_flag, 2000))) break;
         tc_fence_after();
         const uint32_t s_tmem = tmem_base + buf * BUFCOLS;
         uint32_t acc = 0;
 #pragma unroll 1
         for (int kc = 0; kc < p.nk; ++kc) {
-          if (!mbar_wait(bar(FULL + s), ph, abort_flag, 2000)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(FULL + s), ph, abort_flag, 2000))) { ok = false; break; }
           tc_fence_after();
           const uint32_t stage_addr = smem_u32(ring + (size_t)s * kStage);
           const uint32_t al = desc_lo(stage_addr), a2l = desc_lo(stage_addr + kAChunk),
@@ -630,33 +641,38 @@ tck_pv_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ 
           const int nks = (kc + 1 < p.nk) ? 4 : p.klast;
 #pragma unroll 1
           for (int ks = 0; ks < nks; ++ks) {
-            umma_tf32(s_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1, acc);
-            if (MAT5)
-              umma_tf32(s_tmem + WCOLS, pack_desc(a2l + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1,
-                        acc);
+            if (elect_one()) {
+              umma_tf32(s_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc1, acc);
+              if (MAT5)
+                umma_tf32(s_tmem + WCOLS, pack_desc(a2l + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128),
+                          idesc1, acc);
+            }
             acc = 1;
           }
-          umma_commit(bar(EMPTY + s));
+          if (elect_one()) umma_commit(bar(EMPTY + s));
+          __syncwarp();
           if (++s == p.nstage) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(bar(S_FULL + buf));
+        if (elect_one()) umma_commit(bar(S_FULL + buf));
+        __syncwarp();
       }
-      if (*abort_flag) {
+      __syncwarp();
+      if (*abort_flag && lane == 0) {
         umma_commit(bar(DRAIN));
         mbar_wait_quiet(bar(DRAIN), 0);
       }
     }
   } else if (warp == 3) {
-    if (lane == 0) {  // second GEMM O += W_j . V_j (W read from TMEM) once the weights of tile j are written
+    {  // second GEMM O += W_j . V_j (W read from TMEM) once the weights of tile j are written
       const uint32_t idesc2 = make_idesc(p.dv_pad);
       const uint32_t v_blk_units = v_blk >> 4;
       uint32_t o_acc = 0;
 #pragma unroll 1
       for (int j = 0; j < p.ntiles; ++j) {
         const int sv = j % p.nv, buf = j % NSW;
-        if (!mbar_wait(bar(V_FULL + sv), (j / p.nv) & 1, abort_flag, 2000)) break;
-        if (!mbar_wait(bar(W_FULL + buf), (j / NSW) & 1, abort_flag, 2000)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(V_FULL + sv), (j / p.nv) & 1, abort_flag, 2000))) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(W_FULL + buf), (j / NSW) & 1, abort_flag, 2000))) break;
         tc_fence_after();
         const uint32_t w_tmem = tmem_base + buf * BUFCOLS;
         const uint32_t v_lo0 = desc_lo(smem_u32(v_smem + (size_t)sv * v_stage));
@@ -668,18 +684,24 @@ tck_pv_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ 
           for (int kb = 0; kb < BN / 32; ++kb) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_tf32_ts(o_tmem, wa + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
+              if (elect_one()) umma_tf32_ts(o_tmem, wa + ks * 8, pack_desc(vl + 2 * ks, kDescHi128), idesc2, o_acc);
               o_acc = 1;
             }
             wa += 32;
             vl += v_blk_units;
           }
         }
-        umma_commit(bar(V_EMPTY + sv));
-        umma_commit(bar(W_FREE + buf));
+        if (elect_one()) {
+          umma_commit(bar(V_EMPTY + sv));
+          umma_commit(bar(W_FREE + buf));
+        }
+        __syncwarp();
       }
-      umma_commit(bar(O_FULL));
-      if (*abort_flag) mbar_wait_quiet(bar(O_FULL), 0);
+      __syncwarp();
+      if (lane == 0) {
+        umma_commit(bar(O_FULL));
+        if (*abort_flag) mbar_wait_quiet(bar(O_FULL), 0);
+      }
     }
   } else if (warp >= 4) {
     // Two warpgroups share the 128 rows: each takes half of every tile's 32-column chunks.
