@@ -58,6 +58,7 @@ SIGNATURES = {
     "fs_set_pv_split": (c_int, [c_int]),
     "fs_engine": (c_int, [c_int, c_int, c_int, c_int]),
     "fs_plan_ctas": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "fs_plan_pv_split": (c_int, [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),
     "fs_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "fs_workspace_bytes_labels": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "fs_lse": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_float, c_float, c_float, c_int, _P, c_size_t, _P]),

@@ -416,6 +416,10 @@ int fs_engine(int n, int m, int d, int prec) {
   return tc::k_streamed(d, prec, 0) ? 2 : 1;
 }
 
+int fs_plan_pv_split(int rows, int cols, int prec, int sms, int* slots) {
+  return tc::plan_pv_split(rows, cols, prec, sms, slots);
+}
+
 int fs_plan_ctas(int n_row_blocks, int n_col_tiles, int sms, int reserved, int limit) {
   return tc::plan_ctas(n_row_blocks, n_col_tiles, sms, reserved, limit);
 }

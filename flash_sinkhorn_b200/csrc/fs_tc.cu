@@ -1592,6 +1592,15 @@ cudaError_t launch_pv(const CUtensorMap* maps, const PvKernelParams& kp, int gri
 
 }  // namespace
 
+int plan_pv_split(int rows, int cols, int prec, int sms, int* slots) {
+  if (rows <= 0 || cols <= 0 || sms <= 0) return 0;
+  const int bn = prec == 1 ? 64 : 128;
+  const int nm = rows > cols ? rows : cols;
+  const int have = pv_share_slots(nm, bn);
+  if (slots) *slots = have;
+  return pick_pv_split((rows + 127) / 128, (cols + bn - 1) / bn, have, sms);
+}
+
 bool pv_supported(int d, int prec, int dv, int nlab) {
   if (prec != 0 && prec != 1) return false;
   if (plan_shape(d, prec, nlab).streamed) return dv >= 1;  // one column, or V in slices through kstream_pv

@@ -44,6 +44,10 @@ int set_cta_limit(int k);
 // CTA count a streaming pass over nblk row blocks x ntiles column tiles would get on a device with `sms`
 // SMs of which `reserved` are left free and with CTA limit `limit` (0 = none). Pure host arithmetic.
 int plan_ctas(int nblk, int ntiles, int sms, int reserved, int limit);
+// Host arithmetic of the plan-times-matrix kernel with the row operand resident: column shares per row block
+// for `rows` output rows against `cols` columns on `sms` SMs (prec 0: 128-column tiles, 1: 64-column tiles), and
+// through *slots (may be null) the raw output tiles the scratch holds for clouds of at most max(rows, cols) points.
+int plan_pv_split(int rows, int cols, int prec, int sms, int* slots);
 
 bool supported(int n, int m, int d, int prec, int nlab = 0);
 size_t staged_bytes(int n, int m, int d, int prec, int nlab = 0);

@@ -138,6 +138,13 @@ int fs_engine(int n, int m, int d, int prec);
  * limit is `limit` (0 = none). At most 16 CTAs ever share a row block. Returns 0 on non-positive sizes. */
 int fs_plan_ctas(int n_row_blocks, int n_col_tiles, int sms, int reserved, int limit);
 
+/* Host arithmetic only (no reference counterpart): the column shares per 128-row block that the plan-times-matrix
+ * kernel with the row operand resident uses for `rows` output rows against `cols` columns on a device with `sms`
+ * SMs (prec FS_PREC_TF32: 128-column tiles, FS_PREC_FP32: 64-column tiles); *slots (may be NULL) receives the number
+ * of raw output tiles the scratch holds for clouds of at most max(rows, cols) points. rows/128 * shares never
+ * exceeds it, and a share never has fewer than 8 column tiles. Returns 0 on non-positive sizes. */
+int fs_plan_pv_split(int rows, int cols, int prec, int sms, int* slots);
+
 /* Optional label-augmented ground cost (OTDD), reference kernels/sinkhorn_flashstyle_sqeuclid.py:545-560
  * and kernels/sinkhorn_triton_grad_sqeuclid.py:225-236: the logit of entry (i, j) becomes
  *   (lambda_x * 2cs * x_i.y_j - lambda_y * cs * W[label_x_i, label_y_j]) / eps + bias_j.

@@ -67,3 +67,31 @@ def test_cta_split_respects_the_sm_count_and_the_partial_slots(sms):
                 if nblk * ntiles <= 200000:  # the check walks every row block
                     assert _pieces(nblk, ntiles, g) <= 16
     assert lib.fs_plan_ctas(0, 5, sms, 0, 0) == 0
+
+
+@pytest.mark.parametrize("sms", [148, 132, 16])
+def test_matrix_pass_column_shares_fit_the_scratch(sms):
+    """Column shares of the plan-times-matrix kernel: never more raw output tiles than the scratch was sized for
+    (sized from the larger cloud, used for any row range of it), at least 8 column tiles per share, none for
+    small clouds, and a better SM fill than without shares whenever shares are used."""
+    import ctypes
+    lib = _lib.load()
+    for prec, bn in ((0, 128), (1, 64)):
+        for n, m in [(50000, 50000), (6250, 50000), (50000, 6250), (4096, 4096), (1000, 900), (300, 9000), (128, 128),
+                     (100000, 80000), (1, 1), (200000, 200000)]:
+            slots = ctypes.c_int(-1)
+            s = lib.fs_plan_pv_split(n, m, prec, sms, ctypes.byref(slots))
+            nblk, ntiles = (n + 127) // 128, (m + bn - 1) // bn
+            assert 1 <= s <= 8
+            if s > 1:
+                assert nblk * s <= slots.value
+                assert ntiles // s >= 8
+                fill = lambda k: nblk * k / (-(-nblk * k // sms) * sms)
+                assert fill(s) > fill(1)
+            # a row shard of the same problem must fit the slots sized for the whole problem
+            full = ctypes.c_int(-1)
+            lib.fs_plan_pv_split(max(n, m), max(n, m), prec, sms, ctypes.byref(full))
+            assert slots.value == full.value
+            if -(-max(n, m) // bn) < 16:  # fewer than 16 column tiles: no shares
+                assert slots.value == 0 and s == 1
+    assert lib.fs_plan_pv_split(0, 5, 0, sms, None) == 0
