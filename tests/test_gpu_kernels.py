@@ -249,7 +249,7 @@ def test_c_transform_shapes_and_ties(monkeypatch, mode, n, m, d):
 
 @pytest.mark.parametrize("tf32", [True, False])
 @pytest.mark.parametrize("n,m,d,vec", [(2100, 4200, 16, False), (4200, 2100, 40, False), (2305, 5000, 8, True),
-                                       (300, 9000, 24, False), (1300, 4100, 100, False)])
+                                       (300, 9000, 24, False), (1300, 4100, 100, False), (700, 4100, 140, False)])
 @pytest.mark.parametrize("split", [0, 1, 2, 3, 4])
 def test_plan_times_matrix_work_split(n, m, d, vec, split, tf32):
     """The plan-times-matrix kernel with the row operand resident cuts the column range of a row block into
