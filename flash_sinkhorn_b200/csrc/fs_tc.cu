@@ -273,8 +273,13 @@ tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
     // well before the soft-max warps ask for them, instead of just in time. All 32 lanes run the loop and one
     // elected lane issues: descriptor arithmetic is then warp-uniform (uniform registers, which is where
     // tcgen05 instructions take their operands) instead of per-thread values moved over for every MMA. Every
-    // exit decision is a warp vote, since elect.sync needs all 32 lanes at the same instruction.
-    {
+    // exit decision is a warp vote, since elect.sync needs all 32 lanes at the same instruction. Tile lists keep
+    // the loop on lane 0 alone (kWarpIssue false): with one MMA per tile (d = 3) and the list look-ups in the
+    // loop the converged form measured 15 % slower per pass there.
+    constexpr bool kWarpIssue = !CSR;
+    auto vote = [&](bool okl) { return kWarpIssue ? (__all_sync(0xffffffffu, okl) != 0) : okl; };
+    auto pick = [&]() { return kWarpIssue ? elect_one() : true; };
+    if (kWarpIssue || lane == 0) {
       const int h = (warp == 1) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc(BN);
       const uint32_t a_lo0 = desc_lo(smem_u32(a_smem + h * a_half_bytes));
@@ -284,16 +289,16 @@ tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
 #pragma unroll 1
       for (int w = w_begin; ok && w < w_end; ++seg) {
         const int nseg = (row_end(blk) < w_end ? row_end(blk) : w_end) - w;
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(A_FULL), seg & 1, abort_flag, 2000))) break;
+        if (!vote(mbar_wait(bar(A_FULL), seg & 1, abort_flag, 2000))) break;
         tc_fence_after();
 #pragma unroll 1
         for (int i = 0; i < nseg; ++i, ++jt) {
           const int s = jt % P.nstage;
           const uint32_t ph = (jt / P.nstage) & 1;
-          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000))) { ok = false; break; }
+          if (!vote(mbar_wait(bar(B_FULL + s), ph, abort_flag, 2000))) { ok = false; break; }
           const int buf = jt & 1;
           const uint32_t sph = (jt >> 1) & 1;
-          if (!__all_sync(0xffffffffu, mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000))) {
+          if (!vote(mbar_wait(bar(S_EMPTY + h * 2 + buf), sph ^ 1, abort_flag, 2000))) {
             ok = false;
             break;
           }
@@ -306,13 +311,13 @@ tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
           // 10 % for the arg-max pass), one per instruction in the 128-row plans with their long K (d = 128:
           // 1.3 % faster that way). kTileElect false: all lanes enter and every instruction is elected.
           constexpr bool kTileElect = (NHALF == 2);
-          if (kTileElect ? elect_one() : true) {
+          if (kTileElect ? pick() : true) {
             uint32_t acc = 0;
 #pragma unroll 1
             for (int kb = 0; kb < P.nfull; ++kb) {
 #pragma unroll
               for (int ks = 0; ks < 4; ++ks) {
-                if (kTileElect || elect_one())
+                if (kTileElect || pick())
                   umma_tf32(d_tmem, pack_desc(al + 2 * ks, kDescHi128), pack_desc(bl + 2 * ks, kDescHi128), idesc, acc);
                 acc = 1;
               }
@@ -321,26 +326,26 @@ tc_lse_kernel(const __grid_constant__ Launch<NSUB> P) {
             }
 #pragma unroll 1
             for (int t = 0; t < P.ntail; ++t) {
-              if (kTileElect || elect_one())
+              if (kTileElect || pick())
                 umma_tf32(d_tmem, pack_desc(al, kDescHi32), pack_desc(bl, kDescHi32), idesc, acc);
               acc = 1;
               al += (128 * 32) >> 4;
               bl += (BN * 32) >> 4;
             }
-            if (kTileElect || elect_one()) {
+            if (kTileElect || pick()) {
               umma_commit(bar(S_FULL + h * 2 + buf));
               umma_commit(bar(B_EMPTY + s));
             }
           }
-          __syncwarp();
+          if (kWarpIssue) __syncwarp();
         }
         // the row operand may be replaced once every MMA issued so far retired
-        if (elect_one()) umma_commit(bar(A_EMPTY));
-        __syncwarp();
+        if (pick()) umma_commit(bar(A_EMPTY));
+        if (kWarpIssue) __syncwarp();
         w += nseg;
         if (w < w_end) blk = next_blk(blk, w);
       }
-      __syncwarp();
+      if (kWarpIssue) __syncwarp();
       if (*abort_flag && lane == 0) {  // wait (bounded) for every MMA issued by this warp before TMEM is freed
         umma_commit(bar(DRAIN + h));
         mbar_wait_quiet(bar(DRAIN + h), 0);
